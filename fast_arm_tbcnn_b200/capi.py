@@ -1,0 +1,207 @@
+"""ctypes binding of include/tbn_cuda.h.
+
+Device memory comes from torch (``tensor.data_ptr()``); torch is plumbing only -- every
+computation below runs in the library's own kernels.  There is no fallback: if the shared
+library is missing ``load()`` raises, and every call checks the returned status.
+"""
+import ctypes as C
+import os
+
+from . import build as _build
+
+MODE_AUTO, MODE_TC_BF16X1, MODE_TC_BF16X2, MODE_TC_BF16X3, MODE_SIMT = 0, 1, 2, 3, 4
+EPI_RELU, EPI_BIAS_BEFORE_ALPHA = 1, 2
+LAYOUT_KN, LAYOUT_NK = 0, 1
+
+_vp, _i64, _i32, _f32, _u32, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_uint32, C.c_size_t
+
+#: name -> (restype, argtypes); must list every symbol include/tbn_cuda.h declares.
+SIGNATURES = {
+    "tbn_cuda_init": (_i32, [_i32]),
+    "tbn_cuda_last_error": (_i32, [C.c_char_p, _sz]),
+    "tbn_cuda_malloc": (_i32, [C.POINTER(_vp), _sz]),
+    "tbn_cuda_free": (_i32, [_vp]),
+    "tbn_cuda_memset": (_i32, [_vp, _i32, _sz, _vp]),
+    "tbn_cuda_h2d": (_i32, [_vp, _vp, _sz, _vp]),
+    "tbn_cuda_d2h": (_i32, [_vp, _vp, _sz, _vp]),
+    "tbn_cuda_d2d": (_i32, [_vp, _vp, _sz, _vp]),
+    "tbn_cuda_sync": (_i32, [_vp]),
+    "tbn_cuda_launch_count": (_i64, []),
+    "tbn_packed_dims": (_i32, [_i64, _i64, C.POINTER(_i64), C.POINTER(_i64)]),
+    "tbn_quantize_to_binary": (_i32, [_vp, _i64, _f32, _vp, _vp]),
+    "tbn_quantize_to_ternary": (_i32, [_vp, _i64, _f32, _f32, _vp, _vp]),
+    "tbn_quant_pack_workspace_bytes": (_sz, [_i64, _i64, _i32]),
+    "tbn_quant_pack_binary": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _i32, _vp, _vp, _vp, _sz, _vp]),
+    "tbn_quant_pack_ternary": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _f32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "tbn_gemm_workspace_bytes": (_sz, [_i64, _i64, _i32]),
+    "tbn_gemm_fxb": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _i32, _u32, _vp, _sz, _vp]),
+    "tbn_gemm_tbn": (_i32, [_vp, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _u32, _vp, _sz, _vp]),
+}
+
+
+class TbnError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"tbn_cuda status {status}: {message}")
+        self.status = status
+
+
+_LIB = None
+
+
+def load(path=None):
+    """Loads lib/libtbn_cuda.so (building it first when the sources are newer and nvcc exists)."""
+    global _LIB
+    if _LIB is not None and path is None:
+        return _LIB
+    path = path or _build.LIB_PATH
+    if not os.path.exists(path):
+        try:
+            _build.build()
+        except Exception as exc:  # noqa: BLE001
+            raise ImportError(f"{path} is missing and could not be built: {exc}") from exc
+    handle = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(handle, name)  # AttributeError if the library does not export it
+        fn.restype, fn.argtypes = res, args
+    _LIB = handle
+    return handle
+
+
+def last_error():
+    buf = C.create_string_buffer(1024)
+    load().tbn_cuda_last_error(buf, 1024)
+    return buf.value.decode(errors="replace")
+
+
+def check(status):
+    if status != 0:
+        raise TbnError(status, last_error())
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _Lib:
+    """Tensor-level convenience wrappers (torch CUDA tensors in, torch CUDA tensors out)."""
+
+    def __init__(self):
+        self._inited = set()
+
+    @property
+    def h(self):
+        return load()
+
+    def init(self, device=None):
+        import torch
+        if device is None:
+            device = torch.cuda.current_device()
+        if device not in self._inited:
+            check(self.h.tbn_cuda_init(device))
+            self._inited.add(device)
+        return device
+
+    def sync(self):
+        check(self.h.tbn_cuda_sync(_stream()))
+
+    def launch_count(self):
+        return int(self.h.tbn_cuda_launch_count())
+
+    @staticmethod
+    def packed_dims(K, N):
+        return (K + 127) // 128 * 128, (N + 7) // 8 * 8
+
+    # ---- quantise / pack --------------------------------------------------------------
+    def quantize_to_binary(self, w, thr=0.0):
+        import torch
+        self.init()
+        w = w.contiguous()
+        out = torch.empty(w.shape, dtype=torch.uint8, device=w.device)
+        check(self.h.tbn_quantize_to_binary(_ptr(w), w.numel(), thr, _ptr(out), _stream()))
+        return out
+
+    def quantize_to_ternary(self, w, lo=-0.1, hi=0.1):
+        import torch
+        self.init()
+        w = w.contiguous()
+        out = torch.empty(w.shape, dtype=torch.int8, device=w.device)
+        check(self.h.tbn_quantize_to_ternary(_ptr(w), w.numel(), lo, hi, _ptr(out), _stream()))
+        return out
+
+    def quant_pack_binary(self, w, layout=LAYOUT_KN, thr=0.0, ge=False, want_alpha=True):
+        """-> (words int32-viewed-as-uint32 [N_pad, K_pad/32], alpha [N] or None)."""
+        import torch
+        self.init()
+        assert w.dim() == 2 and w.dtype == torch.float32 and w.stride(1) == 1
+        K, N = (w.shape if layout == LAYOUT_KN else (w.shape[1], w.shape[0]))
+        Kp, Np = self.packed_dims(K, N)
+        words = torch.empty((Np, Kp // 32), dtype=torch.int32, device=w.device)
+        alpha = torch.empty(N, dtype=torch.float32, device=w.device) if want_alpha else None
+        ws_bytes = self.h.tbn_quant_pack_workspace_bytes(K, N, 0) if want_alpha else 0
+        ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=w.device)
+        check(self.h.tbn_quant_pack_binary(_ptr(w), K, N, w.stride(0), layout, thr, int(ge), _ptr(words), _ptr(alpha),
+                                           _ptr(ws), ws_bytes, _stream()))
+        return words, alpha
+
+    def quant_pack_ternary(self, w, lo, hi, layout=LAYOUT_KN, want_alpha=True, want_codes=True):
+        """-> (codes [(K*N+15)/16] or None, pos, neg [N_pad, K_pad/32], alpha [N] or None)."""
+        import torch
+        self.init()
+        assert w.dim() == 2 and w.dtype == torch.float32 and w.stride(1) == 1
+        K, N = (w.shape if layout == LAYOUT_KN else (w.shape[1], w.shape[0]))
+        Kp, Np = self.packed_dims(K, N)
+        pos = torch.empty((Np, Kp // 32), dtype=torch.int32, device=w.device)
+        neg = torch.empty_like(pos)
+        codes = torch.empty((K * N + 15) // 16, dtype=torch.int32, device=w.device) if want_codes else None
+        alpha = torch.empty(N, dtype=torch.float32, device=w.device) if want_alpha else None
+        ws_bytes = self.h.tbn_quant_pack_workspace_bytes(K, N, 1) if want_alpha else 0
+        ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=w.device)
+        check(self.h.tbn_quant_pack_ternary(_ptr(w), K, N, w.stride(0), layout, lo, hi, _ptr(codes), _ptr(pos), _ptr(neg),
+                                            _ptr(alpha), _ptr(ws), ws_bytes, _stream()))
+        return codes, pos, neg, alpha
+
+    # ---- GEMM ---------------------------------------------------------------------------
+    def gemm_workspace(self, M, K, mode, device):
+        import torch
+        nbytes = self.h.tbn_gemm_workspace_bytes(M, K, mode)
+        return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device), nbytes
+
+    def gemm_fxb(self, a, neg, N, pos=None, alpha=None, scale=1.0, bias=None, mode=MODE_AUTO, epilogue=0, out=None,
+                 workspace=None):
+        import torch
+        self.init()
+        assert a.dim() == 2 and a.dtype == torch.float32 and a.stride(1) == 1
+        M, K = a.shape
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        if workspace is None:
+            workspace, nbytes = self.gemm_workspace(M, K, mode, a.device)
+        else:
+            nbytes = workspace.numel() * workspace.element_size()
+        check(self.h.tbn_gemm_fxb(_ptr(a), M, K, a.stride(0), _ptr(neg), _ptr(pos), N, _ptr(alpha), scale, _ptr(bias),
+                                  _ptr(out), out.stride(0), mode, epilogue, _ptr(workspace), nbytes, _stream()))
+        return out
+
+    def gemm_tbn(self, a, neg, N, lo=-0.1, hi=0.1, alpha=None, scale=1.0, bias=None, epilogue=0, out=None,
+                 workspace=None):
+        import torch
+        self.init()
+        assert a.dim() == 2 and a.dtype == torch.float32 and a.stride(1) == 1
+        M, K = a.shape
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        if workspace is None:
+            workspace, nbytes = self.gemm_workspace(M, K, MODE_TC_BF16X1, a.device)
+        else:
+            nbytes = workspace.numel() * workspace.element_size()
+        check(self.h.tbn_gemm_tbn(_ptr(a), M, K, a.stride(0), lo, hi, _ptr(neg), N, _ptr(alpha), scale, _ptr(bias),
+                                  _ptr(out), out.stride(0), epilogue, _ptr(workspace), nbytes, _stream()))
+        return out
+
+
+lib = _Lib()

@@ -1,0 +1,277 @@
+// Weight quantise-and-pack kernels (HBM-bound, one read of the fp32 weights).
+//
+// Replaces, in one pass: tbn::quantize_to_binary / quantize_to_ternary
+// (tbn-runtime/src/operators/quantized_gemm_neon.cpp:544-597), the +1 padding and
+// BinaryMatrix::pack (quantized_gemm_neon.cpp:199-214, GeMM/05-final/GeMM.cpp:114-151),
+// the Session's transposed conv-weight packing (tbn/runtime/model.hpp:464-477) and the
+// TernaryPackedWeights::set_weight loop (tbn/memory/packed_weights.hpp:53-71).
+//
+// Packed layout (all planes): uint32 word[n * (K_pad/32) + k/32], bit (k % 32);
+// K_pad = ceil128(K), N_pad = ceil8(N); padding bits are 0.
+// Comparisons are IEEE (no flush-to-zero on the compare, NaN compares false).
+#include "common.cuh"
+
+namespace tbn_cuda {
+namespace {
+
+constexpr int kChunkK = 128;  // k rows per partial sum / per uint4 of packed words
+
+// +1/-1/0 decision of one weight.  Returns bit0 = "negative plane", bit1 = "positive plane".
+// Binary: the negative-plane bit is what the reference packs (bit set <=> -1).
+template <bool TERNARY>
+__device__ __forceinline__ uint32_t classify(float w, float lo_or_thr, float hi, int ge) {
+    if (TERNARY) {
+        const uint32_t neg = w < lo_or_thr ? 1u : 0u;
+        const uint32_t pos = (!neg && w > hi) ? 2u : 0u;
+        return neg | pos;
+    }
+    const bool plus = ge ? (w >= lo_or_thr) : (w > lo_or_thr);
+    return plus ? 0u : 1u;
+}
+
+// Layout KN: W[k*ldw + n].  One warp packs a 128(k) x 32(n) tile: lane = column, rows read
+// coalesced (128 B per row), 4 words per plane written as one uint4 per lane.
+template <bool TERNARY>
+__global__ void __launch_bounds__(128) pack_kn_kernel(const float* __restrict__ w, int64_t K, int64_t N,
+                                                      int64_t ldw, float lo, float hi, int ge,
+                                                      uint32_t* __restrict__ neg_words,
+                                                      uint32_t* __restrict__ pos_words, int64_t KW,
+                                                      int64_t N_pad, float* __restrict__ part_sum,
+                                                      float* __restrict__ part_cnt) {
+    const int lane = threadIdx.x & 31;
+    const int64_t chunk = static_cast<int64_t>(blockIdx.y) * 4 + (threadIdx.x >> 5);
+    const int64_t n = static_cast<int64_t>(blockIdx.x) * 32 + lane;
+    if (chunk * kChunkK >= KW * 32 || n >= N_pad) return;
+    const int64_t k0 = chunk * kChunkK;
+    uint32_t negw[4] = {0, 0, 0, 0}, posw[4] = {0, 0, 0, 0};
+    float sum = 0.0f, cnt = 0.0f;
+    if (n < N) {
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            float v[32];
+#pragma unroll
+            for (int r = 0; r < 32; ++r) {
+                const int64_t k = k0 + wi * 32 + r;
+                v[r] = (k < K) ? __ldg(w + k * ldw + n) : __int_as_float(0x7fc00000);
+            }
+#pragma unroll
+            for (int r = 0; r < 32; ++r) {
+                const int64_t k = k0 + wi * 32 + r;
+                if (k < K) {
+                    const uint32_t c = classify<TERNARY>(v[r], lo, hi, ge);
+                    negw[wi] |= (c & 1u) << r;
+                    if (TERNARY) {
+                        posw[wi] |= (c >> 1) << r;
+                        if (c) {
+                            sum += fabsf(v[r]);
+                            cnt += 1.0f;
+                        }
+                    } else {
+                        sum += fabsf(v[r]);
+                    }
+                }
+            }
+        }
+    }
+    const int64_t widx = n * KW + chunk * 4;
+    *reinterpret_cast<uint4*>(neg_words + widx) = make_uint4(negw[0], negw[1], negw[2], negw[3]);
+    if (TERNARY) *reinterpret_cast<uint4*>(pos_words + widx) = make_uint4(posw[0], posw[1], posw[2], posw[3]);
+    if (part_sum && n < N) {
+        part_sum[chunk * N + n] = sum;
+        if (TERNARY) part_cnt[chunk * N + n] = cnt;
+    }
+}
+
+// Layout NK: W[n*ldw + k] (k contiguous).  One warp packs one 128-k chunk of one column:
+// four coalesced 128 B reads, four ballots.
+template <bool TERNARY>
+__global__ void __launch_bounds__(128) pack_nk_kernel(const float* __restrict__ w, int64_t K, int64_t N,
+                                                      int64_t ldw, float lo, float hi, int ge,
+                                                      uint32_t* __restrict__ neg_words,
+                                                      uint32_t* __restrict__ pos_words, int64_t KW,
+                                                      int64_t N_pad, float* __restrict__ part_sum,
+                                                      float* __restrict__ part_cnt) {
+    const int lane = threadIdx.x & 31;
+    const int64_t chunk = static_cast<int64_t>(blockIdx.y) * 4 + (threadIdx.x >> 5);
+    const int64_t n = blockIdx.x;
+    if (chunk * kChunkK >= KW * 32) return;
+    const int64_t k0 = chunk * kChunkK;
+    float v[4];
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        const int64_t k = k0 + wi * 32 + lane;
+        v[wi] = (n < N && k < K) ? __ldg(w + n * ldw + k) : __int_as_float(0x7fc00000);
+    }
+    uint32_t negw[4], posw[4];
+    float sum = 0.0f, cnt = 0.0f;
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        const int64_t k = k0 + wi * 32 + lane;
+        const bool valid = n < N && k < K;
+        const uint32_t c = valid ? classify<TERNARY>(v[wi], lo, hi, ge) : 0u;
+        negw[wi] = __ballot_sync(0xffffffffu, c & 1u);
+        posw[wi] = TERNARY ? __ballot_sync(0xffffffffu, c & 2u) : 0u;
+        if (valid && (!TERNARY || c)) {
+            sum += fabsf(v[wi]);
+            cnt += 1.0f;
+        }
+    }
+    // Deterministic in-warp tree reduction of the partial |w| sum.
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        sum += __shfl_down_sync(0xffffffffu, sum, off);
+        cnt += __shfl_down_sync(0xffffffffu, cnt, off);
+    }
+    if (lane == 0) {
+        const int64_t widx = n * KW + chunk * 4;
+        *reinterpret_cast<uint4*>(neg_words + widx) = make_uint4(negw[0], negw[1], negw[2], negw[3]);
+        if (TERNARY) *reinterpret_cast<uint4*>(pos_words + widx) = make_uint4(posw[0], posw[1], posw[2], posw[3]);
+        if (part_sum && n < N) {
+            part_sum[chunk * N + n] = sum;
+            if (TERNARY) part_cnt[chunk * N + n] = cnt;
+        }
+    }
+}
+
+// alpha[n] = (sum over chunks, in chunk order) / (K or number of non-zero weights).
+__global__ void alpha_finalize_kernel(const float* __restrict__ part_sum, const float* __restrict__ part_cnt,
+                                      int64_t chunks, int64_t N, int64_t K, float* __restrict__ alpha) {
+    const int64_t n = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float s = 0.0f, c = 0.0f;
+    for (int64_t i = 0; i < chunks; ++i) {
+        s += part_sum[i * N + n];
+        if (part_cnt) c += part_cnt[i * N + n];
+    }
+    if (part_cnt) alpha[n] = c > 0.0f ? __fdiv_rn(s, c) : 0.0f;
+    else alpha[n] = __fdiv_rn(s, static_cast<float>(K));
+}
+
+// Reference 2-bit codes over the flat row-major [K,N] element order: one thread per uint32.
+__global__ void ternary_codes_kernel(const float* __restrict__ w, int64_t K, int64_t N, int64_t ldw, int layout,
+                                     float lo, float hi, uint32_t* __restrict__ codes, int64_t n_words) {
+    const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (j >= n_words) return;
+    const int64_t total = K * N;
+    uint32_t word = 0;
+#pragma unroll 4
+    for (int e = 0; e < 16; ++e) {
+        const int64_t i = j * 16 + e;
+        if (i >= total) break;
+        const int64_t k = i / N, n = i - k * N;
+        const float v = layout == TBN_LAYOUT_KN ? __ldg(w + k * ldw + n) : __ldg(w + n * ldw + k);
+        const uint32_t code = v < lo ? 0u : (v > hi ? 2u : 1u);
+        word |= code << (2 * e);
+    }
+    codes[j] = word;
+}
+
+__global__ void quantize_binary_kernel(const float* __restrict__ w, int64_t n, float thr, uint8_t* __restrict__ out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = w[i] > thr ? 1 : 0;
+}
+
+__global__ void quantize_ternary_kernel(const float* __restrict__ w, int64_t n, float lo, float hi,
+                                        int8_t* __restrict__ out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = w[i];
+        out[i] = v < lo ? -1 : (v > hi ? 1 : 0);
+    }
+}
+
+int grid_for(int64_t n, int block) {
+    const int64_t want = (n + block - 1) / block;
+    const int64_t cap = static_cast<int64_t>(sm_count() > 0 ? sm_count() : 148) * 16;
+    return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+template <bool TERNARY>
+int32_t quant_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout, float lo, float hi,
+                   int32_t ge, uint32_t* d_neg, uint32_t* d_pos, float* d_alpha, void* d_ws, size_t ws_bytes,
+                   cudaStream_t st) {
+    TBN_REQUIRE(K > 0 && N > 0, TBN_INVALID_SHAPE, "quant_pack: K and N must be positive");
+    TBN_REQUIRE(d_w && d_neg && (!TERNARY || d_pos), TBN_INVALID_ARGUMENT, "quant_pack: null pointer");
+    TBN_REQUIRE(layout == TBN_LAYOUT_KN || layout == TBN_LAYOUT_NK, TBN_INVALID_ARGUMENT, "quant_pack: bad layout");
+    TBN_REQUIRE(ldw >= (layout == TBN_LAYOUT_KN ? N : K), TBN_INVALID_ARGUMENT, "quant_pack: ldw too small");
+    const int64_t K_pad = round_up(K, 128), N_pad = round_up(N, 8), KW = K_pad / 32;
+    const int64_t chunks = K_pad / kChunkK;
+    TBN_REQUIRE(N_pad <= 0x7fffffffLL && chunks <= 4LL * 65535, TBN_INVALID_SHAPE, "quant_pack: matrix too large");
+    float* part_sum = nullptr;
+    float* part_cnt = nullptr;
+    if (d_alpha) {
+        const size_t need = tbn_quant_pack_workspace_bytes(K, N, TERNARY ? 1 : 0);
+        TBN_REQUIRE(d_ws && ws_bytes >= need, TBN_INVALID_ARGUMENT, "quant_pack: workspace too small for alpha");
+        part_sum = static_cast<float*>(d_ws);
+        if (TERNARY) part_cnt = part_sum + chunks * N;
+    }
+    const unsigned gy = static_cast<unsigned>((chunks + 3) / 4);
+    if (layout == TBN_LAYOUT_KN) {
+        dim3 grid(static_cast<unsigned>((N_pad + 31) / 32), gy);
+        pack_kn_kernel<TERNARY><<<grid, 128, 0, st>>>(d_w, K, N, ldw, lo, hi, ge, d_neg, d_pos, KW, N_pad, part_sum,
+                                                      part_cnt);
+    } else {
+        dim3 grid(static_cast<unsigned>(N_pad), gy);
+        pack_nk_kernel<TERNARY><<<grid, 128, 0, st>>>(d_w, K, N, ldw, lo, hi, ge, d_neg, d_pos, KW, N_pad, part_sum,
+                                                      part_cnt);
+    }
+    int32_t rc = launched(TERNARY ? "pack_kernel<ternary>" : "pack_kernel<binary>");
+    if (rc) return rc;
+    if (d_alpha) {
+        alpha_finalize_kernel<<<static_cast<unsigned>((N + 127) / 128), 128, 0, st>>>(part_sum, part_cnt, chunks, N, K,
+                                                                                     d_alpha);
+        rc = launched("alpha_finalize_kernel");
+    }
+    return rc;
+}
+
+}  // namespace
+}  // namespace tbn_cuda
+
+using namespace tbn_cuda;
+
+extern "C" {
+
+int32_t tbn_quantize_to_binary(const float* d_w, int64_t n, float thr, uint8_t* d_out, void* stream) {
+    TBN_REQUIRE(n >= 0, TBN_INVALID_ARGUMENT, "tbn_quantize_to_binary: negative size");
+    if (n == 0) return TBN_SUCCESS;
+    TBN_REQUIRE(d_w && d_out, TBN_INVALID_ARGUMENT, "tbn_quantize_to_binary: null pointer");
+    quantize_binary_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(d_w, n, thr, d_out);
+    return launched("quantize_binary_kernel");
+}
+
+int32_t tbn_quantize_to_ternary(const float* d_w, int64_t n, float lo, float hi, int8_t* d_out, void* stream) {
+    TBN_REQUIRE(n >= 0, TBN_INVALID_ARGUMENT, "tbn_quantize_to_ternary: negative size");
+    if (n == 0) return TBN_SUCCESS;
+    TBN_REQUIRE(d_w && d_out, TBN_INVALID_ARGUMENT, "tbn_quantize_to_ternary: null pointer");
+    quantize_ternary_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(d_w, n, lo, hi, d_out);
+    return launched("quantize_ternary_kernel");
+}
+
+size_t tbn_quant_pack_workspace_bytes(int64_t K, int64_t N, int32_t ternary) {
+    if (K <= 0 || N <= 0) return 0;
+    const int64_t chunks = round_up(K, 128) / kChunkK;
+    return static_cast<size_t>(chunks * N) * sizeof(float) * (ternary ? 2 : 1);
+}
+
+int32_t tbn_quant_pack_binary(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout, float thr,
+                              int32_t ge, uint32_t* d_words, float* d_alpha, void* d_workspace,
+                              size_t workspace_bytes, void* stream) {
+    return quant_pack<false>(d_w, K, N, ldw, layout, thr, 0.0f, ge, d_words, nullptr, d_alpha, d_workspace,
+                             workspace_bytes, as_stream(stream));
+}
+
+int32_t tbn_quant_pack_ternary(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout, float lo,
+                               float hi, uint32_t* d_codes, uint32_t* d_pos, uint32_t* d_neg, float* d_alpha,
+                               void* d_workspace, size_t workspace_bytes, void* stream) {
+    int32_t rc = quant_pack<true>(d_w, K, N, ldw, layout, lo, hi, 0, d_neg, d_pos, d_alpha, d_workspace,
+                                  workspace_bytes, as_stream(stream));
+    if (rc || !d_codes) return rc;
+    const int64_t n_words = (K * N + 15) / 16;
+    ternary_codes_kernel<<<static_cast<unsigned>((n_words + 255) / 256), 256, 0, as_stream(stream)>>>(
+        d_w, K, N, ldw, layout, lo, hi, d_codes, n_words);
+    return launched("ternary_codes_kernel");
+}
+
+}  // extern "C"

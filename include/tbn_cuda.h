@@ -1,0 +1,155 @@
+/* tbn_cuda.h -- C ABI of the B200 (sm_100a) implementation of the fast-arm-tbcnn hot path.
+ *
+ * The reference (Babushkin05/fast-arm-tbcnn) has no FFI for this path: its boundary is the
+ * C++ API in namespace tbn (free operator functions + TBNModel::Session).  This header is the
+ * C boundary placed underneath that API: the C++ host layer of this repository (host/include/tbn)
+ * and any foreign binding (ctypes, pybind11, cgo ...) call exactly these entry points.
+ * Each entry point names the reference function it stands in for (path within the reference
+ * project : line).
+ *
+ * Conventions
+ *   - every pointer named d_* (and workspaces) is DEVICE memory on the current CUDA device;
+ *     sizes are in elements unless the name says bytes; matrices are row-major;
+ *   - GEMM dims follow C[M,N] = A[M,K] * B[K,N];
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); all work is
+ *     asynchronous on that stream unless stated otherwise;
+ *   - the return value is a status: 0 or one of the reference's tbn::ErrorCode values
+ *     (tbn/utils/errors.hpp:10-22) or one of the TBN_CUDA_* extensions below;
+ *     tbn_cuda_last_error() returns the message of the calling thread's last failure;
+ *   - there is no CPU fallback anywhere: without a usable sm_100 device every call fails.
+ */
+#ifndef TBN_CUDA_H
+#define TBN_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---------------------------------------------------------------- */
+#define TBN_SUCCESS 0
+#define TBN_INVALID_ARGUMENT (-1)   /* tbn::ErrorCode::INVALID_ARGUMENT   */
+#define TBN_OUT_OF_MEMORY (-2)      /* tbn::ErrorCode::OUT_OF_MEMORY      */
+#define TBN_NOT_IMPLEMENTED (-3)    /* tbn::ErrorCode::NOT_IMPLEMENTED    */
+#define TBN_RUNTIME_ERROR (-5)      /* tbn::ErrorCode::RUNTIME_ERROR      */
+#define TBN_INVALID_SHAPE (-7)      /* tbn::ErrorCode::INVALID_SHAPE      */
+#define TBN_DEVICE_NOT_SUPPORTED (-8) /* tbn::ErrorCode::DEVICE_NOT_SUPPORTED */
+#define TBN_CUDA_ERROR (-100)       /* a CUDA runtime/driver call failed  */
+#define TBN_CUDA_TIMEOUT (-101)     /* a bounded device-side wait expired */
+
+/* ---- numeric modes of the float x {binary,ternary} GEMM ---------------------------- */
+/* Weights +-1/0 are exact in bf16; the fp32 activations are split into NPASS bf16 terms
+ * (hi [+ mid] [+ lo]) that are multiplied on the tcgen05 tensor cores into one fp32
+ * accumulator.  Relative L2 error against the fp32 reference: X3 ~1e-7 (exact split),
+ * X2 ~2e-6 (default; inside the 1e-5 bar), X1 ~2e-3 (declared bf16-activation variant). */
+#define TBN_MODE_AUTO 0
+#define TBN_MODE_TC_BF16X1 1
+#define TBN_MODE_TC_BF16X2 2
+#define TBN_MODE_TC_BF16X3 3
+#define TBN_MODE_SIMT 4 /* CUDA-core add/subtract-by-sign, fp32, k ascending: bit-equal to
+                           qlinear_matmul_binary_naive */
+
+/* ---- epilogue flags -------------------------------------------------------------- */
+#define TBN_EPI_RELU 1u
+/* (acc*scale + bias[n]) * alpha[n]: the order of Session::execute_conv's cached path
+ * (tbn/runtime/model.hpp:523-557).  Default order is acc*alpha[n]*scale + bias[n]. */
+#define TBN_EPI_BIAS_BEFORE_ALPHA 2u
+
+/* ---- weight layouts accepted by the packers ---------------------------------------- */
+#define TBN_LAYOUT_KN 0 /* W[K,N] row-major (Gemm B, transB = 0)                          */
+#define TBN_LAYOUT_NK 1 /* W[N,K] row-major (conv weights [M_out, C*kh*kw]; Gemm transB=1) */
+
+/* ---- runtime --------------------------------------------------------------------- */
+
+/* Selects `device`, verifies compute capability 10.x and sets up per-device state.
+ * Must be called once per device (per process) before any other entry point. */
+int32_t tbn_cuda_init(int32_t device);
+/* Copies the calling thread's last error message into buf (NUL terminated). Returns its length. */
+int32_t tbn_cuda_last_error(char* buf, size_t buf_bytes);
+/* Replaces tbn::Tensor's host allocation (tbn/runtime/tensor.hpp:23-28): device buffer, zero-filled. */
+int32_t tbn_cuda_malloc(void** d_ptr, size_t bytes);
+int32_t tbn_cuda_free(void* d_ptr);
+int32_t tbn_cuda_memset(void* d_ptr, int32_t value, size_t bytes, void* stream);
+int32_t tbn_cuda_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream);
+int32_t tbn_cuda_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream);
+int32_t tbn_cuda_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream);
+/* Waits for `stream` and reports any device-side error recorded by the kernels
+ * (TBN_CUDA_TIMEOUT when a bounded wait expired). */
+int32_t tbn_cuda_sync(void* stream);
+/* Number of kernels this library has launched so far in this process. */
+int64_t tbn_cuda_launch_count(void);
+
+/* Padded dims of the packed layouts: K_pad = ceil128(K), N_pad = ceil8(N)
+ * (PaddedDimensions, tbn-runtime/src/operators/quantized_gemm_neon.cpp:38-58). */
+int32_t tbn_packed_dims(int64_t K, int64_t N, int64_t* K_pad, int64_t* N_pad);
+
+/* ---- quantise ---------------------------------------------------------------------- */
+
+/* tbn::quantize_to_binary (quantized_gemm_neon.cpp:544-565): out[i] = w[i] > thr ? 1 : 0. */
+int32_t tbn_quantize_to_binary(const float* d_w, int64_t n, float thr, uint8_t* d_out, void* stream);
+/* tbn::quantize_to_ternary (quantized_gemm_neon.cpp:570-597): -1 / 0 / +1 as int8. */
+int32_t tbn_quantize_to_ternary(const float* d_w, int64_t n, float lo, float hi, int8_t* d_out,
+                                void* stream);
+
+/* Bytes of scratch tbn_quant_pack_* needs when d_alpha != NULL (0 otherwise). */
+size_t tbn_quant_pack_workspace_bytes(int64_t K, int64_t N, int32_t ternary);
+
+/* Sign-threshold-and-pack in one pass.  Replaces quantize_to_binary + pad(+1) +
+ * BinaryMatrix::pack (quantized_gemm_neon.cpp:544-565,199-214; GeMM/05-final/GeMM.cpp:114-151;
+ * Session caches tbn/runtime/model.hpp:464-477,819-830).
+ *   d_w     fp32 weights; layout KN: element (k,n) at d_w[k*ldw+n]; layout NK: d_w[n*ldw+k]
+ *   ge      0: +1 iff w > thr (quantize_to_binary); 1: +1 iff w >= thr (Session caches)
+ *   d_words out, uint32 [N_pad][K_pad/32]: word[n*(K_pad/32) + k/32] bit (k%32) set <=> -1;
+ *           padding bits are 0 (+1) -- byte-identical to BinaryMatrix::pack's plane.
+ *   d_alpha out (nullable), fp32 [N]: mean |w| over k (per-output-channel scale,
+ *           model.hpp:388-394; summation is chunked, not bit-equal to the sequential sum). */
+int32_t tbn_quant_pack_binary(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout,
+                              float thr, int32_t ge, uint32_t* d_words, float* d_alpha,
+                              void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Threshold-and-pack for ternary weights.  Replaces quantize_to_ternary
+ * (quantized_gemm_neon.cpp:570-597) + the TernaryPackedWeights::set_weight loop
+ * (tbn/memory/packed_weights.hpp:53-71) and produces the operand planes of the GEMM.
+ *   d_codes out (nullable), uint32 [(K*N+15)/16]: 2-bit code (0=-1, 1=0, 2=+1) of flat element
+ *           i = k*N+n at bits 2*(i%16) of word i/16 -- byte-identical to the reference packer.
+ *   d_pos/d_neg out, uint32 [N_pad][K_pad/32]: planes in the binary layout above
+ *           (bit set in pos <=> +1, in neg <=> -1; padding 0 = weight 0).
+ *   d_alpha out (nullable), fp32 [N]: mean |w| over the non-zero entries of the column. */
+int32_t tbn_quant_pack_ternary(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout,
+                               float lo, float hi, uint32_t* d_codes, uint32_t* d_pos, uint32_t* d_neg,
+                               float* d_alpha, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* ---- GEMM ---------------------------------------------------------------------------- */
+
+/* Bytes of scratch tbn_gemm_fxb / tbn_gemm_tbn need for the split activations. */
+size_t tbn_gemm_workspace_bytes(int64_t M, int64_t K, int32_t mode);
+
+/* Float x binary / float x ternary GEMM:
+ *     C[m,n] = (sum_k A[m,k] * w[k,n]) * alpha[n] * scale + bias[n]      (then optional ReLU)
+ * with w[k,n] = -1 where the neg plane has its bit set, else +1 (binary: d_pos == NULL) or
+ * +1/-1/0 from the pos/neg planes (ternary).  This is the product the reference defines in
+ * qlinear_matmul_binary_naive (quantized_gemm_neon.cpp:63-90) and evaluates through
+ * tbn::gemm on alpha*sign(W) (gemm.cpp:349-360); it replaces the CPU GEMM engine
+ * (GeMM/05-final/GeMM.cpp:303-363) on this path.
+ *   d_a [M,K] fp32, row stride lda;  d_c [M,N] fp32, row stride ldc
+ *   d_alpha, d_bias: nullable fp32 [N];  mode: TBN_MODE_*;  epilogue: TBN_EPI_* flags */
+int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,
+                     const uint32_t* d_pos, int64_t N, const float* d_alpha, float scale,
+                     const float* d_bias, float* d_c, int64_t ldc, int32_t mode, uint32_t epilogue,
+                     void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* "TBN mode": activations ternarised at (lo, hi) x binary weights, exact integer accumulation,
+ * C = float(acc) * scale (then alpha/bias per the epilogue flags).  Bit-equal to
+ * tbn::qlinear_matmul_binary (quantized_gemm_neon.cpp:165-243, 380-430) and to the GEMM inside
+ * Session::execute_conv/execute_gemm with quantisation on (model.hpp:482-503, 835-837). */
+int32_t tbn_gemm_tbn(const float* d_a, int64_t M, int64_t K, int64_t lda, float lo, float hi,
+                     const uint32_t* d_neg, int64_t N, const float* d_alpha, float scale,
+                     const float* d_bias, float* d_c, int64_t ldc, uint32_t epilogue,
+                     void* d_workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TBN_CUDA_H */
