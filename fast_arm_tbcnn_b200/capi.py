@@ -27,6 +27,9 @@ SIGNATURES = {
     "tbn_cuda_d2d": (_i32, [_vp, _vp, _sz, _vp]),
     "tbn_cuda_sync": (_i32, [_vp]),
     "tbn_cuda_launch_count": (_i64, []),
+    "tbn_cuda_profile_enable": (_i32, [_i32]),
+    "tbn_cuda_profile_read": (_i32, [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(_i64)]),
+    "tbn_gather_cols_permute": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tbn_packed_dims": (_i32, [_i64, _i64, C.POINTER(_i64), C.POINTER(_i64)]),
     "tbn_quantize_to_binary": (_i32, [_vp, _i64, _f32, _vp, _vp]),
     "tbn_quantize_to_ternary": (_i32, [_vp, _i64, _f32, _f32, _vp, _vp]),
@@ -111,6 +114,25 @@ class _Lib:
 
     def launch_count(self):
         return int(self.h.tbn_cuda_launch_count())
+
+    def profile_enable(self, on=True):
+        check(self.h.tbn_cuda_profile_enable(int(on)))
+
+    def profile_read(self):
+        """-> dict(gemm_ms, gemm_launches, split_ms, split_launches) since the last read."""
+        g, gn, s, sn = C.c_double(), _i64(), C.c_double(), _i64()
+        check(self.h.tbn_cuda_profile_read(C.byref(g), C.byref(gn), C.byref(s), C.byref(sn)))
+        return {"gemm_ms": g.value, "gemm_launches": gn.value, "split_ms": s.value, "split_launches": sn.value}
+
+    def gather_cols_permute(self, slabs, out=None):
+        """slabs [G, M, Nc] -> out [M, G*Nc]."""
+        import torch
+        self.init()
+        G, M, Nc = slabs.shape
+        if out is None:
+            out = torch.empty((M, G * Nc), dtype=torch.float32, device=slabs.device)
+        check(self.h.tbn_gather_cols_permute(_ptr(slabs), G, M, Nc, _ptr(out), out.stride(0), _stream()))
+        return out
 
     @staticmethod
     def packed_dims(K, N):

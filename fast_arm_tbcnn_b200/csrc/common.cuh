@@ -23,6 +23,12 @@ int32_t launched(const char* kernel_name);
 // error code; 0 = no error.  Valid after tbn_cuda_init on the current device.
 int* device_error_word();
 int sm_count();
+// Benchmark instrumentation (tbn_cuda_profile_enable): records an event on `st` that opens
+// (begin) or closes (end) the timing bracket of one kernel of the given kind.  No-ops while
+// profiling is disabled.
+enum ProfileKind : int { kProfGemm = 0, kProfSplit = 1 };
+void profile_begin(ProfileKind kind, cudaStream_t st);
+void profile_end(ProfileKind kind, cudaStream_t st);
 
 #define TBN_CUDA_TRY(expr)                                         \
     do {                                                           \

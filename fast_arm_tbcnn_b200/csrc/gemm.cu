@@ -16,10 +16,15 @@
 //                               warp 0      TMA producer: activation tiles (128 x 64 bf16, SWIZZLE_128B)
 //                               warp 1      MMA issuer: tcgen05.mma kind::f16 into a double-buffered
 //                                           fp32 accumulator in tensor memory
-//                               warps 2-5   weight transform: packed words -> registers -> +-1/0 bf16
+//                               warps 2-9   weight transform: packed words -> registers -> +-1/0 bf16
 //                                           written straight into the swizzled K-major operand tile
-//                               warps 6-9   epilogue: tcgen05.ld, alpha/scale/bias/ReLU, store
+//                               warps 10-13 epilogue: tcgen05.ld, alpha/scale/bias/ReLU, store
 //                             The weight tile is unpacked once per k-block and reused by all passes.
+//                             The tensor cores add into the fp32 accumulator with truncation, an error
+//                             that grows linearly with the number of accumulation steps; long K is
+//                             therefore cut into segments that each start a fresh accumulator, and the
+//                             epilogue adds the segments in fp32 (round to nearest) through a per-CTA
+//                             scratch tile that stays resident in L2.
 //   gemm_simt_kernel          CUDA-core add/subtract-by-sign, fp32, k ascending (bit-equal to the
 //                             naive reference loop); used for tiny problems and as a cross-check.
 #include <cuda.h>
@@ -126,7 +131,7 @@ constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2;
 constexpr int kProducerWarp = 0, kMmaWarp = 1;
-constexpr int kTransformThreads = 128, kEpilogueThreads = 128;
+constexpr int kTransformThreads = 256, kEpilogueThreads = 128;
 constexpr int kThreads = 64 + kTransformThreads + kEpilogueThreads;
 constexpr int kGroupM = 16;     // rasterisation: 16 m-tiles share a sweep over n for L2 reuse
 constexpr int kAuxBarrierBytes = 1024;
@@ -159,7 +164,13 @@ struct Params {
     Epilogue ep;
     int* err_word;
     int c_vec_ok;          // rows of C are 16-byte aligned
+    int num_seg;           // K segments per tile, each with a fresh accumulator
+    int kb_per_seg;        // k-blocks per segment (the last one may be shorter)
+    float4* scratch;       // [gridDim.x][BN/4][128] partial sums, used when num_seg > 1
 };
+
+// Accumulation steps (k elements x passes) after which a fresh accumulator is started.
+constexpr int kMaxAccumSteps = 4096;
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
     const int group_size = kGroupM * tiles_n;
@@ -250,42 +261,47 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             constexpr uint32_t idesc = ptx::umma_idesc_bf16_f32(BM, BN);
             int stage = 0;
             uint32_t phase = 0;
-            int iter = 0;
+            int iter = 0;  // counts (tile, segment) units; each uses one accumulator buffer
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++iter) {
-                const int buf = iter & 1;
-                const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
-                if (!ptx::mbar_wait(bar_tmem_empty + 8 * buf, acc_parity ^ 1u, p.err_word, kErrWaitTmemEmpty)) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!ptx::mbar_wait(bar_full_a + 8 * stage, phase, p.err_word, kErrWaitFullA) ||
-                        !ptx::mbar_wait(bar_full_b + 8 * stage, phase, p.err_word, kErrWaitFullB)) {
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                for (int seg = 0; seg < p.num_seg && ok; ++seg, ++iter) {
+                    const int buf = iter & 1;
+                    const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
+                    if (!ptx::mbar_wait(bar_tmem_empty + 8 * buf, acc_parity ^ 1u, p.err_word, kErrWaitTmemEmpty)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t b_addr = base + stage * C::STAGE_BYTES;
-                    const uint32_t a_addr = b_addr + C::B_TILE_BYTES;
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+                    const int kb_begin = seg * p.kb_per_seg;
+                    const int kb_end = min(p.num_kb, kb_begin + p.kb_per_seg);
+                    for (int kb = kb_begin; kb < kb_end; ++kb) {
+                        if (!ptx::mbar_wait(bar_full_a + 8 * stage, phase, p.err_word, kErrWaitFullA) ||
+                            !ptx::mbar_wait(bar_full_b + 8 * stage, phase, p.err_word, kErrWaitFullB)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t b_addr = base + stage * C::STAGE_BYTES;
+                        const uint32_t a_addr = b_addr + C::B_TILE_BYTES;
 #pragma unroll
-                    for (int q = 0; q < NPASS; ++q) {
+                        for (int q = 0; q < NPASS; ++q) {
 #pragma unroll
-                        for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
-                            const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr + q * A_TILE_BYTES + k4 * UMMA_K * 2);
-                            const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * UMMA_K * 2);
-                            ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | q | k4) != 0 ? 1u : 0u);
+                            for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+                                const uint64_t a_desc =
+                                    ptx::umma_desc_k_sw128(a_addr + q * A_TILE_BYTES + k4 * UMMA_K * 2);
+                                const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * UMMA_K * 2);
+                                ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || q != 0 || k4 != 0) ? 1u : 0u);
+                            }
+                        }
+                        ptx::umma_commit(bar_empty + 8 * stage);  // smem stage free once these MMAs retire
+                        if (++stage == C::STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
                         }
                     }
-                    ptx::umma_commit(bar_empty + 8 * stage);  // smem stage free once these MMAs retire
-                    if (++stage == C::STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                    if (ok) ptx::umma_commit(bar_tmem_full + 8 * buf);  // this segment's accumulator is complete
                 }
-                if (ok) ptx::umma_commit(bar_tmem_full + 8 * buf);  // accumulator complete
             }
         }
     } else if (warp < 2 + kTransformThreads / 32) {
@@ -363,58 +379,84 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         // ------------------------------------------------------------ epilogue
         const int e = threadIdx.x - (64 + kTransformThreads);
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+        float4* scratch = p.scratch + static_cast<int64_t>(blockIdx.x) * (BN / 4) * kEpilogueThreads + e;
         int iter = 0;
+        int tile_iter = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++iter) {
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-            const int buf = iter & 1;
+            const int sbuf = tile_iter & 1;
             const int64_t n0 = static_cast<int64_t>(tn) * BN;
             for (int j = e; j < BN; j += kEpilogueThreads) {
                 const int64_t n = n0 + j;
-                alpha_s[buf * BN + j] = (p.ep.alpha && n < p.N) ? __ldg(p.ep.alpha + n) : 1.0f;
-                bias_s[buf * BN + j] = (p.ep.bias && n < p.N) ? __ldg(p.ep.bias + n) : 0.0f;
+                alpha_s[sbuf * BN + j] = (p.ep.alpha && n < p.N) ? __ldg(p.ep.alpha + n) : 1.0f;
+                bias_s[sbuf * BN + j] = (p.ep.bias && n < p.N) ? __ldg(p.ep.bias + n) : 0.0f;
             }
             ptx::named_barrier_sync(1, kEpilogueThreads);
-            if (!ptx::mbar_wait(bar_tmem_full + 8 * buf, static_cast<uint32_t>((iter >> 1) & 1), p.err_word,
-                                kErrWaitTmemFull)) {
-                ok = false;
-                break;
-            }
-            ptx::tc_fence_after_sync();
             const int64_t m = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
             float* c_row = p.c + m * p.ldc;
+            for (int seg = 0; seg < p.num_seg && ok; ++seg, ++iter) {
+                const int buf = iter & 1;
+                if (!ptx::mbar_wait(bar_tmem_full + 8 * buf, static_cast<uint32_t>((iter >> 1) & 1), p.err_word,
+                                    kErrWaitTmemFull)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const bool first = seg == 0, last = seg == p.num_seg - 1;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                       static_cast<uint32_t>(buf * BN + c * 32), r);
-                ptx::tmem_ld_wait();
-                const int64_t nc = n0 + c * 32;
-                if (m < p.M) {
-                    const float* as = alpha_s + buf * BN + c * 32;
-                    const float* bs = bias_s + buf * BN + c * 32;
-                    if (p.c_vec_ok && nc + 32 <= p.N) {
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                           static_cast<uint32_t>(buf * BN + c * 32), r);
+                    ptx::tmem_ld_wait();
+                    float v[32];
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o;
-                            o.x = apply_epilogue(__uint_as_float(r[j + 0]), as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags);
-                            o.y = apply_epilogue(__uint_as_float(r[j + 1]), as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags);
-                            o.z = apply_epilogue(__uint_as_float(r[j + 2]), as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags);
-                            o.w = apply_epilogue(__uint_as_float(r[j + 3]), as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags);
-                            *reinterpret_cast<float4*>(c_row + nc + j) = o;
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (!first) {
+                        // Add the earlier segments (fp32, round to nearest).  Slot layout
+                        // [column group][thread] keeps each warp access contiguous.
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 s4 = __ldcg(scratch + (c * 8 + j4) * kEpilogueThreads);
+                            v[4 * j4 + 0] = __fadd_rn(v[4 * j4 + 0], s4.x);
+                            v[4 * j4 + 1] = __fadd_rn(v[4 * j4 + 1], s4.y);
+                            v[4 * j4 + 2] = __fadd_rn(v[4 * j4 + 2], s4.z);
+                            v[4 * j4 + 3] = __fadd_rn(v[4 * j4 + 3], s4.w);
                         }
-                    } else {
+                    }
+                    if (!last) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (nc + j < p.N)
-                                c_row[nc + j] = apply_epilogue(__uint_as_float(r[j]), as[j], bs[j], p.ep.scale, p.ep.flags);
+                        for (int j4 = 0; j4 < 8; ++j4)
+                            __stcg(scratch + (c * 8 + j4) * kEpilogueThreads,
+                                   make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]));
+                    } else if (m < p.M) {
+                        const int64_t nc = n0 + c * 32;
+                        const float* as = alpha_s + sbuf * BN + c * 32;
+                        const float* bs = bias_s + sbuf * BN + c * 32;
+                        if (p.c_vec_ok && nc + 32 <= p.N) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 o;
+                                o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags);
+                                o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags);
+                                o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags);
+                                o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags);
+                                *reinterpret_cast<float4*>(c_row + nc + j) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (nc + j < p.N)
+                                    c_row[nc + j] = apply_epilogue(v[j], as[j], bs[j], p.ep.scale, p.ep.flags);
+                            }
                         }
                     }
                 }
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
             }
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
         }
     }
 
@@ -533,6 +575,9 @@ int pick_bn(int64_t N) {
     return 64;
 }
 
+// Per-CTA partial-sum tiles of the segmented accumulation: one 128 x 256 fp32 tile per SM.
+size_t scratch_bytes() { return static_cast<size_t>(std::max(sm_count(), 1)) * tc::BM * 256 * sizeof(float); }
+
 template <int NPASS, bool TERN_ACT>
 int32_t launch_split(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_t M_pad, int64_t K_pad,
                      __nv_bfloat16* out, float lo, float hi, cudaStream_t st) {
@@ -541,7 +586,9 @@ int32_t launch_split(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     const int grid = static_cast<int>(std::max<int64_t>(1, std::min(want, cap)));
     const int vec_ok = (lda % 4 == 0) && (reinterpret_cast<uintptr_t>(d_a) % 16 == 0);
+    profile_begin(kProfSplit, st);
     split_activations_kernel<NPASS, TERN_ACT><<<grid, 256, 0, st>>>(d_a, M, K, lda, M_pad, K_pad, out, lo, hi, vec_ok);
+    profile_end(kProfSplit, st);
     return launched("split_activations_kernel");
 }
 
@@ -552,7 +599,9 @@ int32_t launch_tc(const CUtensorMap& tmap, const tc::Params& p, cudaStream_t st)
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
+    profile_begin(kProfGemm, st);
     kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(tmap, p);
+    profile_end(kProfGemm, st);
     return launched("gemm_tc_kernel");
 }
 
@@ -570,7 +619,8 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
                          float act_hi, int npass, const uint32_t* d_neg, const uint32_t* d_pos, int64_t N,
                          const Epilogue& ep, float* d_c, int64_t ldc, void* d_ws, size_t ws_bytes, cudaStream_t st) {
     const int64_t M_pad = round_up(M, tc::BM), K_pad = round_up(K, 128), N_pad = round_up(N, 8);
-    const size_t need = static_cast<size_t>(npass) * M_pad * K_pad * sizeof(__nv_bfloat16);
+    const size_t split_bytes = static_cast<size_t>(npass) * M_pad * K_pad * sizeof(__nv_bfloat16);
+    const size_t need = split_bytes + scratch_bytes();
     TBN_REQUIRE(d_ws && ws_bytes >= need, TBN_INVALID_ARGUMENT,
                 "gemm: workspace too small (see tbn_gemm_workspace_bytes)");
     TBN_REQUIRE(reinterpret_cast<uintptr_t>(d_ws) % 128 == 0, TBN_INVALID_ARGUMENT,
@@ -616,6 +666,11 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.ep = ep;
     p.err_word = device_error_word();
     p.c_vec_ok = (ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(d_c) % 16 == 0);
+    // Fresh accumulator every kMaxAccumSteps accumulation steps (see the header comment).
+    const int max_kb = std::max(1, tc::kMaxAccumSteps / (npass * tc::BK));
+    p.num_seg = (p.num_kb + max_kb - 1) / max_kb;
+    p.kb_per_seg = (p.num_kb + p.num_seg - 1) / p.num_seg;
+    p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(d_ws) + split_bytes);
     const bool ternary_w = d_pos != nullptr;
     if (npass == 1) return ternary_w ? dispatch_bn<1, true>(bn, tmap, p, st) : dispatch_bn<1, false>(bn, tmap, p, st);
     if (npass == 2) return ternary_w ? dispatch_bn<2, true>(bn, tmap, p, st) : dispatch_bn<2, false>(bn, tmap, p, st);
@@ -664,7 +719,9 @@ size_t tbn_gemm_workspace_bytes(int64_t M, int64_t K, int32_t mode) {
     int np = npass_of(mode);
     if (mode == TBN_MODE_SIMT) return 0;
     if (np == 0) np = 2;  // AUTO resolves to at most the two-term split
-    return static_cast<size_t>(np) * round_up(M, tc::BM) * round_up(K, 128) * sizeof(__nv_bfloat16);
+    // Split activations + the per-SM partial-sum tiles (sized for the largest SM count in use).
+    return static_cast<size_t>(np) * round_up(M, tc::BM) * round_up(K, 128) * sizeof(__nv_bfloat16) +
+           static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float);
 }
 
 int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,

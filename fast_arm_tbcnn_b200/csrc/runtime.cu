@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -59,6 +60,37 @@ int* device_error_word() {
 int sm_count() {
     DeviceState* s = current_state();
     return s ? s->sms : 0;
+}
+
+namespace {
+std::atomic<bool> g_profile{false};
+struct ProfileSpan {
+    cudaEvent_t start, stop;
+    int kind;
+};
+std::mutex g_prof_mutex;
+std::vector<ProfileSpan> g_spans;
+cudaEvent_t g_open[2] = {nullptr, nullptr};
+}  // namespace
+
+void profile_begin(ProfileKind kind, cudaStream_t st) {
+    if (!g_profile.load(std::memory_order_relaxed)) return;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    cudaEvent_t ev;
+    if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, st);
+    g_open[kind] = ev;
+}
+
+void profile_end(ProfileKind kind, cudaStream_t st) {
+    if (!g_profile.load(std::memory_order_relaxed)) return;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (!g_open[kind]) return;
+    cudaEvent_t ev;
+    if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, st);
+    g_spans.push_back({g_open[kind], ev, static_cast<int>(kind)});
+    g_open[kind] = nullptr;
 }
 
 }  // namespace tbn_cuda
@@ -165,6 +197,39 @@ int32_t tbn_cuda_sync(void* stream) {
 }
 
 int64_t tbn_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int32_t tbn_cuda_profile_enable(int32_t enable) {
+    g_profile.store(enable != 0, std::memory_order_relaxed);
+    return TBN_SUCCESS;
+}
+
+int32_t tbn_cuda_profile_read(double* gemm_ms, int64_t* gemm_launches, double* split_ms, int64_t* split_launches) {
+    double ms[2] = {0.0, 0.0};
+    int64_t n[2] = {0, 0};
+    std::vector<ProfileSpan> spans;
+    {
+        std::lock_guard<std::mutex> lock(g_prof_mutex);
+        spans.swap(g_spans);
+    }
+    int32_t rc = TBN_SUCCESS;
+    for (const ProfileSpan& s : spans) {
+        float t = 0.0f;
+        cudaError_t e = cudaEventSynchronize(s.stop);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, s.start, s.stop);
+        if (e != cudaSuccess) rc = cuda_fail(e, "tbn_cuda_profile_read");
+        else {
+            ms[s.kind] += t;
+            n[s.kind] += 1;
+        }
+        cudaEventDestroy(s.start);
+        cudaEventDestroy(s.stop);
+    }
+    if (gemm_ms) *gemm_ms = ms[kProfGemm];
+    if (gemm_launches) *gemm_launches = n[kProfGemm];
+    if (split_ms) *split_ms = ms[kProfSplit];
+    if (split_launches) *split_launches = n[kProfSplit];
+    return rc;
+}
 
 int32_t tbn_packed_dims(int64_t K, int64_t N, int64_t* K_pad, int64_t* N_pad) {
     TBN_REQUIRE(K >= 0 && N >= 0 && K_pad && N_pad, TBN_INVALID_ARGUMENT, "tbn_packed_dims: bad arguments");

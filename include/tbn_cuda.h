@@ -80,6 +80,13 @@ int32_t tbn_cuda_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream)
 int32_t tbn_cuda_sync(void* stream);
 /* Number of kernels this library has launched so far in this process. */
 int64_t tbn_cuda_launch_count(void);
+/* Per-kernel device timing for benchmarks: while enabled, the GEMM entry points bracket their
+ * two kernels (activation split, tensor-core GEMM) with CUDA events on the launching stream.
+ * tbn_cuda_profile_read waits for the recorded events, returns the accumulated milliseconds and
+ * launch counts since the last read, and clears them.  Off by default (no events recorded). */
+int32_t tbn_cuda_profile_enable(int32_t enable);
+int32_t tbn_cuda_profile_read(double* gemm_ms, int64_t* gemm_launches, double* split_ms,
+                              int64_t* split_launches);
 
 /* Padded dims of the packed layouts: K_pad = ceil128(K), N_pad = ceil8(N)
  * (PaddedDimensions, tbn-runtime/src/operators/quantized_gemm_neon.cpp:38-58). */
@@ -148,6 +155,15 @@ int32_t tbn_gemm_tbn(const float* d_a, int64_t M, int64_t K, int64_t lda, float 
                      const uint32_t* d_neg, int64_t N, const float* d_alpha, float scale,
                      const float* d_bias, float* d_c, int64_t ldc, uint32_t epilogue,
                      void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* ---- multi-GPU helper -------------------------------------------------------------- */
+
+/* Column-sharded GEMM across G GPUs: rank g computes C[:, g*Nc:(g+1)*Nc] as a contiguous
+ * [M, Nc] slab; after one all-gather the slabs sit as d_slabs[G][M][Nc].  This kernel
+ * interleaves them into the row-major d_c[M][G*Nc] (row stride ldc).  (New: the reference is
+ * single-device and has no counterpart.) */
+int32_t tbn_gather_cols_permute(const float* d_slabs, int64_t G, int64_t M, int64_t Nc, float* d_c,
+                                int64_t ldc, void* stream);
 
 #ifdef __cplusplus
 }

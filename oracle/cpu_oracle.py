@@ -345,6 +345,29 @@ class Reference(_Base):
                                                        _p(out, _f32p)), "qlinear_matmul_binary")
         return out
 
+    def pack_binary_weights(self, b_bin):
+        """BINARY bytes [K,N] -> opaque handle of the reference's packed BinaryMatrix."""
+        b = np.ascontiguousarray(b_bin, dtype=np.uint8)
+        self.lib.ref_pack_binary_weights.restype = C.c_void_p
+        h = self.lib.ref_pack_binary_weights(_p(b, _u8p), C.c_uint32(b.shape[0]), C.c_uint32(b.shape[1]))
+        if not h:
+            raise RuntimeError("ref_pack_binary_weights failed: " + self.last_error())
+        return C.c_void_p(h), b.shape[1]
+
+    def free_binary_weights(self, handle):
+        self.lib.ref_free_binary_weights(handle[0])
+
+    def qlinear_matmul_binary_packed(self, a, handle, scale=1.0, tiling=None):
+        a = _f32(a)
+        t = self._tiling(tiling)
+        M, K = a.shape
+        N = handle[1]
+        out = np.empty((M, N), dtype=np.float32)
+        self._check(self.lib.ref_qlinear_matmul_binary_packed(_p(a, _f32p), C.c_int64(M), C.c_int64(K), handle[0],
+                                                              C.c_uint32(N), C.c_float(scale), _p(t, _u32p),
+                                                              _p(out, _f32p)), "qlinear_matmul_binary_packed")
+        return out
+
     def conv2d_f32(self, x, w, bias, p):
         x, w = _f32(x), _f32(w)
         p = _i64arr(p)

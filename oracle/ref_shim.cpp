@@ -181,6 +181,36 @@ int ref_qlinear_matmul_binary(const float* a, int64_t M, int64_t K, const uint8_
     });
 }
 
+// Weights packed once, the way the Session caches them (model.hpp:810-833): BINARY bytes [K,N]
+// -> +-1 int8 padded with +1 to [ceil128(K), ceil8(N)] -> BinaryMatrix::pack.  Returns a handle
+// for ref_qlinear_matmul_binary_packed, or NULL on failure.
+void* ref_pack_binary_weights(const uint8_t* b, uint32_t K, uint32_t N) {
+    tbn::BinaryMatrix* out = nullptr;
+    const int rc = guarded([&] {
+        const uint32_t Kp = (K + 127) / 128 * 128, Np = (N + 7) / 8 * 8;
+        std::vector<int8_t> padded(static_cast<size_t>(Kp) * Np, 1);
+        for (uint32_t i = 0; i < K; ++i)
+            for (uint32_t j = 0; j < N; ++j)
+                padded[static_cast<size_t>(i) * Np + j] = (b[static_cast<size_t>(i) * N + j] == tbn::BINARY_ONE) ? 1 : -1;
+        out = new tbn::BinaryMatrix(tbn::BinaryMatrix::pack({padded.data(), padded.size()}, Kp, Np));
+    });
+    return rc == 0 ? out : nullptr;
+}
+
+void ref_free_binary_weights(void* handle) { delete static_cast<tbn::BinaryMatrix*>(handle); }
+
+// tbn::qlinear_matmul_binary_blocked_packed (quantized_gemm_neon.cpp:249-309): the per-inference
+// part of the reference's "float x binary" path with cached weights.
+int ref_qlinear_matmul_binary_packed(const float* a, int64_t M, int64_t K, const void* handle, uint32_t N,
+                                     float scale, const uint32_t* tiling, float* c_out) {
+    return guarded([&] {
+        tbn::Tensor at = f32_tensor({M, K}, a);
+        tbn::Tensor c = tbn::qlinear_matmul_binary_blocked_packed(
+            at, *static_cast<const tbn::BinaryMatrix*>(handle), N, scale, tiling_from(tiling));
+        std::memcpy(c_out, c.data(), static_cast<size_t>(M) * N * sizeof(float));
+    });
+}
+
 // tbn::qlinear_matmul_binary_naive (quantized_gemm_neon.cpp:63-90): the true float x binary product.
 int ref_fxb_naive(const float* a, int64_t M, int64_t K, const uint8_t* b, int64_t N, float scale,
                   float* c_out) {

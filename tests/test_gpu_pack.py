@@ -6,6 +6,10 @@ from util import pack_plane, special_weights, u32
 
 pytestmark = pytest.mark.gpu
 
+# The reference sums |w| sequentially in fp32 (model.hpp:388-394), which itself carries a rounding
+# error of about sqrt(K) * 2^-24; the kernel sums 128-row chunks, so the two agree to that level.
+ALPHA_RTOL = 1e-5
+
 SHAPES = [(64, 8), (128, 8), (200, 37), (576, 128), (1, 1), (129, 9), (1000, 300), (4608, 512)]
 
 
@@ -35,7 +39,7 @@ def test_binary_pack_kn(tbn, oracle, K, N, ge):
     finite = np.where(np.isfinite(w), w, 0).astype(np.float32)
     ref_alpha = oracle.column_abs_mean(finite)
     cols = np.all(np.isfinite(w), axis=0)
-    np.testing.assert_allclose(alpha.cpu().numpy()[cols], ref_alpha[cols], rtol=2e-6, atol=0)
+    np.testing.assert_allclose(alpha.cpu().numpy()[cols], ref_alpha[cols], rtol=ALPHA_RTOL, atol=0)
 
 
 @pytest.mark.parametrize("K,N", SHAPES)
@@ -49,7 +53,7 @@ def test_binary_pack_nk_conv_layout(tbn, oracle, K, N):
     tbn.lib.sync()
     assert np.array_equal(u32(words), pack_plane((oracle.sign_ge0(w_nk) == -1).T))
     rows = np.all(np.isfinite(w_nk), axis=1)
-    np.testing.assert_allclose(alpha.cpu().numpy()[rows], oracle.channel_abs_mean(w_nk)[rows], rtol=2e-6)
+    np.testing.assert_allclose(alpha.cpu().numpy()[rows], oracle.channel_abs_mean(w_nk)[rows], rtol=ALPHA_RTOL)
 
 
 def test_binary_pack_threshold_and_stride(tbn, oracle):
@@ -93,7 +97,7 @@ def test_ternary_pack(tbn, oracle, K, N, layout):
     assert np.array_equal(u32(neg), pack_plane(t == -1))
     cols = np.all(np.isfinite(w), axis=0)
     ref_alpha = oracle.column_abs_mean_nonzero(np.where(np.isfinite(w), w, 0).astype(np.float32), lo, hi)
-    np.testing.assert_allclose(alpha.cpu().numpy()[cols], ref_alpha[cols], rtol=2e-6)
+    np.testing.assert_allclose(alpha.cpu().numpy()[cols], ref_alpha[cols], rtol=ALPHA_RTOL)
 
 
 def test_quantize_byte_tensors(tbn, oracle):
@@ -108,9 +112,21 @@ def test_quantize_byte_tensors(tbn, oracle):
     assert tbn.lib.quantize_to_binary(torch.empty(0, device="cuda")).numel() == 0
 
 
+def _popcount(words):
+    import torch
+    pop = 0
+    for chunk in words.view(torch.uint8).reshape(-1).split(1 << 26):
+        x = chunk.to(torch.int32)
+        x = x - ((x >> 1) & 0x55)
+        x = (x & 0x33) + ((x >> 2) & 0x33)
+        pop += int(((x + (x >> 4)) & 0x0F).sum())
+    return pop
+
+
 def test_pack_full_size_properties(tbn):
     """16384 x 16384 (the benchmark size): checked through properties that need no CPU pass over
-    the matrix -- packing -W flips every bit of the data region, and popcounts match the sign count."""
+    the matrix -- the number of set bits equals the number of non-positive weights, and packing -W
+    sets exactly the complementary bits (exact zeros are -1 under both signs)."""
     import torch
     g = torch.Generator(device="cuda").manual_seed(1)
     K = N = 16384
@@ -118,14 +134,9 @@ def test_pack_full_size_properties(tbn):
     words, alpha = tbn.lib.quant_pack_binary(w)
     words_neg, _ = tbn.lib.quant_pack_binary(-w, want_alpha=False)
     tbn.lib.sync()
-    assert int((words ^ words_neg).ne(-1).sum()) == 0  # no exact zeros in randn: every bit flips
-    neg_count = int((w <= 0).sum())
-    pop = 0
-    wv = words.view(torch.uint8)
-    for chunk in wv.reshape(-1).split(1 << 26):
-        x = chunk.to(torch.int32)
-        x = x - ((x >> 1) & 0x55)
-        x = (x & 0x33) + ((x >> 2) & 0x33)
-        pop += int(((x + (x >> 4)) & 0x0F).sum())
-    assert pop == neg_count
+    zeros = int((w == 0).sum())
+    assert _popcount(words) == int((w <= 0).sum())
+    assert _popcount(words_neg) == int((w >= 0).sum())
+    assert _popcount(words & words_neg) == zeros
+    assert _popcount(~(words | words_neg)) == 0
     torch.testing.assert_close(alpha, w.abs().mean(dim=0), rtol=1e-5, atol=0)
