@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: float x binary GEMM  C = A (alpha * sign(W)),  M = N = K = 16384.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size n]
+
+One "step" is one GEMM over the whole activation matrix (activation split + tensor-core kernel;
+on N > 1 GPUs additionally the all-gather of the column slabs and the interleave).  The packed
+weights are prepared once before the timed region, as the reference Session caches them.
+Rank 0 prints ONE JSON line.  N > 1 is launched with torchrun (one rank per GPU, NCCL): the
+weight columns are sharded across ranks (strong scaling of the fixed 16384^3 problem).
+
+`--impl reference` times the reference's own CPU code for this path (compiled from its sources as
+oracle/_ref/libtbn_ref.so) on the host cores, on a bounded row sample of the same workload.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "float x binary GEMM throughput (2*M*N*K / time)"
+UNIT = "TFLOP/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def make_inputs(n, rank_cols=None):
+    """A from seed 0, W from seed 1, both N(0,1) fp32 (numpy default_rng), generated on the host."""
+    A = np.random.default_rng(0).standard_normal((n, n), dtype=np.float32)
+    W = np.random.default_rng(1).standard_normal((n, n), dtype=np.float32)
+    if rank_cols is not None:
+        W = np.ascontiguousarray(W[:, rank_cols[0]:rank_cols[1]])
+    return A, W
+
+
+def cpu_reference_arm(n, steps, warmup, threads, rows_per_thread):
+    """Times the reference's CPU path on a row sample: per step, `threads` host threads each run
+    tbn::qlinear_matmul_binary_blocked_packed on `rows_per_thread` rows of A against the full
+    cached packed weight matrix (the reference itself is single-threaded; independent row blocks
+    are the only way to use more cores without touching its code)."""
+    from oracle import cpu_oracle
+    ref = cpu_oracle.Reference()
+    rng = np.random.default_rng(1)
+    W = rng.standard_normal((n, n), dtype=np.float32)
+    qb = ref.quantize_to_binary(W, 0.0)
+    del W
+    handle = ref.pack_binary_weights(qb)
+    del qb
+    rows = threads * rows_per_thread
+    A = np.random.default_rng(0).standard_normal((rows, n), dtype=np.float32)
+    blocks = [A[i * rows_per_thread:(i + 1) * rows_per_thread] for i in range(threads)]
+
+    def one_step():
+        ts = [threading.Thread(target=ref.qlinear_matmul_binary_packed, args=(b, handle, 1.0)) for b in blocks]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = time.perf_counter() - t0
+    # The same sample through the reference's float GEMM (its exact fp32 evaluation of the product).
+    Wd = np.random.default_rng(1).standard_normal((n, n), dtype=np.float32)
+    Wd = np.where(Wd > 0, np.float32(1), np.float32(-1))
+    frows = max(1, min(rows, 8))
+    t1 = time.perf_counter()
+    ref.gemm_f32(A[:frows], Wd)
+    dtf = time.perf_counter() - t1
+    ref.free_binary_weights(handle)
+    return {
+        "tflops": 2.0 * rows * n * n * steps / dt / 1e12,
+        "ms_per_step": dt / steps * 1e3,
+        "rows_per_step": rows,
+        "float_gemm_tflops_1core": 2.0 * frows * n * n / dtf / 1e12,
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cpu_oracle
+    n = args.size
+    if not cpu_oracle.reference_available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libtbn_ref.so is not present"}))
+        return
+    threads = os.cpu_count() or 1
+    # ~1.5 s per step per thread at ~30 GFLOP-equivalent/s per core.
+    rows_per_thread = max(1, int(1.5 * 30e9 / (2.0 * n * n)) // 16 * 16 or 16)
+    rows_per_thread = max(1, min(rows_per_thread, n // threads))
+    r = cpu_reference_arm(n, args.steps, args.warmup, threads, rows_per_thread)
+    sample = (f"per step: {threads} host threads x {rows_per_thread} rows of A (of {n}) against the full {n}x{n} "
+              f"cached packed weights through tbn::qlinear_matmul_binary_blocked_packed "
+              f"(ternarised activations, scalar popcount: the portable branch, host is not ARM)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["tflops"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int1 x int2 popcount (reference TBN mode)",
+        "data": "synthetic N(0,1), numpy default_rng seeds 0/1",
+        "config": {"workload": f"float x binary GEMM {n}^3 (row sample of {r['rows_per_step']} rows per step)"},
+        "cpu_baseline": {"value": r["tflops"], "unit": UNIT, "cores": threads, "kind": "reference", "sample": sample,
+                         "float_gemm_tflops_1core": r["float_gemm_tflops_1core"]},
+        "e2e": {"value": r["tflops"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from fast_arm_tbcnn_b200 import capi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = capi.lib
+    L.init(local)
+    n = args.size
+    mode = {"x1": capi.MODE_TC_BF16X1, "x2": capi.MODE_TC_BF16X2, "x3": capi.MODE_TC_BF16X3}[args.mode]
+    npass = {"x1": 1, "x2": 2, "x3": 3}[args.mode]
+    assert n % world == 0
+    nc = n // world
+    A_h, W_h = make_inputs(n, (rank * nc, (rank + 1) * nc))
+
+    # ---- one-time weight preparation (outside the timed region; timed separately) -------------
+    W_d = torch.from_numpy(W_h).to(dev)
+    L.quant_pack_binary(W_d)
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    words, alpha = L.quant_pack_binary(W_d)
+    ev1.record()
+    torch.cuda.synchronize()
+    pack_ms = ev0.elapsed_time(ev1)
+    pack_bytes = 4.0 * n * nc + n * nc / 8.0 + 4.0 * nc
+    del W_d, W_h
+
+    A_pin = torch.from_numpy(A_h).pin_memory()
+    A_d = A_pin.to(dev, non_blocking=True)
+    C_slab = torch.empty((n, nc), dtype=torch.float32, device=dev)
+    ws, _ = L.gemm_workspace(n, n, mode, dev)
+    gathered = torch.empty((world, n, nc), dtype=torch.float32, device=dev) if world > 1 else None
+    C_full = torch.empty((n, n), dtype=torch.float32, device=dev) if world > 1 else C_slab
+
+    def step():
+        L.gemm_fxb(A_d, words, nc, alpha=alpha, mode=mode, out=C_slab, workspace=ws)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, C_slab)
+            L.gather_cols_permute(gathered, out=C_full)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    L.sync()
+    L.profile_enable(True)
+    L.profile_read()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.launch_count()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = L.launch_count() - launches0
+    prof = L.profile_read()
+    L.profile_enable(False)
+    ms_total = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
+    ms_total = float(ms_total.item())
+    L.sync()
+
+    # ---- end to end through the C ABI with host buffers ---------------------------------------
+    C_pin = torch.empty((n, nc), dtype=torch.float32).pin_memory()
+    e2e_steps = max(1, min(args.steps, 5))
+    h = L.h
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    a_bytes, c_bytes = A_pin.numel() * 4, C_pin.numel() * 4
+
+    def e2e_step():
+        capi.check(h.tbn_cuda_h2d(C.c_void_p(A_d.data_ptr()), C.c_void_p(A_pin.data_ptr()), a_bytes, stream))
+        step()
+        capi.check(h.tbn_cuda_d2h(C.c_void_p(C_pin.data_ptr()), C.c_void_p(C_slab.data_ptr()), c_bytes, stream))
+
+    e2e_step()
+    barrier()
+    ev0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    e2e_ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_ms.item())
+
+    if rank == 0:
+        peaks = load_peaks()
+        flops_step = 2.0 * n * n * n
+        value = flops_step * args.steps / (ms_total * 1e-3) / 1e12
+        e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+        gemm_ms = prof["gemm_ms"] / max(prof["gemm_launches"], 1)
+        kernel_flops = 2.0 * n * nc * n
+        achieved = kernel_flops / (gemm_ms * 1e-3) / 1e12
+        sustained = ms_total >= 500.0
+        pipe_peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+        peak = pipe_peak / npass
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": f"bf16 x{npass} split of fp32 activations, +-1 weights, fp32 accumulate", "data":
+            "synthetic N(0,1), numpy default_rng seeds 0 (A) / 1 (W)",
+            "config": {"workload": f"float x binary GEMM M=N=K={n}, per-column scale mean|W|", "mode": args.mode,
+                       "parallelism": "single GPU" if world == 1 else f"weight columns sharded x{world}, one NCCL all-gather of C",
+                       "l2": "inputs (1 GiB A per step) larger than the 126 MB L2; no flush needed"},
+            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": a_bytes, "d2h_bytes_per_step": c_bytes,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {
+                "bound": "tensor", "kernel": "gemm_tc_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "peak_source": f"{peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} "
+                               f"{pipe_peak} TFLOP/s / {npass} passes",
+                "executed_tflops": achieved * npass, "frac_of_pipe_raw": achieved / pipe_peak,
+                "kernel_ms": gemm_ms, "split_kernel_ms": prof["split_ms"] / max(prof["split_launches"], 1),
+                "hbm_algorithmic_gbs": (4.0 * n * n + n * nc / 8.0 + 4.0 * n * nc) / (gemm_ms * 1e-3) / 1e9,
+            },
+            "weight_pack": {"ms": pack_ms, "algorithmic_gbs": pack_bytes / (pack_ms * 1e-3) / 1e9,
+                            "frac_of_hbm": pack_bytes / (pack_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                            "peak_source": f"{peaks['source']} copy {peaks['hbm_gbs']} GB/s"},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import cpu_oracle
+            if cpu_oracle.reference_available():
+                r = cpu_reference_arm(n, 3, 1, 1, 64)
+                line["cpu_baseline"] = {
+                    "value": r["tflops"], "unit": UNIT, "cores": 1, "kind": "reference",
+                    "sample": f"3 steps of 64 rows of A (of {n}) against the full cached packed weights through the "
+                              "reference's tbn::qlinear_matmul_binary_blocked_packed (single-threaded like the "
+                              "reference; portable scalar-popcount branch; its float tbn::gemm on 8 rows is given beside)",
+                    "float_gemm_tflops_1core": r["float_gemm_tflops_1core"], "host_cores": os.cpu_count()}
+            else:
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference",
+                                        "sample": "oracle/_ref/libtbn_ref.so not present"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=16384)
+    ap.add_argument("--mode", default="x2", choices=["x1", "x2", "x3"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
