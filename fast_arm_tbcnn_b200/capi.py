@@ -35,6 +35,7 @@ SIGNATURES = {
     "tbn_quantize_to_ternary": (_i32, [_vp, _i64, _f32, _f32, _vp, _vp]),
     "tbn_quant_pack_workspace_bytes": (_sz, [_i64, _i64, _i32]),
     "tbn_quant_pack_binary": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _i32, _vp, _vp, _vp, _sz, _vp]),
+    "tbn_quant_pack_binary_noalloc": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _i32, _vp, _vp, _vp]),
     "tbn_quant_pack_ternary": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _f32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "tbn_gemm_workspace_bytes": (_sz, [_i64, _i64, _i32]),
     "tbn_gemm_fxb": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _i32, _u32, _vp, _sz, _vp]),
@@ -169,6 +170,14 @@ class _Lib:
         check(self.h.tbn_quant_pack_binary(_ptr(w), K, N, w.stride(0), layout, thr, int(ge), _ptr(words), _ptr(alpha),
                                            _ptr(ws), ws_bytes, _stream()))
         return words, alpha
+
+    def quant_pack_binary_noalloc(self, w, words, alpha, layout=LAYOUT_KN, thr=0.0, ge=False):
+        """Variant that allocates nothing: the caller passes the outputs (`words` int32
+        [N_pad, K_pad/32], `alpha` float32 [N] or None); the scratch is built into the library."""
+        self.init()
+        K, N = (w.shape if layout == LAYOUT_KN else (w.shape[1], w.shape[0]))
+        check(self.h.tbn_quant_pack_binary_noalloc(_ptr(w), K, N, w.stride(0), layout, thr, int(ge), _ptr(words),
+                                                   _ptr(alpha), _stream()))
 
     def quant_pack_ternary(self, w, lo, hi, layout=LAYOUT_KN, want_alpha=True, want_codes=True):
         """-> (codes [(K*N+15)/16] or None, pos, neg [N_pad, K_pad/32], alpha [N] or None)."""

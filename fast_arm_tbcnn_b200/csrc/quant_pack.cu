@@ -9,6 +9,8 @@
 // Packed layout (all planes): uint32 word[n * (K_pad/32) + k/32], bit (k % 32);
 // K_pad = ceil128(K), N_pad = ceil8(N); padding bits are 0.
 // Comparisons are IEEE (no flush-to-zero on the compare, NaN compares false).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace tbn_cuda {
@@ -226,12 +228,59 @@ int32_t quant_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t 
     return rc;
 }
 
+// ---- scratch of the entry point that allocates nothing --------------------------------
+// Lives in the library image: every GPU that loads the library holds these 4 MiB until the
+// process exits.  Shared by all calls of tbn_quant_pack_binary_noalloc on a device.
+constexpr size_t kNoAllocScratchFloats = size_t(1) << 20;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+// Device address of g_noalloc_scratch on the CURRENT device.  In host code the array's name is
+// only a handle for the runtime; the address a kernel can use has to be asked for, once per
+// device, with that device current.
+int32_t noalloc_scratch_address(float** out) {
+    int dev = -1;
+    TBN_CUDA_TRY(cudaGetDevice(&dev));
+    TBN_REQUIRE(dev >= 0 && dev < kNoAllocMaxDevices, TBN_RUNTIME_ERROR, "device index out of range");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        TBN_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch));
+        TBN_REQUIRE(p != nullptr, TBN_CUDA_ERROR, "cudaGetSymbolAddress returned a null scratch address");
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return TBN_SUCCESS;
+}
+
 }  // namespace
 }  // namespace tbn_cuda
 
 using namespace tbn_cuda;
 
 extern "C" {
+
+int32_t tbn_quant_pack_binary_noalloc(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout, float thr,
+                                      int32_t ge, uint32_t* d_words, float* d_alpha, void* stream) {
+    TBN_REQUIRE(K > 0 && N > 0, TBN_INVALID_SHAPE, "tbn_quant_pack_binary_noalloc: K and N must be positive");
+    const int64_t chunks = round_up(K, 128) / kChunkK;
+    if (static_cast<size_t>(chunks) * static_cast<size_t>(N) > kNoAllocScratchFloats) {
+        return fail(TBN_INVALID_ARGUMENT,
+                    "tbn_quant_pack_binary_noalloc: ceil(K/128)*N = " + std::to_string(chunks * N) +
+                        " exceeds the built-in scratch of " + std::to_string(kNoAllocScratchFloats) +
+                        " partial sums; use tbn_quant_pack_binary with a caller workspace");
+    }
+    float* scratch = nullptr;
+    const int32_t rc = noalloc_scratch_address(&scratch);
+    if (rc) return rc;
+    // Every partial sum that alpha_finalize_kernel reads is written by the pack kernel of this same
+    // call first, so nothing left over from an earlier call is ever read and nothing needs clearing.
+    return quant_pack<false>(d_w, K, N, ldw, layout, thr, 0.0f, ge, d_words, nullptr, d_alpha, scratch,
+                             kNoAllocScratchFloats * sizeof(float), as_stream(stream));
+}
 
 int32_t tbn_quantize_to_binary(const float* d_w, int64_t n, float thr, uint8_t* d_out, void* stream) {
     TBN_REQUIRE(n >= 0, TBN_INVALID_ARGUMENT, "tbn_quantize_to_binary: negative size");

@@ -116,6 +116,28 @@ int32_t tbn_quant_pack_binary(const float* d_w, int64_t K, int64_t N, int64_t ld
                               float thr, int32_t ge, uint32_t* d_words, float* d_alpha,
                               void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* Same result as tbn_quant_pack_binary, for callers that must not allocate device memory and have
+ * no workspace to lend.  (No counterpart in the reference, which only ever uses host memory.)
+ * Who needs it: a host that reserves all of its GPU memory when it starts -- an inference server
+ * whose tensor arena owns HBM, or a plugin running under another framework's caching allocator --
+ * where a cudaMalloc on the request path can fail for lack of free memory and stalls every stream of
+ * the device while it runs.  This call takes the scratch for the per-column scale (one partial sum per
+ * 128 weight rows and column) from a 4 MiB array built into the library instead.
+ *   - limit: ceil(K/128) * N <= 1,048,576 partial sums (e.g. 8192 x 16384); larger shapes are
+ *     refused with TBN_INVALID_ARGUMENT and a message naming the limit;
+ *   - every GPU that loads the library holds the 4 MiB until the process exits;
+ *   - the first call on each device looks up the array's device address (no allocation); make that
+ *     first call before any stream capture begins;
+ *   - all calls on a device share the array, so two calls whose kernels may overlap on the GPU
+ *     (different streams, different host threads) race on it: issue them on one stream or order
+ *     them yourself.  Nothing needs clearing between calls: each call writes every partial sum
+ *     before it reads it;
+ *   - it calls no cudaMalloc / cudaFree or other allocating routine; inputs, d_words and d_alpha are
+ *     the caller's. */
+int32_t tbn_quant_pack_binary_noalloc(const float* d_w, int64_t K, int64_t N, int64_t ldw,
+                                      int32_t layout, float thr, int32_t ge, uint32_t* d_words,
+                                      float* d_alpha, void* stream);
+
 /* Threshold-and-pack for ternary weights.  Replaces quantize_to_ternary
  * (quantized_gemm_neon.cpp:570-597) + the TernaryPackedWeights::set_weight loop
  * (tbn/memory/packed_weights.hpp:53-71) and produces the operand planes of the GEMM.
