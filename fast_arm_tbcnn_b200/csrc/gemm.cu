@@ -16,7 +16,9 @@
 //                               warp 0      TMA producer: activation tiles (128 x 64 bf16, SWIZZLE_128B)
 //                               warp 1      MMA issuer: tcgen05.mma kind::f16 into a double-buffered
 //                                           fp32 accumulator in tensor memory
-//                               warps 2-9   weight transform: packed words -> registers -> +-1/0 bf16
+//                               warp 0 also streams the packed weight words (16 bytes = 128 k per column)
+//                                           into a small shared-memory ring with TMA
+//                               warps 2-9   weight transform: packed words smem -> registers -> +-1/0 bf16
 //                                           written straight into the swizzled K-major operand tile
 //                               warps 10-13 epilogue: tcgen05.ld, alpha/scale/bias/ReLU, store
 //                             The weight tile is unpacked once per k-block and reused by all passes.
@@ -133,15 +135,18 @@ constexpr int A_TILE_BYTES = BM * BK * 2;
 constexpr int kProducerWarp = 0, kMmaWarp = 1;
 constexpr int kTransformThreads = 256, kEpilogueThreads = 128;
 constexpr int kThreads = 64 + kTransformThreads + kEpilogueThreads;
-constexpr int kGroupM = 16;     // rasterisation: 16 m-tiles share a sweep over n for L2 reuse
+constexpr int kGroupM = 8;      // rasterisation: 8 m-tiles share a sweep over n for L2 reuse
+constexpr int kWordStages = 2;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
 constexpr int kAuxBarrierBytes = 1024;
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 
-template <int BN, int NPASS>
+template <int BN, int NPASS, bool TERNARY = false>
 struct Cfg {
     static constexpr int B_TILE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = B_TILE_BYTES + NPASS * A_TILE_BYTES;
-    static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4;  // barriers + alpha/bias staging (x2 buffers)
+    static constexpr int WORD_TILE_BYTES = BN * 16 * (TERNARY ? 2 : 1);  // 4 words per column and plane
+    // barriers + alpha/bias staging (x2 buffers) + packed-word ring
+    static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4 + kWordStages * WORD_TILE_BYTES;
     static constexpr int RAW_STAGES = (kSmemLimit - 1024 - AUX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = RAW_STAGES > 6 ? 6 : RAW_STAGES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;  // + alignment slack
@@ -183,8 +188,11 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 }
 
 template <int BN, int NPASS, bool TERNARY>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const Params p) {
-    using C = Cfg<BN, NPASS>;
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                              const __grid_constant__ CUtensorMap tmap_neg,
+                                                              const __grid_constant__ CUtensorMap tmap_pos,
+                                                              const Params p) {
+    using C = Cfg<BN, NPASS, TERNARY>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -196,11 +204,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     const uint32_t bar_empty = aux + 16 * C::STAGES;
     const uint32_t bar_tmem_full = aux + 24 * C::STAGES;   // 2 x 8 B
     const uint32_t bar_tmem_empty = bar_tmem_full + 16;    // 2 x 8 B
-    const uint32_t tmem_slot = bar_tmem_empty + 16;        // 4 B
+    const uint32_t bar_full_w = bar_tmem_empty + 16;       // kWordStages x 8 B
+    const uint32_t bar_empty_w = bar_full_w + 8 * kWordStages;
+    const uint32_t tmem_slot = bar_empty_w + 8 * kWordStages;  // 4 B
     uint8_t* aux_ptr = base_ptr + C::STAGES * C::STAGE_BYTES;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(aux_ptr + (tmem_slot - aux));
     float* alpha_s = reinterpret_cast<float*>(aux_ptr + kAuxBarrierBytes);  // [2][BN]
     float* bias_s = alpha_s + 2 * BN;                                       // [2][BN]
+    const uint32_t word_ring = aux + kAuxBarrierBytes + 4 * BN * 4;         // [kWordStages][planes][BN][4 words]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -216,8 +227,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             ptx::mbar_init(bar_tmem_full + 8 * b, 1);
             ptx::mbar_init(bar_tmem_empty + 8 * b, kEpilogueThreads);
         }
+        for (int w = 0; w < kWordStages; ++w) {
+            ptx::mbar_init(bar_full_w + 8 * w, 1);
+            ptx::mbar_init(bar_empty_w + 8 * w, kTransformThreads);
+        }
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_neg);
+        if (TERNARY) ptx::prefetch_tensormap(&tmap_pos);
     }
     if (warp == kMmaWarp) {
         ptx::tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -231,13 +248,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, wstage = 0;
+            uint32_t phase = 0, wphase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int tm, tn;
                 tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if ((kb & 1) == 0) {
+                        // Packed words of k-blocks kb and kb+1 for the BN columns of this tile
+                        // (rows past the end of the plane are zero-filled by TMA).
+                        if (!ptx::mbar_wait(bar_empty_w + 8 * wstage, wphase ^ 1u, p.err_word, kErrWaitEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t wbar = bar_full_w + 8 * wstage;
+                        const uint32_t wdst = word_ring + wstage * C::WORD_TILE_BYTES;
+                        ptx::mbar_arrive_expect_tx(wbar, C::WORD_TILE_BYTES);
+                        ptx::tma_load_2d(wdst, &tmap_neg, kb * 2, tn * BN, wbar);
+                        if (TERNARY) ptx::tma_load_2d(wdst + BN * 16, &tmap_pos, kb * 2, tn * BN, wbar);
+                        if (++wstage == kWordStages) {
+                            wstage = 0;
+                            wphase ^= 1u;
+                        }
+                    }
                     if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, p.err_word, kErrWaitEmpty)) {
                         ok = false;
                         break;
@@ -306,69 +340,51 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
     } else if (warp < 2 + kTransformThreads / 32) {
         // ------------------------------------------------------------ weight transform
-        constexpr int RPT = (BN + kTransformThreads - 1) / kTransformThreads;  // rows per thread
-        const int tt = threadIdx.x - 64;
-        int stage = 0;
-        uint32_t phase = 0;
+        static_assert(BN <= kTransformThreads, "one transform thread per weight column of the tile");
+        const int r = threadIdx.x - 64;  // weight column (row of the K-major operand tile) of this thread
+        int stage = 0, wstage = 0;
+        uint32_t phase = 0, wphase = 0;
         bool ok = true;
+        uint4 wn = make_uint4(0u, 0u, 0u, 0u), wp = make_uint4(0u, 0u, 0u, 0u);
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            int tm, tn;
-            tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-            const int64_t n0 = static_cast<int64_t>(tn) * BN;
-            const uint2* neg_src[RPT];
-            const uint2* pos_src[RPT];
-            bool valid[RPT];
-#pragma unroll
-            for (int i = 0; i < RPT; ++i) {
-                const int r = tt + i * kTransformThreads;
-                const int64_t n = n0 + r;
-                valid[i] = r < BN && n < p.N_pad;
-                neg_src[i] = reinterpret_cast<const uint2*>(p.neg + (valid[i] ? n : 0) * p.KW);
-                pos_src[i] = TERNARY ? reinterpret_cast<const uint2*>(p.pos + (valid[i] ? n : 0) * p.KW) : nullptr;
-            }
-            uint2 cur_n[RPT], cur_p[RPT], nxt_n[RPT], nxt_p[RPT];
-#pragma unroll
-            for (int i = 0; i < RPT; ++i) {
-                cur_n[i] = valid[i] ? __ldg(neg_src[i]) : make_uint2(0u, 0u);
-                cur_p[i] = (TERNARY && valid[i]) ? __ldg(pos_src[i]) : make_uint2(0u, 0u);
-            }
             for (int kb = 0; kb < p.num_kb; ++kb) {
-                if (kb + 1 < p.num_kb) {
-#pragma unroll
-                    for (int i = 0; i < RPT; ++i) {
-                        nxt_n[i] = valid[i] ? __ldg(neg_src[i] + kb + 1) : make_uint2(0u, 0u);
-                        nxt_p[i] = (TERNARY && valid[i]) ? __ldg(pos_src[i] + kb + 1) : make_uint2(0u, 0u);
+                if ((kb & 1) == 0) {
+                    // Words of this and the next k-block: shared memory -> registers, then free the slot.
+                    if (!ptx::mbar_wait(bar_full_w + 8 * wstage, wphase, p.err_word, kErrWaitFullB)) {
+                        ok = false;
+                        break;
+                    }
+                    if (r < BN) {
+                        const uint32_t wt = word_ring + wstage * C::WORD_TILE_BYTES + r * 16;
+                        wn = ptx::ld_shared_v4(wt);
+                        if (TERNARY) wp = ptx::ld_shared_v4(wt + BN * 16);
+                    }
+                    // The slot may be refilled by TMA as soon as this arrive lands, so the loads above
+                    // must have returned their data first: the arrive is made to depend on them.
+                    ptx::mbar_arrive_after(bar_empty_w + 8 * wstage, wn.x ^ wn.w ^ wp.x ^ wp.w);
+                    if (++wstage == kWordStages) {
+                        wstage = 0;
+                        wphase ^= 1u;
                     }
                 }
                 if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, p.err_word, kErrWaitEmpty)) {
                     ok = false;
                     break;
                 }
-                uint8_t* b_tile = base_ptr + stage * C::STAGE_BYTES;
+                if (r < BN) {
+                    uint8_t* row = base_ptr + stage * C::STAGE_BYTES + r * 128;
+                    const uint32_t nw[2] = {(kb & 1) ? wn.z : wn.x, (kb & 1) ? wn.w : wn.y};
+                    const uint32_t pw[2] = {(kb & 1) ? wp.z : wp.x, (kb & 1) ? wp.w : wp.y};
 #pragma unroll
-                for (int i = 0; i < RPT; ++i) {
-                    const int r = tt + i * kTransformThreads;
-                    if (r < BN) {
-                        uint8_t* row = b_tile + r * 128;
-                        const uint32_t nw[2] = {cur_n[i].x, cur_n[i].y};
-                        const uint32_t pw[2] = {cur_p[i].x, cur_p[i].y};
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const uint32_t nb = (nw[c >> 2] >> (8 * (c & 3))) & 0xffu;
-                            const uint32_t pb = (pw[c >> 2] >> (8 * (c & 3))) & 0xffu;
-                            // A row of a ternary plane past N_pad / an invalid row is all-zero bits,
-                            // which unpacks to +1 (binary) or 0 (ternary); those columns are never stored.
-                            *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8<TERNARY>(nb, pb);
-                        }
+                    for (int c = 0; c < 8; ++c) {
+                        const uint32_t nb = (nw[c >> 2] >> (8 * (c & 3))) & 0xffu;
+                        const uint32_t pb = (pw[c >> 2] >> (8 * (c & 3))) & 0xffu;
+                        // 16-byte chunk c of row r lands at chunk (c ^ (r & 7)): the 128-byte swizzle.
+                        *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8<TERNARY>(nb, pb);
                     }
                 }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(bar_full_b + 8 * stage);
-#pragma unroll
-                for (int i = 0; i < RPT; ++i) {
-                    cur_n[i] = nxt_n[i];
-                    cur_p[i] = nxt_p[i];
-                }
                 if (++stage == C::STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -592,25 +608,43 @@ int32_t launch_split(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_
     return launched("split_activations_kernel");
 }
 
+struct TensorMaps {
+    CUtensorMap a, neg, pos;
+};
+
+// Packed-word plane [N_pad][KW] uint32 -> box of 4 words (128 k) x BN columns, no swizzle.
+int32_t make_word_map(EncodeTiledFn encode, const uint32_t* words, int64_t KW, int64_t N_pad, int bn, CUtensorMap* out) {
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(KW), static_cast<cuuint64_t>(N_pad)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(KW) * 4};
+    const cuuint32_t box[2] = {4, static_cast<cuuint32_t>(bn)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(words), gdim, gstride, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
+                "cuTensorMapEncodeTiled (packed words) failed with CUresult " + std::to_string(static_cast<int>(cr)));
+    return TBN_SUCCESS;
+}
+
 template <int BN, int NPASS, bool TERNARY>
-int32_t launch_tc(const CUtensorMap& tmap, const tc::Params& p, cudaStream_t st) {
-    using C = tc::Cfg<BN, NPASS>;
+int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
+    using C = tc::Cfg<BN, NPASS, TERNARY>;
     auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY>;
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
     profile_begin(kProfGemm, st);
-    kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(tmap, p);
+    kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, p);
     profile_end(kProfGemm, st);
     return launched("gemm_tc_kernel");
 }
 
 template <int NPASS, bool TERNARY>
-int32_t dispatch_bn(int bn, const CUtensorMap& tmap, const tc::Params& p, cudaStream_t st) {
+int32_t dispatch_bn(int bn, const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
     switch (bn) {
-        case 256: return launch_tc<256, NPASS, TERNARY>(tmap, p, st);
-        case 128: return launch_tc<128, NPASS, TERNARY>(tmap, p, st);
-        default: return launch_tc<64, NPASS, TERNARY>(tmap, p, st);
+        case 256: return launch_tc<256, NPASS, TERNARY>(maps, p, st);
+        case 128: return launch_tc<128, NPASS, TERNARY>(maps, p, st);
+        default: return launch_tc<64, NPASS, TERNARY>(maps, p, st);
     }
 }
 
@@ -638,7 +672,8 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     else rc = launch_split<3, false>(d_a, M, K, lda, M_pad, K_pad, split, 0.f, 0.f, st);
     if (rc) return rc;
 
-    CUtensorMap tmap;
+    TensorMaps maps;
+    CUtensorMap& tmap = maps.a;
     const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(K_pad), static_cast<cuuint64_t>(M_pad),
                                 static_cast<cuuint64_t>(npass)};
     const cuuint64_t gstride[2] = {static_cast<cuuint64_t>(K_pad) * 2, static_cast<cuuint64_t>(M_pad) * K_pad * 2};
@@ -651,6 +686,12 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
                 "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(cr)));
 
     const int bn = pick_bn(N);
+    TBN_REQUIRE(reinterpret_cast<uintptr_t>(d_neg) % 16 == 0 && (!d_pos || reinterpret_cast<uintptr_t>(d_pos) % 16 == 0),
+                TBN_INVALID_ARGUMENT, "gemm: packed weight planes must be 16-byte aligned");
+    rc = make_word_map(encode, d_neg, K_pad / 32, N_pad, bn, &maps.neg);
+    if (rc) return rc;
+    rc = make_word_map(encode, d_pos ? d_pos : d_neg, K_pad / 32, N_pad, bn, &maps.pos);
+    if (rc) return rc;
     tc::Params p;
     p.neg = d_neg;
     p.pos = d_pos;
@@ -672,9 +713,9 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.kb_per_seg = (p.num_kb + p.num_seg - 1) / p.num_seg;
     p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(d_ws) + split_bytes);
     const bool ternary_w = d_pos != nullptr;
-    if (npass == 1) return ternary_w ? dispatch_bn<1, true>(bn, tmap, p, st) : dispatch_bn<1, false>(bn, tmap, p, st);
-    if (npass == 2) return ternary_w ? dispatch_bn<2, true>(bn, tmap, p, st) : dispatch_bn<2, false>(bn, tmap, p, st);
-    return ternary_w ? dispatch_bn<3, true>(bn, tmap, p, st) : dispatch_bn<3, false>(bn, tmap, p, st);
+    if (npass == 1) return ternary_w ? dispatch_bn<1, true>(bn, maps, p, st) : dispatch_bn<1, false>(bn, maps, p, st);
+    if (npass == 2) return ternary_w ? dispatch_bn<2, true>(bn, maps, p, st) : dispatch_bn<2, false>(bn, maps, p, st);
+    return ternary_w ? dispatch_bn<3, true>(bn, maps, p, st) : dispatch_bn<3, false>(bn, maps, p, st);
 }
 
 int32_t gemm_simt(const float* d_a, int64_t M, int64_t K, int64_t lda, bool ternarise_act, float act_lo, float act_hi,

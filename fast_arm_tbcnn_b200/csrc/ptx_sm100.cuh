@@ -30,6 +30,26 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive that cannot issue before `dep` (a value produced by earlier shared-memory loads) is
+// available: the barrier address is computed from it (dep & 0 == 0).  Used when the arrive hands
+// a buffer back to an asynchronous writer and the loads from that buffer must have completed.
+__device__ __forceinline__ void mbar_arrive_after(uint32_t bar, uint32_t dep) {
+    asm volatile(
+        "{\n"
+        ".reg .b32 t;\n"
+        "and.b32 t, %1, 0;\n"
+        "add.u32 t, t, %0;\n"
+        "fence.proxy.async.shared::cta;\n"
+        "mbarrier.arrive.shared::cta.b64 _, [t];\n"
+        "}\n" ::"r"(bar),
+        "r"(dep)
+        : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -81,6 +101,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+// Tiled 2-D load (no multicast).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* m, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
 

@@ -146,6 +146,28 @@ def test_relu_and_strided_output(tbn, oracle):
     assert float(big[:, 90:].min()) == -7.0 and float(big[:, 90:].max()) == -7.0  # nothing written past N
 
 
+@pytest.mark.parametrize("mode", ["x1", "x2"])
+def test_repeated_runs_are_bitwise_identical(tbn, mode):
+    """Several tiles per CTA, launched repeatedly: the kernel has a fixed accumulation order, so any
+    difference between runs is a synchronisation bug (a reused shared-memory slot read too late, a
+    stale accumulator).  The fast one-term mode stresses the packed-word ring hardest."""
+    import torch
+    n = 4096
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = torch.randn((n, n), generator=g, device="cuda")
+    W = torch.randn((n, n), generator=g, device="cuda")
+    words, _ = tbn.lib.quant_pack_binary(W, want_alpha=False)
+    m = {"x1": tbn.MODE_TC_BF16X1, "x2": tbn.MODE_TC_BF16X2}[mode]
+    first = tbn.lib.gemm_fxb(A, words, n, mode=m).clone()
+    for _ in range(10):
+        out = tbn.lib.gemm_fxb(A, words, n, mode=m)
+        tbn.lib.sync()
+        assert torch.equal(out, first)
+    if mode == "x1":
+        exact = A.bfloat16().double() @ torch.where(W > 0, 1.0, -1.0).double()
+        assert float((first.double() - exact).abs().max()) < 1e-2
+
+
 def test_argument_errors(tbn):
     import torch
     a = torch.zeros((4, 8), device="cuda")
