@@ -9,6 +9,7 @@ import os
 
 from . import build as _build
 
+EPI_ADD_RESIDUAL = 4
 MODE_AUTO, MODE_TC_BF16X1, MODE_TC_BF16X2, MODE_TC_BF16X3, MODE_SIMT = 0, 1, 2, 3, 4
 EPI_RELU, EPI_BIAS_BEFORE_ALPHA = 1, 2
 LAYOUT_KN, LAYOUT_NK = 0, 1
@@ -29,10 +30,20 @@ SIGNATURES = {
     "tbn_cuda_launch_count": (_i64, []),
     "tbn_cuda_profile_enable": (_i32, [_i32]),
     "tbn_cuda_profile_read": (_i32, [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(_i64)]),
+    "tbn_conv2d_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "tbn_conv2d_fxb": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
+                              _vp, _f32, _vp, _vp, _vp, _i32, _u32, _vp, _sz, _vp]),
+    "tbn_conv2d_tbn": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
+                              _i32, _vp, _f32, _vp, _vp, _u32, _vp, _sz, _vp]),
+    "tbn_relu": (_i32, [_vp, _i64, _vp, _vp]),
+    "tbn_add": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp, _vp]),
+    "tbn_pool2d": (_i32, [_i32, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "tbn_global_avgpool2d": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "tbn_gather_cols_permute": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tbn_packed_dims": (_i32, [_i64, _i64, C.POINTER(_i64), C.POINTER(_i64)]),
     "tbn_quantize_to_binary": (_i32, [_vp, _i64, _f32, _vp, _vp]),
     "tbn_quantize_to_ternary": (_i32, [_vp, _i64, _f32, _f32, _vp, _vp]),
+    "tbn_channel_abs_mean": (_i32, [_vp, _i64, _i64, _vp, _vp]),
     "tbn_quant_pack_workspace_bytes": (_sz, [_i64, _i64, _i32]),
     "tbn_quant_pack_binary": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _i32, _vp, _vp, _vp, _sz, _vp]),
     "tbn_quant_pack_binary_noalloc": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _i32, _vp, _vp, _vp]),
@@ -156,6 +167,16 @@ class _Lib:
         check(self.h.tbn_quantize_to_ternary(_ptr(w), w.numel(), lo, hi, _ptr(out), _stream()))
         return out
 
+    def channel_abs_mean(self, w):
+        """[channels, ...] -> [channels] mean |w| per channel, sequential fp32 (bit-equal to the reference)."""
+        import torch
+        self.init()
+        w = w.contiguous()
+        ch = w.shape[0]
+        out = torch.empty(ch, dtype=torch.float32, device=w.device)
+        check(self.h.tbn_channel_abs_mean(_ptr(w), ch, w.numel() // ch, _ptr(out), _stream()))
+        return out
+
     def quant_pack_binary(self, w, layout=LAYOUT_KN, thr=0.0, ge=False, want_alpha=True):
         """-> (words int32-viewed-as-uint32 [N_pad, K_pad/32], alpha [N] or None)."""
         import torch
@@ -232,6 +253,103 @@ class _Lib:
             nbytes = workspace.numel() * workspace.element_size()
         check(self.h.tbn_gemm_tbn(_ptr(a), M, K, a.stride(0), lo, hi, _ptr(neg), N, _ptr(alpha), scale, _ptr(bias),
                                   _ptr(out), out.stride(0), epilogue, _ptr(workspace), nbytes, _stream()))
+        return out
+
+
+    # ---- convolution and glue ops -----------------------------------------------------------
+    @staticmethod
+    def conv_out_hw(H, W, kh, kw, p):
+        sh, sw, ph, pw, dh, dw = p
+        if sh <= 0 or sw <= 0:
+            return 0, 0  # the library rejects the call; the output shape does not matter
+        return (H + 2 * ph - dh * (kh - 1) - 1) // sh + 1, (W + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+
+    def conv_workspace(self, C_in, kh, kw, device):
+        import torch
+        nbytes = self.h.tbn_conv2d_workspace_bytes(C_in, kh, kw)
+        return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device), nbytes
+
+    def conv2d_fxb(self, x, neg, wshape, p, pos=None, alpha=None, scale=1.0, bias=None, residual=None, mode=MODE_AUTO,
+                   epilogue=0, out=None, workspace=None):
+        """x [N,C,H,W]; packed weights of shape wshape = (M_out, C, kh, kw); p = (sh, sw, ph, pw, dh, dw)."""
+        import torch
+        self.init()
+        x = x.contiguous()
+        N, Cc, H, W = x.shape
+        M_out, _, kh, kw = wshape
+        oh, ow = self.conv_out_hw(H, W, kh, kw, p)
+        if out is None:
+            out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
+        if workspace is None:
+            workspace, nbytes = self.conv_workspace(Cc, kh, kw, x.device)
+        else:
+            nbytes = workspace.numel()
+        if residual is not None:
+            epilogue |= EPI_ADD_RESIDUAL
+        check(self.h.tbn_conv2d_fxb(_ptr(x), N, Cc, H, W, _ptr(neg), _ptr(pos), M_out, kh, kw, *[int(v) for v in p],
+                                    _ptr(alpha), scale, _ptr(bias), _ptr(residual), _ptr(out), mode, epilogue,
+                                    _ptr(workspace), nbytes, _stream()))
+        return out
+
+    def conv2d_tbn(self, x, neg, wshape, p, lo=-0.1, hi=0.1, alpha=None, scale=1.0, bias=None, epilogue=0, out=None,
+                   workspace=None):
+        import torch
+        self.init()
+        x = x.contiguous()
+        N, Cc, H, W = x.shape
+        M_out, _, kh, kw = wshape
+        oh, ow = self.conv_out_hw(H, W, kh, kw, p)
+        if out is None:
+            out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
+        if workspace is None:
+            workspace, nbytes = self.conv_workspace(Cc, kh, kw, x.device)
+        else:
+            nbytes = workspace.numel()
+        check(self.h.tbn_conv2d_tbn(_ptr(x), N, Cc, H, W, lo, hi, _ptr(neg), M_out, kh, kw, *[int(v) for v in p],
+                                    _ptr(alpha), scale, _ptr(bias), _ptr(out), epilogue, _ptr(workspace), nbytes,
+                                    _stream()))
+        return out
+
+    def relu(self, x):
+        import torch
+        self.init()
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        check(self.h.tbn_relu(_ptr(x), x.numel(), _ptr(out), _stream()))
+        return out
+
+    def add(self, a, b, relu=False):
+        import torch
+        self.init()
+        a, b = a.contiguous(), b.contiguous()
+        out = torch.empty_like(a)
+        inner = a.shape[2] * a.shape[3] if (a.dim() == 4 and a.numel() != b.numel()) else 1
+        check(self.h.tbn_add(_ptr(a), a.numel(), _ptr(b), b.numel(), inner, int(relu), _ptr(out), _stream()))
+        return out
+
+    def pool2d(self, kind, x, p, ceil_mode=False, count_include_pad=False):
+        """kind 0 max / 1 average; p = (kh, kw, sh, sw, ph, pw)."""
+        import torch
+        self.init()
+        x = x.contiguous()
+        N, Cc, H, W = x.shape
+        kh, kw, sh, sw, ph, pw = [int(v) for v in p]
+        if ceil_mode:
+            oh, ow = (H + 2 * ph - kh + sh - 1) // sh + 1, (W + 2 * pw - kw + sw - 1) // sw + 1
+        else:
+            oh, ow = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        out = torch.empty((N, Cc, oh, ow), dtype=torch.float32, device=x.device)
+        check(self.h.tbn_pool2d(kind, _ptr(x), N, Cc, H, W, kh, kw, sh, sw, ph, pw, int(ceil_mode), int(count_include_pad),
+                                _ptr(out), _stream()))
+        return out
+
+    def global_avgpool2d(self, x):
+        import torch
+        self.init()
+        x = x.contiguous()
+        N, Cc, H, W = x.shape
+        out = torch.empty((N, Cc, 1, 1), dtype=torch.float32, device=x.device)
+        check(self.h.tbn_global_avgpool2d(_ptr(x), N, Cc, H, W, _ptr(out), _stream()))
         return out
 
 

@@ -58,8 +58,9 @@ enum DeviceError : int {
 // ---- epilogue ----------------------------------------------------------------------
 
 struct Epilogue {
-    const float* alpha;  // [N] or nullptr
-    const float* bias;   // [N] or nullptr
+    const float* alpha;     // [N] or nullptr
+    const float* bias;      // [N] or nullptr
+    const float* residual;  // same layout as the output, read when TBN_EPI_ADD_RESIDUAL is set
     float scale;
     uint32_t flags;
 };
@@ -67,7 +68,7 @@ struct Epilogue {
 // Separate multiply and add (no FMA contraction) so that the integer-exact paths are
 // bit-equal to the reference's `float(acc) * scale`, `+= bias`, `*= alpha` loops.
 __device__ __forceinline__ float apply_epilogue(float acc, float alpha, float bias, float scale,
-                                                uint32_t flags) {
+                                                uint32_t flags, float residual) {
     float v;
     if (flags & TBN_EPI_BIAS_BEFORE_ALPHA) {
         v = __fmul_rn(acc, scale);
@@ -78,6 +79,7 @@ __device__ __forceinline__ float apply_epilogue(float acc, float alpha, float bi
         v = __fmul_rn(v, scale);
         v = __fadd_rn(v, bias);
     }
+    if (flags & TBN_EPI_ADD_RESIDUAL) v = __fadd_rn(v, residual);
     if (flags & TBN_EPI_RELU) v = fmaxf(v, 0.0f);
     return v;
 }

@@ -1,0 +1,164 @@
+// Conv2D lowered onto the packed-weight GEMM as an IMPLICIT GEMM: the im2col matrix
+// (tbn-runtime/src/operators/conv2d.cpp:420-507) is never written; the operand-build warps of
+// gemm_tc_kernel gather each 128 x 64 activation tile straight from the NCHW fp32 input, split it
+// into bf16 terms (or ternarise it, TBN mode) and write the swizzled shared-memory tile; the epilogue
+// stores NCHW with alpha / bias / residual / ReLU applied.  Replaces, on this path,
+// tbn::conv2d_binary / conv2d_binary_with_scales (conv2d.cpp:220-369) and the cached fast path of
+// Session::execute_conv (tbn/runtime/model.hpp:375-559).  GEMM view: M = N_img*OH*OW output pixels,
+// K = C*kh*kw in the reference's (c, i, j) order, N = output channels; the weights are packed from
+// [M_out, C*kh*kw] with TBN_LAYOUT_NK, which yields the same words as the Session's transpose + pack.
+#include "gemm_tc.cuh"
+
+namespace tbn_cuda {
+namespace {
+
+// table[k] = {input offset of tap k relative to the window origin, (dy << 16) | dx}; see ConvGeom.
+__global__ void conv_tap_table_kernel(int2* __restrict__ table, int K, int K_pad, int H, int W, int kh, int kw, int dh,
+                                      int dw) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= K_pad) return;
+    if (k >= K) {
+        table[k] = make_int2(0, 0x7fff << 16);
+        return;
+    }
+    const int c = k / (kh * kw);
+    const int rem = k - c * kh * kw;
+    const int i = rem / kw, j = rem - i * kw;
+    table[k] = make_int2(c * H * W + i * dh * W + j * dw, ((i * dh) << 16) | ((j * dw) & 0xffff));
+}
+
+struct ConvArgs {
+    const float* x;
+    int64_t N, C, H, W;
+    const uint32_t* neg;
+    const uint32_t* pos;
+    int64_t M_out, kh, kw;
+    int32_t sh, sw, ph, pw, dh, dw;
+    Epilogue ep;
+    float* y;
+    void* ws;
+    size_t ws_bytes;
+    cudaStream_t st;
+};
+
+size_t table_bytes(int64_t K_pad) { return static_cast<size_t>(round_up(K_pad * static_cast<int64_t>(sizeof(int2)), 256)); }
+
+int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float hi) {
+    TBN_REQUIRE(a.N > 0 && a.C > 0 && a.H > 0 && a.W > 0 && a.M_out > 0 && a.kh > 0 && a.kw > 0, TBN_INVALID_SHAPE,
+                "conv2d: dimensions must be positive");
+    TBN_REQUIRE(a.sh > 0 && a.sw > 0 && a.dh > 0 && a.dw > 0 && a.ph >= 0 && a.pw >= 0, TBN_INVALID_ARGUMENT,
+                "conv2d: strides and dilations must be positive, pads non-negative");
+    TBN_REQUIRE(device_error_word() != nullptr, TBN_RUNTIME_ERROR, "tbn_cuda_init was not called on this device");
+    // out = (in + 2p - d(k-1) - 1)/s + 1   (conv2d.cpp:114-117)
+    const int64_t OH = (a.H + 2 * a.ph - a.dh * (a.kh - 1) - 1) / a.sh + 1;
+    const int64_t OW = (a.W + 2 * a.pw - a.dw * (a.kw - 1) - 1) / a.sw + 1;
+    TBN_REQUIRE(a.H + 2 * a.ph - a.dh * (a.kh - 1) - 1 >= 0 && a.W + 2 * a.pw - a.dw * (a.kw - 1) - 1 >= 0 && OH > 0 &&
+                    OW > 0,
+                TBN_INVALID_SHAPE, "conv2d: invalid output dimensions");
+    TBN_REQUIRE(a.x && a.neg && a.y, TBN_INVALID_ARGUMENT, "conv2d: null pointer");
+    TBN_REQUIRE(a.H < 32000 && a.W < 32000 && a.dh * (a.kh - 1) < 32000 && a.dw * (a.kw - 1) < 32000, TBN_INVALID_SHAPE,
+                "conv2d: image or dilated kernel too large");
+    const int64_t K = a.C * a.kh * a.kw, M = a.N * OH * OW, N = a.M_out;
+    TBN_REQUIRE(K < (1LL << 24) && a.C * a.H * a.W < (1LL << 31) && M < (1LL << 31) && OH * OW < (1LL << 31),
+                TBN_INVALID_SHAPE, "conv2d: problem too large");
+    const int64_t K_pad = round_up(K, 128), N_pad = round_up(N, 8), M_pad = round_up(M, tc::BM);
+    const size_t need = table_bytes(K_pad) + scratch_bytes();
+    TBN_REQUIRE(a.ws && a.ws_bytes >= need, TBN_INVALID_ARGUMENT,
+                "conv2d: workspace too small (see tbn_conv2d_workspace_bytes)");
+    TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.ws) % 128 == 0, TBN_INVALID_ARGUMENT,
+                "conv2d: workspace must be 128-byte aligned");
+    TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.neg) % 16 == 0 && (!a.pos || reinterpret_cast<uintptr_t>(a.pos) % 16 == 0),
+                TBN_INVALID_ARGUMENT, "conv2d: packed weight planes must be 16-byte aligned");
+    TBN_REQUIRE(!(a.ep.flags & TBN_EPI_ADD_RESIDUAL) || a.ep.residual, TBN_INVALID_ARGUMENT,
+                "conv2d: TBN_EPI_ADD_RESIDUAL needs a residual tensor");
+    EncodeTiledFn encode = encode_tiled_fn();
+    TBN_REQUIRE(encode != nullptr, TBN_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+
+    int2* table = static_cast<int2*>(a.ws);
+    conv_tap_table_kernel<<<static_cast<unsigned>((K_pad + 127) / 128), 128, 0, a.st>>>(
+        table, static_cast<int>(K), static_cast<int>(K_pad), static_cast<int>(a.H), static_cast<int>(a.W),
+        static_cast<int>(a.kh), static_cast<int>(a.kw), a.dh, a.dw);
+    int32_t rc = launched("conv_tap_table_kernel");
+    if (rc) return rc;
+
+    const int bn = pick_bn(N);
+    TensorMaps maps;
+    rc = make_word_map(encode, a.neg, K_pad / 32, N_pad, bn, &maps.neg);
+    if (rc) return rc;
+    rc = make_word_map(encode, a.pos ? a.pos : a.neg, K_pad / 32, N_pad, bn, &maps.pos);
+    if (rc) return rc;
+    maps.a = maps.neg;  // unused in CONV mode
+
+    tc::Params p = {};
+    p.M = static_cast<int>(M);
+    p.N = static_cast<int>(N);
+    p.num_kb = static_cast<int>(K_pad / tc::BK);
+    p.tiles_m = static_cast<int>(M_pad / tc::BM);
+    p.tiles_n = static_cast<int>((N + bn - 1) / bn);
+    p.c = a.y;
+    p.ldc = N;
+    p.out_nchw = 1;
+    p.out_hw = static_cast<int>(OH * OW);
+    p.ep = a.ep;
+    p.err_word = device_error_word();
+    p.c_vec_ok = 0;
+    set_segments(p, npass);
+    p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.ws) + table_bytes(K_pad));
+    p.conv.x = a.x;
+    p.conv.table = table;
+    p.conv.C = static_cast<int>(a.C);
+    p.conv.H = static_cast<int>(a.H);
+    p.conv.W = static_cast<int>(a.W);
+    p.conv.OH = static_cast<int>(OH);
+    p.conv.OW = static_cast<int>(OW);
+    p.conv.sh = a.sh;
+    p.conv.sw = a.sw;
+    p.conv.ph = a.ph;
+    p.conv.pw = a.pw;
+    p.conv.act_lo = lo;
+    p.conv.act_hi = hi;
+    const bool ternary_w = a.pos != nullptr;
+    if (tern_act) return dispatch_bn<1, false, true, true>(bn, maps, p, a.st);
+    if (npass == 1)
+        return ternary_w ? dispatch_bn<1, true, true, false>(bn, maps, p, a.st)
+                         : dispatch_bn<1, false, true, false>(bn, maps, p, a.st);
+    return ternary_w ? dispatch_bn<2, true, true, false>(bn, maps, p, a.st)
+                     : dispatch_bn<2, false, true, false>(bn, maps, p, a.st);
+}
+
+}  // namespace
+}  // namespace tbn_cuda
+
+using namespace tbn_cuda;
+
+extern "C" {
+
+size_t tbn_conv2d_workspace_bytes(int64_t C, int64_t kh, int64_t kw) {
+    if (C <= 0 || kh <= 0 || kw <= 0) return 0;
+    return table_bytes(round_up(C * kh * kw, 128)) + static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float);
+}
+
+int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, const uint32_t* d_neg,
+                       const uint32_t* d_pos, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph,
+                       int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale, const float* d_bias,
+                       const float* d_residual, float* d_y, int32_t mode, uint32_t epilogue, void* d_workspace,
+                       size_t workspace_bytes, void* stream) {
+    TBN_REQUIRE(mode == TBN_MODE_AUTO || mode == TBN_MODE_TC_BF16X1 || mode == TBN_MODE_TC_BF16X2, TBN_NOT_IMPLEMENTED,
+                "tbn_conv2d_fxb: modes are AUTO (= two bf16 terms), TC_BF16X1 and TC_BF16X2");
+    const ConvArgs a{d_x, N, C, H, W, d_neg, d_pos, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+                     Epilogue{d_alpha, d_bias, d_residual, scale, epilogue}, d_y, d_workspace, workspace_bytes,
+                     as_stream(stream)};
+    return conv_common(a, mode == TBN_MODE_TC_BF16X1 ? 1 : 2, false, 0.f, 0.f);
+}
+
+int32_t tbn_conv2d_tbn(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float lo, float hi,
+                       const uint32_t* d_neg, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph,
+                       int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale, const float* d_bias,
+                       float* d_y, uint32_t epilogue, void* d_workspace, size_t workspace_bytes, void* stream) {
+    const ConvArgs a{d_x, N, C, H, W, d_neg, nullptr, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+                     Epilogue{d_alpha, d_bias, nullptr, scale, epilogue & ~TBN_EPI_ADD_RESIDUAL}, d_y, d_workspace,
+                     workspace_bytes, as_stream(stream)};
+    return conv_common(a, 1, true, lo, hi);
+}
+
+}  // extern "C"

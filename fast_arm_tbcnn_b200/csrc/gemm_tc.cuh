@@ -1,0 +1,617 @@
+// The tcgen05 GEMM kernel shared by the plain GEMM (gemm.cu) and the implicit-GEMM convolution
+// (conv.cu):   D[m, n] = sum_k A[m, k] * w[k, n]   with w in {-1, +1} or {-1, 0, +1} from packed planes.
+//
+// Persistent, one 448-thread CTA per SM, tile 128 x BN x 64, warp specialised:
+//   warp 0      producer: TMA loads of the packed weight words (16 bytes = 128 k per column) into a
+//               small ring and -- GEMM mode -- of the pre-split bf16 activation tiles (SWIZZLE_128B)
+//   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::f16 (M128 x BN x K16) for every activation
+//               term against the same unpacked weight tile, fp32 accumulators double-buffered in
+//               tensor memory
+//   warps 2-9   operand build: packed words smem -> registers -> +-1/0 bf16 written into the swizzled
+//               K-major operand tile; -- CONV mode -- also the activation operand: gather from the
+//               NCHW fp32 input (the im2col matrix is never materialised), split into bf16 terms (or
+//               ternarise), write the swizzled tile
+//   warps 10-13 epilogue: tcgen05.ld, alpha / scale / bias / residual / ReLU, store (row-major or NCHW)
+//
+// The tensor cores add into the fp32 accumulator with truncation, an error that grows linearly with the
+// number of accumulation steps; long K is therefore cut into segments that each start a fresh
+// accumulator, and the epilogue adds the segments in fp32 (round to nearest) through a per-CTA scratch
+// tile that stays resident in L2.
+//
+// Every wait is bounded and reports through the library's device error word.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <climits>
+#include <cstdint>
+#include <string>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace tbn_cuda {
+namespace {
+
+// 8 packed bits -> 8 bf16 (+1 = 0x3F80, -1 = 0xBF80, 0 = 0x0000)
+template <bool TERNARY>
+__device__ __forceinline__ uint4 unpack8(uint32_t neg_byte, uint32_t pos_byte) {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t n0 = (neg_byte >> (2 * j)) & 1u, n1 = (neg_byte >> (2 * j + 1)) & 1u;
+        if (TERNARY) {
+            const uint32_t p0 = (pos_byte >> (2 * j)) & 1u, p1 = (pos_byte >> (2 * j + 1)) & 1u;
+            const uint32_t lo16 = ((n0 | p0) * 0x3F80u) | (n0 << 15);
+            const uint32_t hi16 = ((n1 | p1) * 0x3F80u) | (n1 << 15);
+            o[j] = lo16 | (hi16 << 16);
+        } else {
+            o[j] = 0x3F803F80u | (n0 << 15) | (n1 << 31);
+        }
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// fp32 -> NPASS bf16 terms whose sum approximates (NPASS = 3: equals) the input; or its ternarisation.
+template <int NPASS, bool TERNARISE>
+__device__ __forceinline__ void split_terms(float v, float lo, float hi, uint16_t (&term)[NPASS]) {
+    if (TERNARISE) {
+        // TernaryMatrix::pack_from_float (GeMM/05-final/GeMM.cpp:99-106): strict compares.
+        const float t = v < lo ? -1.0f : (v > hi ? 1.0f : 0.0f);
+        term[0] = __bfloat16_as_ushort(__float2bfloat16_rn(t));
+#pragma unroll
+        for (int q = 1; q < NPASS; ++q) term[q] = 0;
+    } else {
+        float r = v;
+#pragma unroll
+        for (int q = 0; q < NPASS; ++q) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(r);
+            term[q] = __bfloat16_as_ushort(h);
+            // Exact in fp32; a non-finite input leaves its residual terms at zero.
+            r = (q == 0 && !isfinite(r)) ? 0.0f : __fsub_rn(r, __bfloat162float(h));
+        }
+    }
+}
+
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int kProducerWarp = 0, kMmaWarp = 1;
+constexpr int kBuildThreads = 256, kEpilogueThreads = 128;
+constexpr int kThreads = 64 + kBuildThreads + kEpilogueThreads;
+constexpr int kGroupM = 8;      // rasterisation: 8 m-tiles share a sweep over n for L2 reuse
+constexpr int kWordStages = 2;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
+constexpr int kAuxBarrierBytes = 1024;
+constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
+// Accumulation steps (k elements x passes) after which a fresh accumulator is started.
+constexpr int kMaxAccumSteps = 4096;
+
+template <int BN, int NPASS, bool TERNARY>
+struct Cfg {
+    static constexpr int B_TILE_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = B_TILE_BYTES + NPASS * A_TILE_BYTES;
+    static constexpr int WORD_TILE_BYTES = BN * 16 * (TERNARY ? 2 : 1);  // 4 words per column and plane
+    // barriers + alpha/bias staging (x2 buffers) + packed-word ring
+    static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4 + kWordStages * WORD_TILE_BYTES;
+    static constexpr int RAW_STAGES = (kSmemLimit - 1024 - AUX_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES = RAW_STAGES > 6 ? 6 : RAW_STAGES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;  // + alignment slack
+    static constexpr int TMEM_COLS = 2 * BN;
+    static_assert(STAGES >= 2, "need at least a double-buffered pipeline");
+    static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns must be a power of two");
+    static_assert(B_TILE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+};
+
+// Geometry of the implicit im2col (CONV mode).  Row m of the GEMM is output pixel
+// (img, oh, ow) = (m / (OH*OW), ...); column k is (c, i, j) = the reference's im2col order
+// (tbn-runtime/src/operators/conv2d.cpp:484-501).  `table[k]` = {input offset of tap k relative to the
+// pixel's window origin, (dy << 16) | (dx & 0xffff)} with dy = i*dilation_h, dx = j*dilation_w;
+// entries for k >= K carry dy = 0x7fff so that they always fall outside the image.
+struct ConvGeom {
+    const float* x;
+    const int2* table;
+    int C, H, W, OH, OW;
+    int sh, sw, ph, pw;
+    float act_lo, act_hi;  // thresholds when the activations are ternarised (TBN mode)
+};
+
+struct Params {
+    int M, N;
+    int num_kb;            // K_pad / 64
+    int tiles_m, tiles_n;
+    float* c;
+    int64_t ldc;           // row-major output: row stride
+    int out_nchw;          // 1: output element (m, n) lives at ((img*N + n)*OH*OW + pixel)
+    int out_hw;            // OH*OW when out_nchw
+    Epilogue ep;
+    int* err_word;
+    int c_vec_ok;          // row-major output rows are 16-byte aligned
+    int num_seg;           // K segments per tile, each with a fresh accumulator
+    int kb_per_seg;        // k-blocks per segment (the last one may be shorter)
+    float4* scratch;       // [gridDim.x][BN/4][128] partial sums, used when num_seg > 1
+    ConvGeom conv;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int group_size = kGroupM * tiles_n;
+    const int g = t / group_size;
+    const int first_m = g * kGroupM;
+    const int gm = min(tiles_m - first_m, kGroupM);
+    const int r = t - g * group_size;
+    tm = first_m + r % gm;
+    tn = r / gm;
+}
+
+template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                              const __grid_constant__ CUtensorMap tmap_neg,
+                                                              const __grid_constant__ CUtensorMap tmap_pos,
+                                                              const Params p) {
+    using C = Cfg<BN, NPASS, TERNARY>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+
+    const uint32_t aux = base + C::STAGES * C::STAGE_BYTES;
+    const uint32_t bar_full_a = aux;                       // STAGES x 8 B
+    const uint32_t bar_full_b = aux + 8 * C::STAGES;
+    const uint32_t bar_empty = aux + 16 * C::STAGES;
+    const uint32_t bar_tmem_full = aux + 24 * C::STAGES;   // 2 x 8 B
+    const uint32_t bar_tmem_empty = bar_tmem_full + 16;    // 2 x 8 B
+    const uint32_t bar_full_w = bar_tmem_empty + 16;       // kWordStages x 8 B
+    const uint32_t bar_empty_w = bar_full_w + 8 * kWordStages;
+    const uint32_t tmem_slot = bar_empty_w + 8 * kWordStages;  // 4 B
+    uint8_t* aux_ptr = base_ptr + C::STAGES * C::STAGE_BYTES;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(aux_ptr + (tmem_slot - aux));
+    float* alpha_s = reinterpret_cast<float*>(aux_ptr + kAuxBarrierBytes);  // [2][BN]
+    float* bias_s = alpha_s + 2 * BN;                                       // [2][BN]
+    const uint32_t word_ring = aux + kAuxBarrierBytes + 4 * BN * 4;         // [kWordStages][planes][BN][4 words]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            ptx::mbar_init(bar_full_a + 8 * s, 1);
+            ptx::mbar_init(bar_full_b + 8 * s, kBuildThreads);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(bar_tmem_full + 8 * b, 1);
+            ptx::mbar_init(bar_tmem_empty + 8 * b, kEpilogueThreads);
+        }
+        for (int w = 0; w < kWordStages; ++w) {
+            ptx::mbar_init(bar_full_w + 8 * w, 1);
+            ptx::mbar_init(bar_empty_w + 8 * w, kBuildThreads);
+        }
+        ptx::fence_barrier_init();
+        if (!CONV) ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_neg);
+        if (TERNARY) ptx::prefetch_tensormap(&tmap_pos);
+    }
+    if (warp == kMmaWarp) {
+        ptx::tmem_alloc(tmem_slot, C::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0, wstage = 0;
+            uint32_t phase = 0, wphase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if ((kb & 1) == 0) {
+                        // Packed words of k-blocks kb and kb+1 for the BN columns of this tile
+                        // (rows past the end of the plane are zero-filled by TMA).
+                        if (!ptx::mbar_wait(bar_empty_w + 8 * wstage, wphase ^ 1u, p.err_word, kErrWaitEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t wbar = bar_full_w + 8 * wstage;
+                        const uint32_t wdst = word_ring + wstage * C::WORD_TILE_BYTES;
+                        ptx::mbar_arrive_expect_tx(wbar, C::WORD_TILE_BYTES);
+                        ptx::tma_load_2d(wdst, &tmap_neg, kb * 2, tn * BN, wbar);
+                        if (TERNARY) ptx::tma_load_2d(wdst + BN * 16, &tmap_pos, kb * 2, tn * BN, wbar);
+                        if (++wstage == kWordStages) {
+                            wstage = 0;
+                            wphase ^= 1u;
+                        }
+                    }
+                    if (!CONV) {
+                        if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, p.err_word, kErrWaitEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t bar = bar_full_a + 8 * stage;
+                        ptx::mbar_arrive_expect_tx(bar, NPASS * A_TILE_BYTES);
+                        const uint32_t a_dst = base + stage * C::STAGE_BYTES + C::B_TILE_BYTES;
+#pragma unroll
+                        for (int q = 0; q < NPASS; ++q)
+                            ptx::tma_load_3d(a_dst + q * A_TILE_BYTES, &tmap_a, kb * BK, tm * BM, q, bar);
+                        if (++stage == C::STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc_bf16_f32(BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int iter = 0;  // counts (tile, segment) units; each uses one accumulator buffer
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                for (int seg = 0; seg < p.num_seg && ok; ++seg, ++iter) {
+                    const int buf = iter & 1;
+                    const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
+                    if (!ptx::mbar_wait(bar_tmem_empty + 8 * buf, acc_parity ^ 1u, p.err_word, kErrWaitTmemEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+                    const int kb_begin = seg * p.kb_per_seg;
+                    const int kb_end = min(p.num_kb, kb_begin + p.kb_per_seg);
+                    for (int kb = kb_begin; kb < kb_end; ++kb) {
+                        // CONV mode: the build warps write both operands and signal on full_b only.
+                        if ((!CONV && !ptx::mbar_wait(bar_full_a + 8 * stage, phase, p.err_word, kErrWaitFullA)) ||
+                            !ptx::mbar_wait(bar_full_b + 8 * stage, phase, p.err_word, kErrWaitFullB)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t b_addr = base + stage * C::STAGE_BYTES;
+                        const uint32_t a_addr = b_addr + C::B_TILE_BYTES;
+#pragma unroll
+                        for (int q = 0; q < NPASS; ++q) {
+#pragma unroll
+                            for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+                                const uint64_t a_desc =
+                                    ptx::umma_desc_k_sw128(a_addr + q * A_TILE_BYTES + k4 * UMMA_K * 2);
+                                const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * UMMA_K * 2);
+                                ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || q != 0 || k4 != 0) ? 1u : 0u);
+                            }
+                        }
+                        ptx::umma_commit(bar_empty + 8 * stage);  // smem stage free once these MMAs retire
+                        if (++stage == C::STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                    if (ok) ptx::umma_commit(bar_tmem_full + 8 * buf);  // this segment's accumulator is complete
+                }
+            }
+        }
+    } else if (warp < 2 + kBuildThreads / 32) {
+        // ------------------------------------------------------------ operand build
+        static_assert(BN <= kBuildThreads, "one build thread per weight column of the tile");
+        const int r = threadIdx.x - 64;  // weight column (row of the K-major weight tile) of this thread
+        // CONV mode: this thread also builds activation row (r & 127), 16-byte chunks (r >> 7) + {0, 2, 4, 6}.
+        const int a_row = r & (BM - 1);
+        const int a_chunk0 = r >> 7;
+        int stage = 0, wstage = 0;
+        uint32_t phase = 0, wphase = 0;
+        bool ok = true;
+        uint4 wn = make_uint4(0u, 0u, 0u, 0u), wp = make_uint4(0u, 0u, 0u, 0u);
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            int tm, tn;
+            tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+            // Window origin of this thread's output pixel (CONV mode).
+            int ih0 = 0, iw0 = 0;
+            bool row_valid = false;
+            const float* xwin = nullptr;
+            if (CONV) {
+                const int64_t m = static_cast<int64_t>(tm) * BM + a_row;
+                row_valid = m < p.M;
+                const int hw = p.conv.OH * p.conv.OW;
+                const int64_t img = m / hw;
+                const int pix = static_cast<int>(m - img * hw);
+                const int oh = pix / p.conv.OW, ow = pix - oh * p.conv.OW;
+                ih0 = oh * p.conv.sh - p.conv.ph;
+                iw0 = ow * p.conv.sw - p.conv.pw;
+                xwin = p.conv.x + img * p.conv.C * p.conv.H * p.conv.W +
+                       static_cast<int64_t>(ih0) * p.conv.W + iw0;
+            }
+            for (int kb = 0; kb < p.num_kb; ++kb) {
+                if ((kb & 1) == 0) {
+                    // Words of this and the next k-block: shared memory -> registers, then free the slot.
+                    if (!ptx::mbar_wait(bar_full_w + 8 * wstage, wphase, p.err_word, kErrWaitFullB)) {
+                        ok = false;
+                        break;
+                    }
+                    if (r < BN) {
+                        const uint32_t wt = word_ring + wstage * C::WORD_TILE_BYTES + r * 16;
+                        wn = ptx::ld_shared_v4(wt);
+                        if (TERNARY) wp = ptx::ld_shared_v4(wt + BN * 16);
+                    }
+                    // The slot may be refilled by TMA as soon as this arrive lands, so the loads above
+                    // must have returned their data first: the arrive is made to depend on them.
+                    ptx::mbar_arrive_after(bar_empty_w + 8 * wstage, wn.x ^ wn.w ^ wp.x ^ wp.w);
+                    if (++wstage == kWordStages) {
+                        wstage = 0;
+                        wphase ^= 1u;
+                    }
+                }
+                float av[32];
+                if (CONV) {
+                    // Issue this k-block's 32 gathers before waiting for the stage, so that their latency
+                    // overlaps the wait.  Lanes hold consecutive output pixels: coalesced for stride 1.
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int k = kb * BK + (a_chunk0 + 2 * j) * 8 + i;
+                            const int2 e = __ldg(p.conv.table + k);
+                            const int ih = ih0 + (e.y >> 16);
+                            const int iw = iw0 + static_cast<int>(static_cast<short>(e.y & 0xffff));
+                            const bool inside = row_valid && static_cast<unsigned>(ih) < static_cast<unsigned>(p.conv.H) &&
+                                                static_cast<unsigned>(iw) < static_cast<unsigned>(p.conv.W);
+                            av[j * 8 + i] = inside ? __ldg(xwin + e.x) : 0.0f;
+                        }
+                    }
+                }
+                if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, p.err_word, kErrWaitEmpty)) {
+                    ok = false;
+                    break;
+                }
+                uint8_t* stage_ptr = base_ptr + stage * C::STAGE_BYTES;
+                if (r < BN) {
+                    uint8_t* row = stage_ptr + r * 128;
+                    const uint32_t nw[2] = {(kb & 1) ? wn.z : wn.x, (kb & 1) ? wn.w : wn.y};
+                    const uint32_t pw[2] = {(kb & 1) ? wp.z : wp.x, (kb & 1) ? wp.w : wp.y};
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint32_t nb = (nw[c >> 2] >> (8 * (c & 3))) & 0xffu;
+                        const uint32_t pb = (pw[c >> 2] >> (8 * (c & 3))) & 0xffu;
+                        // 16-byte chunk c of row r lands at chunk (c ^ (r & 7)): the 128-byte swizzle.
+                        *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8<TERNARY>(nb, pb);
+                    }
+                }
+                if (CONV) {
+                    uint8_t* a_tile = stage_ptr + C::B_TILE_BYTES + a_row * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t packed[NPASS][4];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            uint16_t term[NPASS];
+                            split_terms<NPASS, TERN_ACT>(av[j * 8 + i], p.conv.act_lo, p.conv.act_hi, term);
+#pragma unroll
+                            for (int q = 0; q < NPASS; ++q) {
+                                if (i & 1) packed[q][i >> 1] |= static_cast<uint32_t>(term[q]) << 16;
+                                else packed[q][i >> 1] = term[q];
+                            }
+                        }
+                        const int c = a_chunk0 + 2 * j;
+#pragma unroll
+                        for (int q = 0; q < NPASS; ++q)
+                            *reinterpret_cast<uint4*>(a_tile + q * A_TILE_BYTES + ((c ^ (a_row & 7)) << 4)) =
+                                make_uint4(packed[q][0], packed[q][1], packed[q][2], packed[q][3]);
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(bar_full_b + 8 * stage);
+                if (++stage == C::STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int e = threadIdx.x - (64 + kBuildThreads);
+        const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+        float4* scratch = p.scratch + static_cast<int64_t>(blockIdx.x) * (BN / 4) * kEpilogueThreads + e;
+        int iter = 0;
+        int tile_iter = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+            int tm, tn;
+            tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+            const int sbuf = tile_iter & 1;
+            const int64_t n0 = static_cast<int64_t>(tn) * BN;
+            for (int j = e; j < BN; j += kEpilogueThreads) {
+                const int64_t n = n0 + j;
+                alpha_s[sbuf * BN + j] = (p.ep.alpha && n < p.N) ? __ldg(p.ep.alpha + n) : 1.0f;
+                bias_s[sbuf * BN + j] = (p.ep.bias && n < p.N) ? __ldg(p.ep.bias + n) : 0.0f;
+            }
+            ptx::named_barrier_sync(1, kEpilogueThreads);
+            const int64_t m = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
+            // Output element (m, n) lives at out_base + n * out_cs.
+            int64_t out_base, out_cs;
+            if (p.out_nchw) {
+                const int64_t img = m / p.out_hw;
+                out_base = img * p.N * p.out_hw + (m - img * p.out_hw);
+                out_cs = p.out_hw;
+            } else {
+                out_base = m * p.ldc;
+                out_cs = 1;
+            }
+            const float* res = p.ep.residual;
+            const bool add_res = (p.ep.flags & TBN_EPI_ADD_RESIDUAL) != 0;
+            for (int seg = 0; seg < p.num_seg && ok; ++seg, ++iter) {
+                const int buf = iter & 1;
+                if (!ptx::mbar_wait(bar_tmem_full + 8 * buf, static_cast<uint32_t>((iter >> 1) & 1), p.err_word,
+                                    kErrWaitTmemFull)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const bool first = seg == 0, last = seg == p.num_seg - 1;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                           static_cast<uint32_t>(buf * BN + c * 32), r);
+                    ptx::tmem_ld_wait();
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (!first) {
+                        // Add the earlier segments (fp32, round to nearest).  Slot layout
+                        // [column group][thread] keeps each warp access contiguous.
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 s4 = __ldcg(scratch + (c * 8 + j4) * kEpilogueThreads);
+                            v[4 * j4 + 0] = __fadd_rn(v[4 * j4 + 0], s4.x);
+                            v[4 * j4 + 1] = __fadd_rn(v[4 * j4 + 1], s4.y);
+                            v[4 * j4 + 2] = __fadd_rn(v[4 * j4 + 2], s4.z);
+                            v[4 * j4 + 3] = __fadd_rn(v[4 * j4 + 3], s4.w);
+                        }
+                    }
+                    if (!last) {
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4)
+                            __stcg(scratch + (c * 8 + j4) * kEpilogueThreads,
+                                   make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]));
+                    } else if (m < p.M) {
+                        const int64_t nc = n0 + c * 32;
+                        const float* as = alpha_s + sbuf * BN + c * 32;
+                        const float* bs = bias_s + sbuf * BN + c * 32;
+                        if (p.c_vec_ok && !add_res && nc + 32 <= p.N) {
+                            float* c_row = p.c + out_base;
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 o;
+                                o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags, 0.0f);
+                                o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags, 0.0f);
+                                o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags, 0.0f);
+                                o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags, 0.0f);
+                                *reinterpret_cast<float4*>(c_row + nc + j) = o;
+                            }
+                        } else {
+                            // Ragged edge, residual add or NCHW: element stores.  In NCHW consecutive lanes
+                            // hold consecutive pixels of one channel, so each store is coalesced.
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (nc + j < p.N) {
+                                    const int64_t idx = out_base + (nc + j) * out_cs;
+                                    const float rv = add_res ? __ldg(res + idx) : 0.0f;
+                                    p.c[idx] = apply_epilogue(v[j], as[j], bs[j], p.ep.scale, p.ep.flags, rv);
+                                }
+                            }
+                        }
+                    }
+                }
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
+            }
+        }
+    }
+
+    // ------------------------------------------------------------ teardown
+    __syncwarp();
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+}  // namespace tc
+
+// =====================================================================================
+// Host-side helpers shared by the GEMM and convolution entry points
+// =====================================================================================
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            sym = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+inline int pick_bn(int64_t N) {
+    // Largest tile whose padding waste stays within ~12 % of the best candidate.
+    const int cand[3] = {256, 128, 64};
+    int64_t best = INT64_MAX;
+    for (int bn : cand) best = std::min<int64_t>(best, round_up(N, bn));
+    for (int bn : cand)
+        if (round_up(N, bn) * 8 <= best * 9) return bn;
+    return 64;
+}
+
+// Per-CTA partial-sum tiles of the segmented accumulation: one 128 x 256 fp32 tile per SM.
+inline size_t scratch_bytes() { return static_cast<size_t>(std::max(sm_count(), 1)) * tc::BM * 256 * sizeof(float); }
+
+struct TensorMaps {
+    CUtensorMap a, neg, pos;
+};
+
+// Packed-word plane [N_pad][KW] uint32 -> box of 4 words (128 k) x BN columns, no swizzle.
+inline int32_t make_word_map(EncodeTiledFn encode, const uint32_t* words, int64_t KW, int64_t N_pad, int bn,
+                             CUtensorMap* out) {
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(KW), static_cast<cuuint64_t>(N_pad)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(KW) * 4};
+    const cuuint32_t box[2] = {4, static_cast<cuuint32_t>(bn)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(words), gdim, gstride, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
+                "cuTensorMapEncodeTiled (packed words) failed with CUresult " + std::to_string(static_cast<int>(cr)));
+    return TBN_SUCCESS;
+}
+
+// Fills the segmentation fields: a fresh accumulator every kMaxAccumSteps accumulation steps.
+inline void set_segments(tc::Params& p, int npass) {
+    const int max_kb = std::max(1, tc::kMaxAccumSteps / (npass * tc::BK));
+    p.num_seg = (p.num_kb + max_kb - 1) / max_kb;
+    p.kb_per_seg = (p.num_kb + p.num_seg - 1) / p.num_seg;
+}
+
+template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT>
+int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
+    using C = tc::Cfg<BN, NPASS, TERNARY>;
+    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, CONV, TERN_ACT>;
+    TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    const int total = p.tiles_m * p.tiles_n;
+    const int grid = std::max(1, std::min(total, sm_count()));
+    profile_begin(kProfGemm, st);
+    kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, p);
+    profile_end(kProfGemm, st);
+    return launched(CONV ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
+}
+
+template <int NPASS, bool TERNARY, bool CONV, bool TERN_ACT>
+int32_t dispatch_bn(int bn, const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
+    switch (bn) {
+        case 256: return launch_tc<256, NPASS, TERNARY, CONV, TERN_ACT>(maps, p, st);
+        case 128: return launch_tc<128, NPASS, TERNARY, CONV, TERN_ACT>(maps, p, st);
+        default: return launch_tc<64, NPASS, TERNARY, CONV, TERN_ACT>(maps, p, st);
+    }
+}
+
+}  // namespace
+}  // namespace tbn_cuda

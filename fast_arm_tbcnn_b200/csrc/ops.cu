@@ -1,0 +1,125 @@
+// Glue operators of the CNN graphs, device resident (all HBM-bound, one pass over the data):
+// ReLU, Add (the broadcast forms the reference Session accepts), MaxPool / AveragePool,
+// GlobalAveragePool.  Stand in for Session::execute_relu / execute_add (tbn/runtime/model.hpp:905-1174)
+// and tbn-runtime/src/operators/pooling.cpp:10-216.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace tbn_cuda {
+namespace {
+
+__global__ void relu_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        y[i] = fmaxf(x[i], 0.0f);  // std::max(0.0f, x): NaN -> 0 as in the reference
+}
+
+// out[i] = a[i] + b[(i / inner) % b_n]; b_n == a_n (inner 1) is the same-shape add.
+__global__ void add_kernel(const float* __restrict__ a, int64_t a_n, const float* __restrict__ b, int64_t b_n,
+                           int64_t inner, float* __restrict__ y, int relu) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < a_n; i += stride) {
+        const float v = __fadd_rn(a[i], b[(i / inner) % b_n]);
+        y[i] = relu ? fmaxf(v, 0.0f) : v;
+    }
+}
+
+// kind 0: max over the in-range taps (-inf if none); kind 1: average (pooling.cpp:50-76, 116-143).
+__global__ void pool2d_kernel(int kind, const float* __restrict__ x, int64_t NC, int H, int W, int OH, int OW, int kh,
+                              int kw, int sh, int sw, int ph, int pw, int count_include_pad, float* __restrict__ y) {
+    const int64_t total = NC * OH * OW;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int ow = static_cast<int>(idx % OW);
+        const int oh = static_cast<int>((idx / OW) % OH);
+        const int64_t nc = idx / (static_cast<int64_t>(OW) * OH);
+        const float* plane = x + nc * H * W;
+        float best = -INFINITY, sum = 0.0f;
+        int count = 0;
+        for (int i = 0; i < kh; ++i) {
+            const int ih = oh * sh - ph + i;
+            for (int j = 0; j < kw; ++j) {
+                const int iw = ow * sw - pw + j;
+                if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                    const float v = plane[ih * W + iw];
+                    best = best > v ? best : v;
+                    sum = __fadd_rn(sum, v);
+                    ++count;
+                } else if (count_include_pad) {
+                    ++count;
+                }
+            }
+        }
+        y[idx] = kind == 0 ? best : (count > 0 ? __fdiv_rn(sum, static_cast<float>(count)) : 0.0f);
+    }
+}
+
+// One warp per (n, c) plane.
+__global__ void global_avgpool_kernel(const float* __restrict__ x, int64_t NC, int64_t HW, float* __restrict__ y) {
+    const int64_t plane = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (plane >= NC) return;
+    const int lane = threadIdx.x & 31;
+    float sum = 0.0f;
+    for (int64_t i = lane; i < HW; i += 32) sum += x[plane * HW + i];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
+    if (lane == 0) y[plane] = __fdiv_rn(sum, static_cast<float>(HW));
+}
+
+int grid_for(int64_t n) {
+    const int64_t cap = static_cast<int64_t>(sm_count() > 0 ? sm_count() : 148) * 16;
+    return static_cast<int>(std::max<int64_t>(1, std::min((n + 255) / 256, cap)));
+}
+
+}  // namespace
+}  // namespace tbn_cuda
+
+using namespace tbn_cuda;
+
+extern "C" {
+
+int32_t tbn_relu(const float* d_x, int64_t n, float* d_y, void* stream) {
+    TBN_REQUIRE(n >= 0, TBN_INVALID_ARGUMENT, "tbn_relu: negative size");
+    if (n == 0) return TBN_SUCCESS;
+    TBN_REQUIRE(d_x && d_y, TBN_INVALID_ARGUMENT, "tbn_relu: null pointer");
+    relu_kernel<<<grid_for(n), 256, 0, as_stream(stream)>>>(d_x, n, d_y);
+    return launched("relu_kernel");
+}
+
+int32_t tbn_add(const float* d_a, int64_t a_n, const float* d_b, int64_t b_n, int64_t inner, int32_t relu, float* d_y,
+                void* stream) {
+    TBN_REQUIRE(a_n >= 0 && b_n > 0 && inner > 0, TBN_INVALID_ARGUMENT, "tbn_add: bad sizes");
+    if (a_n == 0) return TBN_SUCCESS;
+    TBN_REQUIRE(d_a && d_b && d_y, TBN_INVALID_ARGUMENT, "tbn_add: null pointer");
+    TBN_REQUIRE(a_n == b_n || a_n % (b_n * inner) == 0, TBN_INVALID_SHAPE, "tbn_add: shapes do not broadcast");
+    add_kernel<<<grid_for(a_n), 256, 0, as_stream(stream)>>>(d_a, a_n, d_b, b_n, a_n == b_n ? 1 : inner, d_y, relu);
+    return launched("add_kernel");
+}
+
+int32_t tbn_pool2d(int32_t kind, const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, int32_t kh, int32_t kw,
+                   int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t ceil_mode, int32_t count_include_pad,
+                   float* d_y, void* stream) {
+    TBN_REQUIRE(kind == 0 || kind == 1, TBN_INVALID_ARGUMENT, "tbn_pool2d: kind must be 0 (max) or 1 (average)");
+    TBN_REQUIRE(N > 0 && C > 0 && H > 0 && W > 0 && kh > 0 && kw > 0 && sh > 0 && sw > 0 && ph >= 0 && pw >= 0,
+                TBN_INVALID_SHAPE, "tbn_pool2d: bad dimensions");
+    TBN_REQUIRE(d_x && d_y, TBN_INVALID_ARGUMENT, "tbn_pool2d: null pointer");
+    // pooling.cpp:28-34
+    const int64_t OH = ceil_mode ? (H + 2 * ph - kh + sh - 1) / sh + 1 : (H + 2 * ph - kh) / sh + 1;
+    const int64_t OW = ceil_mode ? (W + 2 * pw - kw + sw - 1) / sw + 1 : (W + 2 * pw - kw) / sw + 1;
+    TBN_REQUIRE(OH > 0 && OW > 0 && H < (1 << 30) && W < (1 << 30), TBN_INVALID_SHAPE, "tbn_pool2d: empty output");
+    pool2d_kernel<<<grid_for(N * C * OH * OW), 256, 0, as_stream(stream)>>>(
+        kind, d_x, N * C, static_cast<int>(H), static_cast<int>(W), static_cast<int>(OH), static_cast<int>(OW), kh, kw,
+        sh, sw, ph, pw, count_include_pad, d_y);
+    return launched("pool2d_kernel");
+}
+
+int32_t tbn_global_avgpool2d(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float* d_y, void* stream) {
+    TBN_REQUIRE(N > 0 && C > 0 && H > 0 && W > 0, TBN_INVALID_SHAPE, "tbn_global_avgpool2d: bad dimensions");
+    TBN_REQUIRE(d_x && d_y, TBN_INVALID_ARGUMENT, "tbn_global_avgpool2d: null pointer");
+    const int64_t planes = N * C;
+    global_avgpool_kernel<<<static_cast<unsigned>((planes + 7) / 8), 256, 0, as_stream(stream)>>>(d_x, planes, H * W, d_y);
+    return launched("global_avgpool_kernel");
+}
+
+}  // extern "C"

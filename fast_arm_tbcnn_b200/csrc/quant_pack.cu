@@ -168,6 +168,18 @@ __global__ void ternary_codes_kernel(const float* __restrict__ w, int64_t K, int
     codes[j] = word;
 }
 
+// alpha[c] = (sum_i |w[c*per + i]|) / per, fp32, summed in memory order by one thread per channel:
+// bit-equal to the loop of Session::execute_conv (model.hpp:388-394).
+__global__ void channel_abs_mean_seq_kernel(const float* __restrict__ w, int64_t channels, int64_t per,
+                                            float* __restrict__ alpha) {
+    const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const float* row = w + c * per;
+    float sum = 0.0f;
+    for (int64_t i = 0; i < per; ++i) sum = __fadd_rn(sum, fabsf(row[i]));
+    alpha[c] = __fdiv_rn(sum, static_cast<float>(per));
+}
+
 __global__ void quantize_binary_kernel(const float* __restrict__ w, int64_t n, float thr, uint8_t* __restrict__ out) {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
@@ -280,6 +292,14 @@ int32_t tbn_quant_pack_binary_noalloc(const float* d_w, int64_t K, int64_t N, in
     // call first, so nothing left over from an earlier call is ever read and nothing needs clearing.
     return quant_pack<false>(d_w, K, N, ldw, layout, thr, 0.0f, ge, d_words, nullptr, d_alpha, scratch,
                              kNoAllocScratchFloats * sizeof(float), as_stream(stream));
+}
+
+int32_t tbn_channel_abs_mean(const float* d_w, int64_t channels, int64_t per, float* d_alpha, void* stream) {
+    TBN_REQUIRE(channels > 0 && per > 0, TBN_INVALID_SHAPE, "tbn_channel_abs_mean: sizes must be positive");
+    TBN_REQUIRE(d_w && d_alpha, TBN_INVALID_ARGUMENT, "tbn_channel_abs_mean: null pointer");
+    channel_abs_mean_seq_kernel<<<static_cast<unsigned>((channels + 63) / 64), 64, 0, as_stream(stream)>>>(d_w, channels, per,
+                                                                                                    d_alpha);
+    return launched("channel_abs_mean_seq_kernel");
 }
 
 int32_t tbn_quantize_to_binary(const float* d_w, int64_t n, float thr, uint8_t* d_out, void* stream) {

@@ -1,0 +1,189 @@
+"""Device-resident graph executor mirroring the reference's ``TBNModel::Session``
+(tbn-runtime/include/tbn/runtime/model.hpp:119-1316) for the operators of the CNN configurations.
+
+A graph is a plain dict with the fields of the reference's ``ModelGraph`` (model.hpp:29-35):
+
+    {"inputs": {name: shape}, "outputs": {name: shape}, "inits": {name: ndarray},
+     "binary": {names of weight tensors to binarise}, "nodes": [{"op", "name", "inputs", "outputs", "attrs"}]}
+
+Same surface as the reference: ``set_quantization(bool)``, ``set_input(name, array)``, ``run()``,
+``get_output(name)``; ``set_input`` checks the shape against the graph (InvalidShapeError there, ValueError
+here).  All tensors live in HBM; weights are sign-packed once at construction (the reference caches them on
+the first run, model.hpp:127-157).  Every operator runs in the CUDA library through its C ABI.
+
+Two numeric modes, selected like the reference's quantisation switch:
+  * quantisation off (default) -- "float x binary": y = x * (alpha * sign(w)) in fp32 accuracy, which is what
+    the reference computes with quantisation off on the dequantised weights alpha*sign(w);
+  * quantisation on -- "TBN mode": activations ternarised at +-0.1, exact integer accumulation,
+    (acc + bias) * alpha for Conv and acc + bias for Gemm, bit-equal to the reference Session with
+    quantisation on when it is given the dequantised weights.
+"""
+import numpy as np
+
+from . import capi
+
+
+class Session:
+    def __init__(self, graph, device=None, fuse=True):
+        import torch
+        self.torch = torch
+        self.graph = graph
+        self.L = capi.lib
+        self.device = torch.device("cuda", self.L.init(device))
+        self.quantization = False
+        self.fuse = fuse
+        self.inputs = {}
+        self.values = {}
+        self.weights = {}
+        for name, arr in graph["inits"].items():
+            t = torch.from_numpy(np.ascontiguousarray(arr, dtype=np.float32)).to(self.device)
+            if name in graph["binary"]:
+                self.weights[name] = self._pack(t)
+            else:
+                self.weights[name] = {"dense": t}
+        self._ws = {}
+
+    # -- weight preparation ----------------------------------------------------------------
+    def _pack(self, w):
+        L = self.L
+        if w.dim() == 4:  # conv [M, C, kh, kw] -> K = C*kh*kw along the row: layout NK
+            flat = w.reshape(w.shape[0], -1)
+            words_gt, alpha = L.quant_pack_binary(flat, capi.LAYOUT_NK, 0.0, False)
+            # TBN mode reproduces the Session on dequantised weights: sign by >= 0 and the scale summed
+            # sequentially over alpha*sign(w) (model.hpp:388-394, 433).
+            deq = self.torch.where(flat > 0, 1.0, -1.0) * alpha[:, None]
+            alpha_seq = L.channel_abs_mean(deq.contiguous())
+            return {"shape": tuple(w.shape), "words": words_gt, "alpha": alpha, "alpha_tbn": alpha_seq}
+        words_gt, alpha = L.quant_pack_binary(w, capi.LAYOUT_KN, 0.0, False)  # Gemm B [K, N]
+        return {"shape": tuple(w.shape), "words": words_gt, "alpha": alpha}
+
+    # -- reference surface -------------------------------------------------------------------
+    def set_quantization(self, enable):
+        self.quantization = bool(enable)
+
+    def is_quantization_enabled(self):
+        return self.quantization
+
+    def set_input(self, name, array):
+        if name not in self.graph["inputs"]:
+            raise KeyError(f"Input '{name}' not found in model")
+        t = array if self.torch.is_tensor(array) else self.torch.from_numpy(np.ascontiguousarray(array, dtype=np.float32))
+        if tuple(t.shape) != tuple(self.graph["inputs"][name]):
+            raise ValueError(f"Input shape mismatch for '{name}'")
+        self.inputs[name] = t.to(self.device, non_blocking=True)
+
+    def get_output(self, name):
+        if name not in self.values or name not in self.graph["outputs"]:
+            raise KeyError(f"Output '{name}' not available")
+        return self.values[name]
+
+    def _workspace(self, key, nbytes):
+        ws = self._ws.get(key)
+        if ws is None or ws.numel() < nbytes:
+            ws = self.torch.empty(max(nbytes, 256), dtype=self.torch.uint8, device=self.device)
+            self._ws[key] = ws
+        return ws
+
+    # -- execution ---------------------------------------------------------------------------
+    def run(self):
+        if len(self.inputs) != len(self.graph["inputs"]):
+            raise ValueError("Not all inputs provided")
+        vals = dict(self.inputs)
+        nodes = self.graph["nodes"]
+        consumers = {}
+        for n in nodes:
+            for i in n["inputs"]:
+                consumers[i] = consumers.get(i, 0) + 1
+        skip = set()
+        for idx, n in enumerate(nodes):
+            if idx in skip:
+                continue
+            op = n["op"]
+            if op == "Conv":
+                out_name, fused = self._conv(n, nodes, idx, vals, consumers, skip)
+                vals[out_name] = fused
+            elif op == "Gemm":
+                vals[n["outputs"][0]] = self._gemm(n, vals)
+            elif op == "Relu":
+                vals[n["outputs"][0]] = self.L.relu(vals[n["inputs"][0]])
+            elif op in ("MaxPool", "AveragePool"):
+                a = n["attrs"]
+                ks = a.get("kernel_shape", [2, 2])
+                st = a.get("strides", ks)
+                pd = a.get("pads", [0, 0, 0, 0])
+                vals[n["outputs"][0]] = self.L.pool2d(0 if op == "MaxPool" else 1, vals[n["inputs"][0]],
+                                                      (ks[0], ks[1], st[0], st[1], pd[0], pd[1]),
+                                                      bool(a.get("ceil_mode", 0)), bool(a.get("count_include_pad", 0)))
+            elif op == "GlobalAveragePool":
+                vals[n["outputs"][0]] = self.L.global_avgpool2d(vals[n["inputs"][0]])
+            elif op == "Flatten":
+                x = vals[n["inputs"][0]]
+                ax = n["attrs"].get("axis", 1)
+                vals[n["outputs"][0]] = x.reshape(int(np.prod(x.shape[:ax])), -1)
+            elif op == "Add":
+                vals[n["outputs"][0]] = self.L.add(vals[n["inputs"][0]], vals[n["inputs"][1]])
+            else:
+                raise NotImplementedError(f"Operator '{op}' not implemented")
+        self.values = {k: vals[k] for k in self.graph["outputs"]}
+        self.intermediates = vals
+
+    def _conv(self, n, nodes, idx, vals, consumers, skip):
+        L = self.L
+        a = n["attrs"]
+        st = a.get("strides", [1, 1])
+        pd = a.get("pads", [0, 0, 0, 0])
+        dl = a.get("dilations", [1, 1])
+        p = (st[0], st[1], pd[0], pd[1], dl[0], dl[1])  # only pads[0], pads[1] are honoured (model.hpp:313-321)
+        x = vals[n["inputs"][0]]
+        w = self.weights[n["inputs"][1]]
+        bias = self.weights[n["inputs"][2]]["dense"] if len(n["inputs"]) > 2 else None
+        if "words" not in w:
+            raise NotImplementedError("float-weight Conv is not on the accelerated path yet")
+        out_name = n["outputs"][0]
+        ws = self._workspace("conv", L.h.tbn_conv2d_workspace_bytes(w["shape"][1], w["shape"][2], w["shape"][3]))
+        if self.quantization:
+            y = L.conv2d_tbn(x, w["words"], w["shape"], p, alpha=w["alpha_tbn"], bias=bias,
+                             epilogue=capi.EPI_BIAS_BEFORE_ALPHA, workspace=ws)
+            return out_name, y
+        # float x binary: fold a following Relu (and Add + Relu of a residual block) into the epilogue.
+        epilogue, residual = 0, None
+        if self.fuse and consumers.get(out_name, 0) == 1 and idx + 1 < len(nodes):
+            nxt = nodes[idx + 1]
+            if nxt["op"] == "Relu" and nxt["inputs"] == [out_name]:
+                epilogue |= capi.EPI_RELU
+                skip.add(idx + 1)
+                out_name = nxt["outputs"][0]
+            elif (nxt["op"] == "Add" and out_name in nxt["inputs"] and idx + 2 < len(nodes)
+                  and nodes[idx + 2]["op"] == "Relu" and nodes[idx + 2]["inputs"] == nxt["outputs"]
+                  and consumers.get(nxt["outputs"][0], 0) == 1):
+                other = [i for i in nxt["inputs"] if i != out_name]
+                if len(other) == 1 and other[0] in vals:
+                    residual = vals[other[0]]
+                    epilogue |= capi.EPI_RELU
+                    skip.update((idx + 1, idx + 2))
+                    out_name = nodes[idx + 2]["outputs"][0]
+        y = L.conv2d_fxb(x, w["words"], w["shape"], p, alpha=w["alpha"], bias=bias, residual=residual,
+                         epilogue=epilogue, workspace=ws)
+        return out_name, y
+
+    def _gemm(self, n, vals):
+        L = self.L
+        a = n["attrs"]
+        if a.get("transA", 0) or a.get("transB", 0):
+            raise NotImplementedError("transposed Gemm operands are not on the accelerated path yet")
+        x = vals[n["inputs"][0]]
+        w = self.weights[n["inputs"][1]]
+        bias = self.weights[n["inputs"][2]]["dense"] if len(n["inputs"]) > 2 else None
+        if "words" not in w:
+            raise NotImplementedError("float-weight Gemm is not on the accelerated path yet")
+        N = w["shape"][1]
+        alpha_attr, beta = float(a.get("alpha", 1.0)), float(a.get("beta", 1.0))
+        if bias is not None and beta != 1.0:
+            bias = bias * beta
+        if self.quantization:
+            # Weights alpha*sign(w) are not exactly +-1, so the reference quantises them on the fly and runs
+            # qlinear_matmul_binary with scale 1 (model.hpp:839-841), then alpha and beta*C (:845-869).
+            ws, _ = L.gemm_workspace(x.shape[0], x.shape[1], capi.MODE_TC_BF16X1, self.device)
+            return L.gemm_tbn(x.contiguous(), w["words"], N, scale=alpha_attr, bias=bias, workspace=ws)
+        ws, _ = L.gemm_workspace(x.shape[0], x.shape[1], capi.MODE_TC_BF16X2, self.device)
+        return L.gemm_fxb(x.contiguous(), w["words"], N, alpha=w["alpha"], scale=alpha_attr, bias=bias, workspace=ws)

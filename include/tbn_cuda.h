@@ -57,6 +57,11 @@ extern "C" {
  * (tbn/runtime/model.hpp:523-557).  Default order is acc*alpha[n]*scale + bias[n]. */
 #define TBN_EPI_BIAS_BEFORE_ALPHA 2u
 
+/* Convolution only: add a residual tensor (same shape and layout as the output) before the ReLU --
+ * the Add + Relu that follows the second convolution of a residual block
+ * (Session::execute_add / execute_relu, tbn/runtime/model.hpp:905-1037, 1127-1174). */
+#define TBN_EPI_ADD_RESIDUAL 4u
+
 /* ---- weight layouts accepted by the packers ---------------------------------------- */
 #define TBN_LAYOUT_KN 0 /* W[K,N] row-major (Gemm B, transB = 0)                          */
 #define TBN_LAYOUT_NK 1 /* W[N,K] row-major (conv weights [M_out, C*kh*kw]; Gemm transB=1) */
@@ -99,6 +104,12 @@ int32_t tbn_quantize_to_binary(const float* d_w, int64_t n, float thr, uint8_t* 
 /* tbn::quantize_to_ternary (quantized_gemm_neon.cpp:570-597): -1 / 0 / +1 as int8. */
 int32_t tbn_quantize_to_ternary(const float* d_w, int64_t n, float lo, float hi, int8_t* d_out,
                                 void* stream);
+
+/* Per-output-channel scale alpha[c] = mean |w[c, :]| of weights [channels, per], summed sequentially in
+ * fp32 in memory order: bit-equal to Session::execute_conv (tbn/runtime/model.hpp:388-394).  One thread
+ * per channel -- meant for the one-time weight preparation of the bit-exact TBN mode; the packers'
+ * d_alpha output is the fast, chunk-summed equivalent. */
+int32_t tbn_channel_abs_mean(const float* d_w, int64_t channels, int64_t per, float* d_alpha, void* stream);
 
 /* Bytes of scratch tbn_quant_pack_* needs when d_alpha != NULL (0 otherwise). */
 size_t tbn_quant_pack_workspace_bytes(int64_t K, int64_t N, int32_t ternary);
@@ -177,6 +188,54 @@ int32_t tbn_gemm_tbn(const float* d_a, int64_t M, int64_t K, int64_t lda, float 
                      const uint32_t* d_neg, int64_t N, const float* d_alpha, float scale,
                      const float* d_bias, float* d_c, int64_t ldc, uint32_t epilogue,
                      void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* ---- convolution (implicit GEMM) ----------------------------------------------------- */
+
+/* Bytes of scratch the convolution entry points need (tap table + partial-sum tiles). */
+size_t tbn_conv2d_workspace_bytes(int64_t C, int64_t kh, int64_t kw);
+
+/* Float x binary / float x ternary Conv2D, NCHW fp32 in and out:
+ *     y[n,m,oh,ow] = (sum_{c,i,j} x[n,c,oh*sh-ph+i*dh, ow*sw-pw+j*dw] * w[m,c,i,j]) * alpha[m] * scale
+ *                    + bias[m] (+ residual[n,m,oh,ow]) (then optional ReLU)
+ * with w = +-1 (0) from the packed planes of the weights [M_out, C*kh*kw] (TBN_LAYOUT_NK); taps
+ * outside the image contribute zero; output size (in + 2p - d(k-1) - 1)/s + 1.  Equals tbn::conv2d
+ * (tbn-runtime/src/operators/conv2d.cpp:78-192) on the dequantised weights alpha*sign(w); replaces
+ * im2col + transpose + GEMM + reorder + bias of tbn::conv2d_binary / conv2d_binary_with_scales
+ * (conv2d.cpp:220-369, 420-507).  The im2col matrix is not materialised.
+ *   mode: TBN_MODE_AUTO (two bf16 terms), TBN_MODE_TC_BF16X2 or TBN_MODE_TC_BF16X1.
+ *   d_residual: nullable; read when TBN_EPI_ADD_RESIDUAL is set (same shape as y). */
+int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, const uint32_t* d_neg,
+                       const uint32_t* d_pos, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw,
+                       int32_t ph, int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale,
+                       const float* d_bias, const float* d_residual, float* d_y, int32_t mode,
+                       uint32_t epilogue, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* "TBN mode" Conv2D: activations ternarised at (lo, hi) while they are gathered, exact integer
+ * accumulation.  With alpha, bias and TBN_EPI_BIAS_BEFORE_ALPHA it is bit-equal to the cached fast
+ * path of Session::execute_conv (tbn/runtime/model.hpp:375-559: im2col_ternary_packed,
+ * conv2d.cpp:511-601, + GemmEngine::compute + reorder + bias + per-channel scale). */
+int32_t tbn_conv2d_tbn(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float lo, float hi,
+                       const uint32_t* d_neg, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw,
+                       int32_t ph, int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale,
+                       const float* d_bias, float* d_y, uint32_t epilogue, void* d_workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* ---- glue operators of the CNN graphs (device resident, fp32) --------------------------- */
+
+/* y = max(0, x)   (Session::execute_relu, model.hpp:1166-1169) */
+int32_t tbn_relu(const float* d_x, int64_t n, float* d_y, void* stream);
+/* y[i] = a[i] + b[(i / inner) % b_n] (+ ReLU): same-shape add (b_n == a_n), per-channel [C] over
+ * [N,C,H,W] (inner = H*W) and row broadcast [N] over [M,N] (inner = 1)
+ * (Session::execute_add, model.hpp:921-1036). */
+int32_t tbn_add(const float* d_a, int64_t a_n, const float* d_b, int64_t b_n, int64_t inner, int32_t relu,
+                float* d_y, void* stream);
+/* kind 0: tbn::maxpool2d, kind 1: tbn::avgpool2d (tbn-runtime/src/operators/pooling.cpp:10-148). */
+int32_t tbn_pool2d(int32_t kind, const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, int32_t kh,
+                   int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t ceil_mode,
+                   int32_t count_include_pad, float* d_y, void* stream);
+/* tbn::global_avgpool2d (pooling.cpp:184-216): [N,C,H,W] -> [N,C,1,1]. */
+int32_t tbn_global_avgpool2d(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float* d_y,
+                             void* stream);
 
 /* ---- multi-GPU helper -------------------------------------------------------------- */
 

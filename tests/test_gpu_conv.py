@@ -1,0 +1,219 @@
+"""Parity of the implicit-GEMM convolution, the glue operators and the device Session with the oracle."""
+import numpy as np
+import pytest
+
+from util import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 1e-5
+
+
+@pytest.fixture(scope="module")
+def tbn():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from fast_arm_tbcnn_b200 import capi
+    capi.lib.init()
+    return capi
+
+
+# (N, C, H, W, M_out, kh, kw, (sh, sw, ph, pw, dh, dw))
+CONV_CASES = [
+    (1, 64, 14, 14, 128, 3, 3, (1, 1, 1, 1, 1, 1)),   # the benchmark layer
+    (2, 3, 13, 12, 5, 3, 3, (1, 1, 1, 1, 1, 1)),
+    (2, 3, 13, 12, 5, 3, 3, (2, 2, 3, 3, 1, 1)),
+    (2, 3, 13, 12, 5, 3, 3, (1, 2, 0, 1, 2, 1)),
+    (1, 1, 28, 28, 6, 5, 5, (1, 1, 0, 0, 1, 1)),       # LeNet conv1
+    (3, 6, 12, 12, 16, 5, 5, (1, 1, 0, 0, 1, 1)),      # LeNet conv2
+    (5, 16, 9, 9, 40, 1, 1, (1, 1, 0, 0, 1, 1)),
+    (2, 3, 32, 32, 64, 7, 7, (2, 2, 3, 3, 1, 1)),
+    (33, 8, 7, 5, 24, 3, 3, (1, 1, 1, 1, 1, 1)),
+    (2, 512, 4, 4, 300, 3, 3, (1, 1, 1, 1, 1, 1)),     # K = 4608: three accumulation segments
+]
+
+
+def _conv_inputs(case, seed=0):
+    N, C, H, W, M, kh, kw, p = case
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((N, C, H, W), dtype=np.float32)
+    w = (rng.standard_normal((M, C, kh, kw), dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    b = (rng.standard_normal(M, dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    return x, w, b, p
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("mode", ["x2", "x1"])
+def test_conv_fxb_vs_float_conv(tbn, oracle, case, mode):
+    import torch
+    from oracle import graphs
+    x, w, b, p = _conv_inputs(case)
+    dw = torch.from_numpy(w).cuda()
+    words, alpha = tbn.lib.quant_pack_binary(dw.reshape(w.shape[0], -1), tbn.LAYOUT_NK)
+    m = tbn.MODE_TC_BF16X2 if mode == "x2" else tbn.MODE_TC_BF16X1
+    y = tbn.lib.conv2d_fxb(torch.from_numpy(x).cuda(), words, w.shape, p, alpha=alpha, bias=torch.from_numpy(b).cuda(),
+                           mode=m)
+    tbn.lib.sync()
+    expect = oracle.conv2d_f32(x, graphs.dequantise(w), b, p)
+    assert tuple(y.shape) == expect.shape
+    err = rel_l2(y.cpu().numpy(), expect)
+    assert err <= (TOL_FP32 if mode == "x2" else 2.5e-3), err
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_tbn_bit_exact(tbn, oracle, case):
+    """Ternarised activations x binary weights, (acc + bias) * alpha: the Session's cached conv path."""
+    import torch
+    from oracle import graphs
+    x, w, b, p = _conv_inputs(case, seed=3)
+    x.reshape(-1)[:4] = [0.1, -0.1, 0.100001, -0.100001]
+    wq = graphs.dequantise(w)  # what the reference sees: alpha * sign(w)
+    dwq = torch.from_numpy(wq).cuda()
+    words, _ = tbn.lib.quant_pack_binary(dwq.reshape(w.shape[0], -1), tbn.LAYOUT_NK, 0.0, True, want_alpha=False)
+    alpha = tbn.lib.channel_abs_mean(dwq)
+    y = tbn.lib.conv2d_tbn(torch.from_numpy(x).cuda(), words, w.shape, p, alpha=alpha, bias=torch.from_numpy(b).cuda(),
+                           epilogue=tbn.EPI_BIAS_BEFORE_ALPHA)
+    tbn.lib.sync()
+    assert np.array_equal(alpha.cpu().numpy(), oracle.channel_abs_mean(wq))
+    assert np.array_equal(y.cpu().numpy(), oracle.conv2d_tbn_session(x, wq, b, p))
+
+
+def test_conv_residual_relu_epilogue(tbn, oracle):
+    import torch
+    from oracle import graphs
+    case = (3, 16, 10, 10, 16, 3, 3, (1, 1, 1, 1, 1, 1))
+    x, w, b, p = _conv_inputs(case, seed=5)
+    res = np.random.default_rng(6).standard_normal((3, 16, 10, 10), dtype=np.float32)
+    dw = torch.from_numpy(w).cuda()
+    words, alpha = tbn.lib.quant_pack_binary(dw.reshape(16, -1), tbn.LAYOUT_NK)
+    y = tbn.lib.conv2d_fxb(torch.from_numpy(x).cuda(), words, w.shape, p, alpha=alpha, bias=torch.from_numpy(b).cuda(),
+                           residual=torch.from_numpy(res).cuda(), epilogue=tbn.EPI_RELU)
+    tbn.lib.sync()
+    expect = oracle.relu(oracle.add(oracle.conv2d_f32(x, graphs.dequantise(w), b, p), res))
+    assert rel_l2(y.cpu().numpy(), expect) <= TOL_FP32
+
+
+def test_conv_argument_errors(tbn):
+    import torch
+    x = torch.zeros((1, 3, 4, 4), device="cuda")
+    words = torch.zeros((8, 4), dtype=torch.int32, device="cuda")
+    with pytest.raises(tbn.TbnError) as e:
+        tbn.lib.conv2d_fxb(x, words, (5, 3, 7, 7), (1, 1, 0, 0, 1, 1))  # kernel larger than the image
+    assert e.value.status == -7
+    with pytest.raises(tbn.TbnError) as e:
+        tbn.lib.conv2d_fxb(x, words, (5, 3, 3, 3), (0, 1, 0, 0, 1, 1))
+    assert e.value.status == -1
+    with pytest.raises(tbn.TbnError) as e:
+        tbn.lib.conv2d_fxb(x, words, (5, 3, 3, 3), (1, 1, 0, 0, 1, 1), mode=tbn.MODE_TC_BF16X3)
+    assert e.value.status == -3
+
+
+def test_glue_operators(tbn, oracle):
+    import torch
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((2, 3, 9, 10), dtype=np.float32)
+    x[0, 0, 0, 0] = np.nan
+    d = torch.from_numpy(x).cuda()
+    assert np.array_equal(tbn.lib.relu(d).cpu().numpy(), oracle.relu(x))
+    x = np.nan_to_num(x)
+    d = torch.from_numpy(x).cuda()
+    for p in [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1), (3, 2, 1, 2, 1, 0)]:
+        for ceil_mode in (False, True):
+            assert np.array_equal(tbn.lib.pool2d(0, d, p, ceil_mode).cpu().numpy(), oracle.pool2d(0, x, p, ceil_mode))
+            for cip in (False, True):
+                assert np.array_equal(tbn.lib.pool2d(1, d, p, ceil_mode, cip).cpu().numpy(),
+                                      oracle.pool2d(1, x, p, ceil_mode, cip))
+    np.testing.assert_allclose(tbn.lib.global_avgpool2d(d).cpu().numpy(), oracle.pool2d(2, x, None), rtol=1e-6, atol=1e-7)
+    y = rng.standard_normal((2, 3, 9, 10), dtype=np.float32)
+    ch = rng.standard_normal(3, dtype=np.float32)
+    assert np.array_equal(tbn.lib.add(d, torch.from_numpy(y).cuda()).cpu().numpy(), oracle.add(x, y))
+    assert np.array_equal(tbn.lib.add(d, torch.from_numpy(ch).cuda()).cpu().numpy(), oracle.add(x, ch))
+    m = rng.standard_normal((5, 7), dtype=np.float32)
+    row = rng.standard_normal(7, dtype=np.float32)
+    assert np.array_equal(tbn.lib.add(torch.from_numpy(m).cuda(), torch.from_numpy(row).cuda()).cpu().numpy(), m + row)
+    assert np.array_equal(tbn.lib.add(d, torch.from_numpy(y).cuda(), relu=True).cpu().numpy(), np.maximum(x + y, 0))
+
+
+@pytest.mark.parametrize("batch", [1, 7, 256])
+def test_lenet_session_float_binary(tbn, oracle, batch):
+    """The simple_cnn-shaped binary CNN: every layer within 1e-5 of the reference's float path on the
+    dequantised weights, and the predicted classes identical."""
+    from fast_arm_tbcnn_b200.session import Session
+    from oracle import graphs
+    net = graphs.lenet(batch=batch, seed=1)
+    x = np.random.default_rng(0).random((batch, 1, 28, 28), dtype=np.float32)
+    keep = {}
+    expect = graphs.run_float(net, x, oracle, keep)
+    for fuse in (True, False):
+        s = Session(net, fuse=fuse)
+        s.set_input("input", x)
+        s.run()
+        tbn.lib.sync()
+        got = s.get_output("output").cpu().numpy()
+        assert rel_l2(got, expect) <= TOL_FP32
+        assert np.array_equal(got.argmax(axis=1), expect.argmax(axis=1))
+        if not fuse:
+            for name, ref in keep.items():
+                assert rel_l2(s.intermediates[name].cpu().numpy().reshape(ref.shape), ref) <= TOL_FP32, name
+    with pytest.raises(ValueError):
+        s.set_input("input", x[:, :, :27])
+    with pytest.raises(KeyError):
+        s.set_input("nope", x)
+
+
+def test_lenet_session_tbn_mode_bit_exact(tbn, golden):
+    """Quantisation on: bit-equal to the reference Session's output stored in the golden fixture."""
+    from fast_arm_tbcnn_b200.session import Session
+    from oracle import graphs
+    r = golden["ref_outputs_small"]
+    net = graphs.lenet(batch=1, seed=1)
+    s = Session(net)
+    s.set_quantization(True)
+    s.set_input("input", r["lenet_x"])
+    s.run()
+    tbn.lib.sync()
+    assert np.array_equal(s.get_output("output").cpu().numpy(), r["lenet_tbn_session"])
+
+
+@pytest.mark.parametrize("batch", [1, 64])
+def test_conv_layer_session_both_modes(tbn, oracle, batch):
+    """64x14x14 -> 128x14x14, 3x3, stride 1, pad 1, with bias."""
+    from fast_arm_tbcnn_b200.session import Session
+    from oracle import graphs
+    net = graphs.conv_layer(batch=batch)
+    x = np.random.default_rng(0).standard_normal((batch, 64, 14, 14), dtype=np.float32)
+    s = Session(net)
+    s.set_input("input", x)
+    s.run()
+    tbn.lib.sync()
+    assert rel_l2(s.get_output("output").cpu().numpy(), graphs.run_float(net, x, oracle)) <= TOL_FP32
+    s.set_quantization(True)
+    s.run()
+    tbn.lib.sync()
+    wq = graphs.dequantise(net["inits"]["w"])
+    expect = oracle.conv2d_tbn_session(x, wq, net["inits"]["b"], (1, 1, 1, 1, 1, 1))
+    assert np.array_equal(s.get_output("output").cpu().numpy(), expect)
+
+
+def test_conv_full_batch_properties(tbn):
+    """Batch 4096 of the benchmark layer (M = 802816 GEMM rows): batch independence -- every image's
+    output equals the output of the same image run alone -- and linearity in the input."""
+    import torch
+    from fast_arm_tbcnn_b200 import capi
+    g = torch.Generator(device="cuda").manual_seed(0)
+    B = 4096
+    x = torch.randn((B, 64, 14, 14), generator=g, device="cuda")
+    w = torch.randn((128, 64, 3, 3), generator=g, device="cuda") * 0.05
+    bias = torch.randn(128, generator=g, device="cuda") * 0.05
+    words, alpha = tbn.lib.quant_pack_binary(w.reshape(128, -1), capi.LAYOUT_NK)
+    p = (1, 1, 1, 1, 1, 1)
+    y = tbn.lib.conv2d_fxb(x, words, w.shape, p, alpha=alpha, bias=bias)
+    tbn.lib.sync()
+    for i in (0, 1, 2047, 4095):
+        yi = tbn.lib.conv2d_fxb(x[i:i + 1].contiguous(), words, w.shape, p, alpha=alpha, bias=bias)
+        tbn.lib.sync()
+        assert torch.equal(yi[0], y[i])
+    y_neg = tbn.lib.conv2d_fxb(-x, words, w.shape, p, alpha=alpha)
+    y_pos = tbn.lib.conv2d_fxb(x, words, w.shape, p, alpha=alpha)
+    tbn.lib.sync()
+    assert torch.equal(y_neg, -y_pos)
