@@ -1,0 +1,53 @@
+"""Builds the C++ host layer (the tbn:: API mirror) and its test driver with g++.
+
+    python -m fast_arm_tbcnn_b200.host_build [--force]
+
+Produces host/lib/libtbn_host.so (links against lib/libtbn_cuda.so) and host/bin/run_graph.
+"""
+import glob
+import os
+import subprocess
+import sys
+
+from . import build as _cuda_build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HOST = os.path.join(ROOT, "host")
+LIB = os.path.join(HOST, "lib", "libtbn_host.so")
+RUN_GRAPH = os.path.join(HOST, "bin", "run_graph")
+
+
+def _stale(target, deps):
+    return not os.path.exists(target) or any(os.path.getmtime(d) > os.path.getmtime(target) for d in deps)
+
+
+def build(force=False):
+    cuda_lib = _cuda_build.build()
+    srcs = sorted(glob.glob(os.path.join(HOST, "src", "*.cpp")))
+    hdrs = glob.glob(os.path.join(HOST, "include", "tbn", "**", "*.hpp"), recursive=True) + [
+        os.path.join(ROOT, "include", "tbn_cuda.h")]
+    os.makedirs(os.path.dirname(LIB), exist_ok=True)
+    os.makedirs(os.path.dirname(RUN_GRAPH), exist_ok=True)
+    cxx = os.environ.get("CXX", "g++")
+    inc = ["-I", os.path.join(HOST, "include"), "-I", os.path.join(ROOT, "include")]
+    cuda_dir = os.path.dirname(cuda_lib)
+    if force or _stale(LIB, srcs + hdrs + [cuda_lib]):
+        cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-o", LIB] + inc + srcs + [
+            "-L", cuda_dir, "-ltbn_cuda", "-Wl,-rpath,$ORIGIN/../../fast_arm_tbcnn_b200/lib"]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+            raise RuntimeError("g++ failed building " + LIB)
+    driver = os.path.join(HOST, "tests", "run_graph.cpp")
+    if force or _stale(RUN_GRAPH, [driver, LIB] + hdrs):
+        cmd = [cxx, "-std=c++17", "-O2", "-Wall", "-o", RUN_GRAPH] + inc + [driver, "-L", os.path.dirname(LIB), "-ltbn_host",
+               "-L", cuda_dir, "-ltbn_cuda", "-Wl,-rpath,$ORIGIN/../lib", "-Wl,-rpath,$ORIGIN/../../fast_arm_tbcnn_b200/lib"]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+            raise RuntimeError("g++ failed building " + RUN_GRAPH)
+    return LIB, RUN_GRAPH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))

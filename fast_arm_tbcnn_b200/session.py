@@ -49,10 +49,10 @@ class Session:
         if w.dim() == 4:  # conv [M, C, kh, kw] -> K = C*kh*kw along the row: layout NK
             flat = w.reshape(w.shape[0], -1)
             words_gt, alpha = L.quant_pack_binary(flat, capi.LAYOUT_NK, 0.0, False)
-            # TBN mode reproduces the Session on dequantised weights: sign by >= 0 and the scale summed
-            # sequentially over alpha*sign(w) (model.hpp:388-394, 433).
-            deq = self.torch.where(flat > 0, 1.0, -1.0) * alpha[:, None]
-            alpha_seq = L.channel_abs_mean(deq.contiguous())
+            # TBN mode uses the scale summed sequentially over the given weights, exactly as the reference
+            # Session does (model.hpp:388-394); given a dequantised model (+-alpha weights) the whole Conv is
+            # then bit-equal to the reference.
+            alpha_seq = L.channel_abs_mean(flat.contiguous())
             return {"shape": tuple(w.shape), "words": words_gt, "alpha": alpha, "alpha_tbn": alpha_seq}
         words_gt, alpha = L.quant_pack_binary(w, capi.LAYOUT_KN, 0.0, False)  # Gemm B [K, N]
         return {"shape": tuple(w.shape), "words": words_gt, "alpha": alpha}

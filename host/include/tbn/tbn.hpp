@@ -1,0 +1,8 @@
+// Umbrella header of the tbn:: API (reference: tbn-runtime/include/tbn/tbn.hpp).
+#pragma once
+#include "operators/ops.hpp"
+#include "runtime/attribute.hpp"
+#include "runtime/model.hpp"
+#include "runtime/tensor.hpp"
+#include "runtime/types.hpp"
+#include "utils/errors.hpp"

@@ -1,0 +1,366 @@
+// TBNModel / Session on the GPU and the graph-spec reader.  Attribute handling follows the reference
+// Session node by node (tbn-runtime/include/tbn/runtime/model.hpp:238-1316); the arithmetic is delegated
+// to the operator functions in ops.cpp, i.e. to CUDA kernels behind the C ABI.
+#include <algorithm>
+#include <sstream>
+
+#include "tbn/runtime/model.hpp"
+
+namespace tbn {
+
+// ------------------------------------------------------------------------- TBNModel
+
+bool TBNModel::has_input(const std::string& name) const {
+    return std::find(graph_->inputs.begin(), graph_->inputs.end(), name) != graph_->inputs.end();
+}
+bool TBNModel::has_output(const std::string& name) const {
+    return std::find(graph_->outputs.begin(), graph_->outputs.end(), name) != graph_->outputs.end();
+}
+const Shape& TBNModel::get_input_shape(const std::string& name) const {
+    auto it = graph_->value_info.find(name);
+    TBN_CHECK(it != graph_->value_info.end(), InvalidArgumentError, "Input '" + name + "' not found in model");
+    return it->second;
+}
+const Shape& TBNModel::get_output_shape(const std::string& name) const {
+    auto it = graph_->value_info.find(name);
+    TBN_CHECK(it != graph_->value_info.end(), InvalidArgumentError, "Output '" + name + "' not found in model");
+    return it->second;
+}
+void TBNModel::validate() const {
+    TBN_CHECK(!graph_->inputs.empty(), InvalidModelError, "Model has no inputs");
+    TBN_CHECK(!graph_->outputs.empty(), InvalidModelError, "Model has no outputs");
+    TBN_CHECK(!graph_->nodes.empty(), InvalidModelError, "Model has no computation nodes");
+    for (const auto& n : graph_->inputs)
+        TBN_CHECK(graph_->value_info.count(n) > 0, InvalidModelError, "Input '" + n + "' shape not defined");
+    for (const auto& n : graph_->outputs)
+        TBN_CHECK(graph_->value_info.count(n) > 0, InvalidModelError, "Output '" + n + "' shape not defined");
+}
+
+// ------------------------------------------------------------------------- Session
+
+TBNModel::Session::Session(std::shared_ptr<ModelGraph> graph, TilingParams tiling) : graph_(std::move(graph)), tiling_(tiling) {}
+
+void TBNModel::Session::set_input(const std::string& name, const Tensor& tensor) {
+    TBN_CHECK(graph_->value_info.count(name) > 0, InvalidArgumentError, "Input '" + name + "' not found in model");
+    TBN_CHECK(tensor.shape() == graph_->value_info.at(name), InvalidShapeError, "Input shape mismatch for '" + name + "'");
+    tensor.device_data();  // upload now (no-op for a tensor that already lives on the device)
+    input_tensors_[name] = tensor;
+}
+
+Tensor TBNModel::Session::get_input(const std::string& name) const {
+    auto it = input_tensors_.find(name);
+    TBN_CHECK(it != input_tensors_.end(), InvalidArgumentError, "Input '" + name + "' not set");
+    return it->second;
+}
+
+Tensor TBNModel::Session::get_output(const std::string& name) const {
+    auto it = output_tensors_.find(name);
+    TBN_CHECK(it != output_tensors_.end(), InvalidArgumentError, "Output '" + name + "' not available");
+    return it->second;
+}
+
+const Tensor& TBNModel::Session::value(const std::string& name) const {
+    auto it = intermediate_tensors_.find(name);
+    TBN_CHECK(it != intermediate_tensors_.end(), RuntimeError, "Input tensor '" + name + "' not found");
+    return it->second;
+}
+
+void TBNModel::Session::run() {
+    size_t user_inputs = 0;
+    for (const auto& n : graph_->inputs)
+        if (graph_->initializers.find(n) == graph_->initializers.end()) ++user_inputs;
+    TBN_CHECK(input_tensors_.size() == user_inputs, InvalidArgumentError,
+              "Not all inputs provided (expected " + std::to_string(user_inputs) + ", got " +
+                  std::to_string(input_tensors_.size()) + ")");
+    output_tensors_.clear();
+    intermediate_tensors_.clear();
+    for (const auto& kv : input_tensors_) intermediate_tensors_[kv.first] = kv.second;
+    for (const auto& kv : graph_->initializers) intermediate_tensors_[kv.first] = kv.second;
+    for (const auto& node : graph_->nodes) execute_node(node);
+    for (const auto& out : graph_->outputs) {
+        auto it = intermediate_tensors_.find(out);
+        TBN_CHECK(it != intermediate_tensors_.end(), RuntimeError, "Output '" + out + "' was not produced");
+        output_tensors_[out] = it->second;
+    }
+    synchronize();
+}
+
+const TBNModel::Session::CachedWeights* TBNModel::Session::weights_for(const std::string& name, const Tensor& w, bool conv) {
+    auto it = weight_cache_.find(name);
+    if (it != weight_cache_.end()) return &it->second;
+    if (w.dtype() != DataType::FLOAT32) return nullptr;
+    CachedWeights cw;
+    const bool declared = declared_binary_.count(name) > 0;
+    if (conv) {
+        std::vector<float> scales;
+        cw.scaled_binary = scaled_binary_channel_scales(w, &scales);
+        if (!cw.scaled_binary && !declared) return nullptr;
+        // Scaled-binary: sign by >= 0 (model.hpp:433).  Declared raw weights: quantize_to_binary's w > 0.
+        cw.packed = pack_binary_weights(w, 0.0f, cw.scaled_binary);
+        if (cw.scaled_binary) cw.alpha_tbn = make_tensor(Shape{static_cast<int64_t>(scales.size())}, scales);
+        else cw.alpha_tbn = cw.packed.alpha;
+    } else {
+        const int64_t K = w.shape().dims[0], N = w.shape().dims[1];
+        const float* b = w.typed_data<float>();
+        Tensor bt(Shape{N, K}, DataType::FLOAT32);
+        float* t = bt.typed_data<float>();
+        for (int64_t k = 0; k < K; ++k)
+            for (int64_t n = 0; n < N; ++n) t[n * K + k] = b[k * N + n];
+        cw.scaled_binary = scaled_binary_channel_scales(bt, nullptr);
+        if (!cw.scaled_binary && !declared) return nullptr;
+        cw.packed = pack_binary_weights(w, 0.0f, false);  // w > 0, as quantize_to_binary (model.hpp:840)
+    }
+    return &weight_cache_.emplace(name, std::move(cw)).first->second;
+}
+
+void TBNModel::Session::execute_conv(const ModelNode& node) {
+    TBN_CHECK(node.inputs.size() >= 2, InvalidArgumentError, "Conv expects at least 2 inputs");
+    TBN_CHECK(node.outputs.size() == 1, InvalidArgumentError, "Conv expects 1 output");
+    const Tensor& X = value(node.inputs[0]);
+    const Tensor& W = value(node.inputs[1]);
+    TBN_CHECK(W.shape().dims.size() == 4, InvalidShapeError, "Conv2D weights must be 4D (MCHW)");
+    Conv2DParams p;
+    p.kernel_h = W.shape().dims[2];
+    p.kernel_w = W.shape().dims[3];
+    auto a = node.attributes.find("strides");
+    if (a != node.attributes.end() && a->second.is_ints() && a->second.as_ints().size() >= 2) {
+        p.stride_h = a->second.as_ints()[0];
+        p.stride_w = a->second.as_ints()[1];
+    }
+    a = node.attributes.find("pads");  // begin_h, begin_w are the ones honoured (model.hpp:313-321)
+    if (a != node.attributes.end() && a->second.is_ints() && a->second.as_ints().size() >= 4) {
+        p.pad_h = a->second.as_ints()[0];
+        p.pad_w = a->second.as_ints()[1];
+    }
+    a = node.attributes.find("auto_pad");
+    if (a != node.attributes.end() && a->second.is_string() &&
+        (a->second.as_string() == "SAME_UPPER" || a->second.as_string() == "SAME_LOWER")) {
+        p.pad_h = (p.kernel_h - 1) * p.dilation_h / 2;
+        p.pad_w = (p.kernel_w - 1) * p.dilation_w / 2;
+    }
+    a = node.attributes.find("dilations");
+    if (a != node.attributes.end() && a->second.is_ints() && a->second.as_ints().size() >= 2) {
+        p.dilation_h = a->second.as_ints()[0];
+        p.dilation_w = a->second.as_ints()[1];
+    }
+    a = node.attributes.find("group");
+    if (a != node.attributes.end() && a->second.is_int()) p.groups = a->second.as_int();
+    const Tensor* B = nullptr;
+    if (node.inputs.size() >= 3) {
+        auto it = intermediate_tensors_.find(node.inputs[2]);
+        if (it != intermediate_tensors_.end()) B = &it->second;
+    }
+    Tensor result;
+    if (W.dtype() == DataType::BINARY) {
+        result = conv2d_binary(X, W, B, p);
+    } else if (W.dtype() == DataType::TERNARY) {
+        result = conv2d_ternary(X, W, B, p);
+    } else {
+        const CachedWeights* cw = weights_for(node.inputs[1], W, true);
+        if (use_quantization_) {
+            if (cw && cw->scaled_binary) {
+                result = conv2d_tbn_packed(X, cw->packed, &cw->alpha_tbn, B, p, true);  // (acc + bias) * alpha
+            } else {
+                // model.hpp:560-563: quantize_to_binary + conv2d_binary (no per-channel scale).
+                result = conv2d_binary(X, quantize_to_binary(W), B, p);
+            }
+        } else {
+            if (!cw) throw NotImplementedError("Conv '" + node.name + "': float filters that are neither scaled-binary nor "
+                                               "declared with mark_binary() are not on the accelerated path");
+            result = conv2d_float_packed(X, cw->packed, B, p);
+        }
+    }
+    intermediate_tensors_[node.outputs[0]] = result;
+}
+
+void TBNModel::Session::execute_gemm(const ModelNode& node) {
+    TBN_CHECK(node.inputs.size() >= 2, InvalidArgumentError, "Gemm expects at least 2 inputs");
+    TBN_CHECK(node.outputs.size() == 1, InvalidArgumentError, "Gemm expects 1 output");
+    const Tensor& A = value(node.inputs[0]);
+    const Tensor& Bw = value(node.inputs[1]);
+    float alpha = 1.0f, beta = 1.0f;
+    bool transA = false, transB = false;
+    auto a = node.attributes.find("alpha");
+    if (a != node.attributes.end() && a->second.is_float()) alpha = a->second.as_float();
+    a = node.attributes.find("beta");
+    if (a != node.attributes.end() && a->second.is_float()) beta = a->second.as_float();
+    a = node.attributes.find("transA");
+    if (a != node.attributes.end() && a->second.is_int()) transA = a->second.as_int() != 0;
+    a = node.attributes.find("transB");
+    if (a != node.attributes.end() && a->second.is_int()) transB = a->second.as_int() != 0;
+    const Tensor* C = nullptr;
+    if (node.inputs.size() >= 3) {
+        auto it = intermediate_tensors_.find(node.inputs[2]);
+        if (it != intermediate_tensors_.end()) C = &it->second;
+    }
+    if (transA || transB) throw NotImplementedError("Gemm '" + node.name + "': transposed operands are not on the accelerated path");
+    TBN_CHECK(Bw.shape().dims.size() == 2, InvalidShapeError, "Gemm B must be 2D");
+    const CachedWeights* cw = weights_for(node.inputs[1], Bw, false);
+    if (!cw) throw NotImplementedError("Gemm '" + node.name + "': float weights that are neither scaled-binary nor declared with "
+                                       "mark_binary() are not on the accelerated path");
+    Tensor bias;
+    if (C && beta != 0.0f) {
+        TBN_CHECK(C->shape().dims.size() == 1, NotImplementedError, "Gemm: only a 1-D C (bias) is accelerated");
+        if (beta == 1.0f) {
+            bias = *C;
+        } else {
+            bias = C->to_device(DeviceType::CPU);
+            float* pb = bias.typed_data<float>();
+            for (int64_t i = 0; i < bias.num_elements(); ++i) pb[i] *= beta;
+        }
+    }
+    Tensor result;
+    if (use_quantization_) {
+        // model.hpp:835-869: binary GEMM with scale 1, then * alpha, + beta * C.
+        result = qlinear_matmul_binary_packed(A, cw->packed, alpha);
+        if (!bias.empty()) result = add(result, bias);
+    } else {
+        result = matmul_float_packed(A, cw->packed, bias.empty() ? nullptr : &bias, alpha);
+    }
+    intermediate_tensors_[node.outputs[0]] = result;
+}
+
+void TBNModel::Session::execute_pool(const ModelNode& node, bool is_max) {
+    const Tensor& X = value(node.inputs.at(0));
+    Pool2DParams p;
+    auto a = node.attributes.find("kernel_shape");
+    if (a != node.attributes.end() && a->second.is_ints() && a->second.as_ints().size() >= 2) {
+        p.kernel_h = a->second.as_ints()[0];
+        p.kernel_w = a->second.as_ints()[1];
+    }
+    p.stride_h = p.kernel_h;
+    p.stride_w = p.kernel_w;
+    a = node.attributes.find("strides");
+    if (a != node.attributes.end() && a->second.is_ints() && a->second.as_ints().size() >= 2) {
+        p.stride_h = a->second.as_ints()[0];
+        p.stride_w = a->second.as_ints()[1];
+    }
+    a = node.attributes.find("pads");
+    if (a != node.attributes.end() && a->second.is_ints() && a->second.as_ints().size() >= 2) {
+        p.pad_h = a->second.as_ints()[0];
+        p.pad_w = a->second.as_ints()[1];
+    }
+    a = node.attributes.find("ceil_mode");
+    if (a != node.attributes.end() && a->second.is_int()) p.ceil_mode = a->second.as_int() != 0;
+    a = node.attributes.find("count_include_pad");
+    if (a != node.attributes.end() && a->second.is_int()) p.count_include_pad = a->second.as_int() != 0;
+    intermediate_tensors_[node.outputs.at(0)] = is_max ? maxpool2d(X, p) : avgpool2d(X, p);
+}
+
+void TBNModel::Session::execute_node(const ModelNode& node) {
+    const std::string& op = node.op_type;
+    if (op == "Conv") {
+        execute_conv(node);
+    } else if (op == "Gemm") {
+        execute_gemm(node);
+    } else if (op == "Relu") {
+        TBN_CHECK(node.inputs.size() == 1, InvalidArgumentError, "ReLU expects 1 input");
+        intermediate_tensors_[node.outputs.at(0)] = relu(value(node.inputs[0]));
+    } else if (op == "MaxPool") {
+        execute_pool(node, true);
+    } else if (op == "AveragePool" || op == "AvgPool") {
+        execute_pool(node, false);
+    } else if (op == "GlobalAveragePool" || op == "GlobalAvgPool") {
+        intermediate_tensors_[node.outputs.at(0)] = global_avgpool2d(value(node.inputs.at(0)));
+    } else if (op == "Add") {
+        TBN_CHECK(node.inputs.size() == 2, InvalidArgumentError, "Add expects 2 inputs");
+        intermediate_tensors_[node.outputs.at(0)] = add(value(node.inputs[0]), value(node.inputs[1]));
+    } else if (op == "Flatten") {
+        const Tensor& X = value(node.inputs.at(0));
+        int64_t axis = 1;
+        auto a = node.attributes.find("axis");
+        if (a != node.attributes.end() && a->second.is_int()) axis = a->second.as_int();
+        int64_t outer = 1;
+        for (int64_t i = 0; i < axis && i < static_cast<int64_t>(X.shape().dims.size()); ++i) outer *= X.shape().dims[i];
+        intermediate_tensors_[node.outputs.at(0)] = X.reshaped(Shape{outer, X.num_elements() / std::max<int64_t>(outer, 1)});
+    } else if (op == "Reshape") {
+        const Tensor& X = value(node.inputs.at(0));
+        const Tensor& S = value(node.inputs.at(1));
+        const int64_t* sd = S.typed_data<int64_t>();
+        std::vector<int64_t> dims(sd, sd + S.num_elements());
+        int64_t known = 1, infer = -1;
+        for (size_t i = 0; i < dims.size(); ++i) {
+            if (dims[i] == -1) infer = static_cast<int64_t>(i);
+            else known *= dims[i];
+        }
+        if (infer >= 0) dims[static_cast<size_t>(infer)] = X.num_elements() / std::max<int64_t>(known, 1);
+        intermediate_tensors_[node.outputs.at(0)] = X.reshaped(Shape(dims));
+    } else if (op == "Cast") {
+        intermediate_tensors_[node.outputs.at(0)] = value(node.inputs.at(0));
+    } else {
+        throw NotImplementedError("Operator '" + op + "' not implemented");
+    }
+}
+
+// ------------------------------------------------------------------------- loaders
+
+TBNModel load_onnx_model(const std::string& model_path) {
+    throw InvalidModelError("load_onnx_model('" + model_path + "'): the ONNX protobuf reader is not part of this build; "
+                            "fill a ModelGraph by hand or use parse_graph_spec()");
+}
+TBNModel load_model(const std::string& model_path) { return load_onnx_model(model_path); }
+const char* get_version() { return "0.1.0-b200"; }
+
+namespace {
+std::vector<std::string> split(const std::string& s, char sep) {
+    std::vector<std::string> out;
+    std::string cur;
+    std::istringstream is(s);
+    while (std::getline(is, cur, sep))
+        if (!cur.empty()) out.push_back(cur);
+    return out;
+}
+std::vector<int64_t> ints(const std::string& s) {
+    std::vector<int64_t> v;
+    for (const auto& p : split(s, ',')) v.push_back(std::stoll(p));
+    return v;
+}
+}  // namespace
+
+TBNModel parse_graph_spec(const std::string& spec, const float* blob, const int64_t* iblob, std::vector<std::string>* binary_names) {
+    auto graph = std::make_shared<ModelGraph>();
+    std::istringstream lines(spec);
+    std::string line;
+    while (std::getline(lines, line)) {
+        const auto tok = split(line, ' ');
+        if (tok.empty() || tok[0][0] == '#') continue;
+        if ((tok[0] == "input" || tok[0] == "output" || tok[0] == "value") && tok.size() >= 3) {
+            graph->value_info[tok[1]] = Shape(ints(tok[2]));
+            if (tok[0] == "input") graph->inputs.push_back(tok[1]);
+            if (tok[0] == "output") graph->outputs.push_back(tok[1]);
+        } else if (tok[0] == "init" && tok.size() >= 5) {
+            const Shape shape(ints(tok[3]));
+            const int64_t off = std::stoll(tok[4]);
+            if (tok[2] == "f32") graph->initializers[tok[1]] = Tensor(shape, DataType::FLOAT32, blob + off);
+            else if (tok[2] == "i64") graph->initializers[tok[1]] = Tensor(shape, DataType::INT64, iblob + off);
+            else throw InvalidModelError("graph spec: unknown initializer type in '" + line + "'");
+        } else if (tok[0] == "node" && tok.size() >= 5) {
+            ModelNode node;
+            node.op_type = tok[1];
+            node.name = tok[2];
+            node.inputs = split(tok[3], ',');
+            node.outputs = split(tok[4], ',');
+            for (size_t i = 5; i < tok.size(); ++i) {
+                const auto eq = tok[i].find('=');
+                if (eq == std::string::npos || eq + 3 > tok[i].size()) throw InvalidModelError("graph spec: bad attribute '" + tok[i] + "'");
+                const std::string key = tok[i].substr(0, eq), val = tok[i].substr(eq + 3);
+                switch (tok[i][eq + 1]) {
+                    case 'i': node.attributes[key] = AttributeValue(static_cast<int64_t>(std::stoll(val))); break;
+                    case 'f': node.attributes[key] = AttributeValue(std::stof(val)); break;
+                    case 's': node.attributes[key] = AttributeValue(val); break;
+                    case 'I': node.attributes[key] = AttributeValue(ints(val)); break;
+                    default: throw InvalidModelError("graph spec: bad attribute kind in '" + tok[i] + "'");
+                }
+            }
+            graph->nodes.push_back(std::move(node));
+        } else if (tok[0] == "binary" && tok.size() >= 2) {
+            if (binary_names)
+                for (const auto& n : split(tok[1], ',')) binary_names->push_back(n);
+        } else {
+            throw InvalidModelError("graph spec: cannot parse '" + line + "'");
+        }
+    }
+    return TBNModel(graph);
+}
+
+}  // namespace tbn

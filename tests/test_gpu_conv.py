@@ -167,6 +167,7 @@ def test_lenet_session_tbn_mode_bit_exact(tbn, golden):
     from oracle import graphs
     r = golden["ref_outputs_small"]
     net = graphs.lenet(batch=1, seed=1)
+    net = dict(net, inits={k: (graphs.dequantise(v) if k in net["binary"] else v) for k, v in net["inits"].items()})
     s = Session(net)
     s.set_quantization(True)
     s.set_input("input", r["lenet_x"])
@@ -187,10 +188,14 @@ def test_conv_layer_session_both_modes(tbn, oracle, batch):
     s.run()
     tbn.lib.sync()
     assert rel_l2(s.get_output("output").cpu().numpy(), graphs.run_float(net, x, oracle)) <= TOL_FP32
+    # TBN mode on the dequantised model (+-alpha weights), which is what the reference Session is given.
+    wq = graphs.dequantise(net["inits"]["w"])
+    net_q = dict(net, inits=dict(net["inits"], w=wq))
+    s = Session(net_q)
     s.set_quantization(True)
+    s.set_input("input", x)
     s.run()
     tbn.lib.sync()
-    wq = graphs.dequantise(net["inits"]["w"])
     expect = oracle.conv2d_tbn_session(x, wq, net["inits"]["b"], (1, 1, 1, 1, 1, 1))
     assert np.array_equal(s.get_output("output").cpu().numpy(), expect)
 

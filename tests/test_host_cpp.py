@@ -1,0 +1,77 @@
+"""The C++ host layer (tbn:: API mirror in host/): builds with g++, exports the reference's entry points,
+and -- on a GPU -- runs the benchmark graphs through tbn::TBNModel::Session with the same results as the
+oracle (float x binary mode) and the stored reference outputs (TBN mode)."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from util import rel_l2
+
+
+@pytest.fixture(scope="module")
+def host():
+    from fast_arm_tbcnn_b200 import host_build
+    lib, driver = host_build.build()
+    return lib, driver
+
+
+def test_host_layer_builds_and_exports_reference_names(host):
+    lib, driver = host
+    out = subprocess.run(["nm", "-DC", lib], capture_output=True, text=True, check=True).stdout
+    for name in ["tbn::qlinear_matmul_binary(", "tbn::quantize_to_binary(", "tbn::quantize_to_ternary(",
+                 "tbn::conv2d_binary(", "tbn::conv2d_binary_with_scales(", "tbn::conv2d(", "tbn::gemm(",
+                 "tbn::maxpool2d(", "tbn::avgpool2d(", "tbn::global_avgpool2d(", "tbn::load_onnx_model(",
+                 "tbn::TBNModel::Session::set_input(", "tbn::TBNModel::Session::run(",
+                 "tbn::TBNModel::Session::get_output(", "tbn::Tensor::to_device("]:
+        assert name in out, name
+    assert os.access(driver, os.X_OK)
+
+
+def _run(driver, tmp_path, net, x, quant, out_shape, dequantised, repeat=1):
+    from oracle import graphs
+    spec, blob, _ = graphs.to_spec(net, dequantised=dequantised)
+    (tmp_path / "spec.txt").write_text(spec)
+    blob.tofile(tmp_path / "blob.f32")
+    np.ascontiguousarray(x, dtype=np.float32).tofile(tmp_path / "x.f32")
+    out = tmp_path / f"out_{quant}.f32"
+    proc = subprocess.run([driver, str(tmp_path / "spec.txt"), str(tmp_path / "blob.f32"), str(tmp_path / "x.f32"), "input",
+                           "output", str(int(quant)), str(out), str(repeat)], capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stderr
+    return np.fromfile(out, dtype=np.float32).reshape(out_shape)
+
+
+@pytest.mark.gpu
+def test_error_paths_throw_the_reference_exception_types(host):
+    proc = subprocess.run([host[1], "--errors"], capture_output=True, text=True)
+    assert proc.returncode == 0 and "errors ok" in proc.stdout, proc.stdout + proc.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dequantised", [False, True])
+def test_lenet_through_cpp_session(host, oracle, golden, tmp_path, dequantised):
+    """Raw fp32 weights declared binary (mark_binary) and a dequantised TBN model (+-alpha weights, detected)
+    give the same float x binary result; TBN mode on the dequantised model is bit-equal to the reference."""
+    from oracle import graphs
+    net = graphs.lenet(batch=1, seed=1)
+    x = golden["ref_outputs_small"]["lenet_x"]
+    expect = graphs.run_float(net, x, oracle)
+    got = _run(host[1], tmp_path, net, x, False, (1, 10), dequantised, repeat=2)
+    assert rel_l2(got, expect) <= 1e-5
+    assert got.argmax() == expect.argmax()
+    if dequantised:
+        got_q = _run(host[1], tmp_path, net, x, True, (1, 10), True)
+        assert np.array_equal(got_q, golden["ref_outputs_small"]["lenet_tbn_session"])
+
+
+@pytest.mark.gpu
+def test_conv_layer_through_cpp_session(host, oracle, tmp_path):
+    from oracle import graphs
+    net = graphs.conv_layer(batch=3)
+    x = np.random.default_rng(0).standard_normal((3, 64, 14, 14), dtype=np.float32)
+    got = _run(host[1], tmp_path, net, x, False, (3, 128, 14, 14), True)
+    assert rel_l2(got, graphs.run_float(net, x, oracle)) <= 1e-5
+    got_q = _run(host[1], tmp_path, net, x, True, (3, 128, 14, 14), True)
+    wq = graphs.dequantise(net["inits"]["w"])
+    assert np.array_equal(got_q, oracle.conv2d_tbn_session(x, wq, net["inits"]["b"], (1, 1, 1, 1, 1, 1)))
