@@ -215,12 +215,40 @@ def run_ours(args):
     A_d = A_pin.to(dev, non_blocking=True)
     C_slab = torch.empty((n, nc), dtype=torch.float32, device=dev)
     ws, _ = L.gemm_workspace(n, n, mode, dev)
-    gathered = torch.empty((world, n, nc), dtype=torch.float32, device=dev) if world > 1 else None
-    C_full = torch.empty((n, n), dtype=torch.float32, device=dev) if world > 1 else C_slab
+    # N > 1: the epilogue of each rank's GEMM writes its column slab straight into every rank's result
+    # matrix (peer-mapped symmetric memory, plain stores over NVLink) -- compute and all-gather in one kernel;
+    # a tiny NCCL all-reduce closes the step as the cross-GPU barrier.  If symmetric memory cannot be set up,
+    # fall back to one NCCL all-gather of the slabs plus the interleave kernel.
+    gathered, dests, fused, flag = None, None, False, None
+    C_full = C_slab
+    if world > 1:
+        flag = torch.zeros(1, device=dev)
+        if not args.no_fused_gather:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                C_full = symm_mem.empty((n, n), dtype=torch.float32, device=dev)
+                hdl = symm_mem.rendezvous(C_full, dist.group.WORLD)
+                ptrs = [int(p) for p in hdl.buffer_ptrs]
+                order = [(rank + i) % world for i in range(world)]
+                dests = [ptrs[r] + col0 * 4 for r in order]
+                fused = True
+            except Exception as exc:  # noqa: BLE001
+                sys.stderr.write(f"[rank {rank}] symmetric memory unavailable ({exc}); using NCCL all-gather\n")
+        ok = torch.tensor([1.0 if fused else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        fused = bool(ok.item() > 0)
+        if not fused:
+            gathered = torch.empty((world, n, nc), dtype=torch.float32, device=dev)
+            C_full = torch.empty((n, n), dtype=torch.float32, device=dev)
 
     def step():
-        L.gemm_fxb(A_d, words, nc, alpha=alpha, mode=mode, out=C_slab, workspace=ws)
-        if world > 1:
+        if world == 1:
+            L.gemm_fxb(A_d, words, nc, alpha=alpha, mode=mode, out=C_slab, workspace=ws)
+        elif fused:
+            L.gemm_fxb_multi(A_d, words, nc, dests, n, alpha=alpha, mode=mode, workspace=ws)
+            dist.all_reduce(flag)
+        else:
+            L.gemm_fxb(A_d, words, nc, alpha=alpha, mode=mode, out=C_slab, workspace=ws)
             dist.all_gather_into_tensor(gathered.view(world * n, nc), C_slab)
             L.gather_cols_permute(gathered, out=C_full)
 
@@ -255,8 +283,21 @@ def run_ours(args):
     ms_total = float(ms_total.item())
     L.sync()
 
+    # Every rank must hold the same full result: compare a checksum of C across ranks.
+    replicas_agree = None
+    if world > 1:
+        cs = C_full.double().sum().reshape(1)
+        lo, hi = cs.clone(), cs.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_agree = bool((lo == hi).item()) and bool(torch.isfinite(cs).item())
+
     # ---- end to end through the C ABI with host buffers ---------------------------------------
-    C_pin = torch.empty((n, nc), dtype=torch.float32).pin_memory()
+    # Each rank returns its block of result rows (contiguous in the row-major C), so that the host holds
+    # the whole product once.
+    rows0, rows1 = rank * (n // world), (rank + 1) * (n // world)
+    C_out_view = C_full[rows0:rows1] if world > 1 else C_slab
+    C_pin = torch.empty(tuple(C_out_view.shape), dtype=torch.float32).pin_memory()
     e2e_steps = max(1, min(args.steps, 5))
     h = L.h
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -265,7 +306,7 @@ def run_ours(args):
     def e2e_step():
         capi.check(h.tbn_cuda_h2d(C.c_void_p(A_d.data_ptr()), C.c_void_p(A_pin.data_ptr()), a_bytes, stream))
         step()
-        capi.check(h.tbn_cuda_d2h(C.c_void_p(C_pin.data_ptr()), C.c_void_p(C_slab.data_ptr()), c_bytes, stream))
+        capi.check(h.tbn_cuda_d2h(C.c_void_p(C_pin.data_ptr()), C.c_void_p(C_out_view.data_ptr()), c_bytes, stream))
 
     e2e_step()
     barrier()
@@ -297,7 +338,10 @@ def run_ours(args):
             "dtype": f"bf16 x{npass} split of fp32 activations, +-1 weights, fp32 accumulate", "data":
             "synthetic N(0,1), numpy default_rng seeds 0 (A) / 1 (W)",
             "config": {"workload": f"float x binary GEMM M=N=K={n}, per-column scale mean|W|", "mode": args.mode,
-                       "parallelism": "single GPU" if world == 1 else f"weight columns sharded x{world}, one NCCL all-gather of C",
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"weight columns sharded x{world}; " + ("all-gather fused into the GEMM epilogue (peer stores over "
+                           "NVLink) + NCCL barrier" if fused else "one NCCL all-gather of C + interleave kernel")),
+                       "replicas_agree": replicas_agree,
                        "l2": "inputs (1 GiB A per step) larger than the 126 MB L2; no flush needed"},
             "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": a_bytes, "d2h_bytes_per_step": c_bytes,
@@ -343,6 +387,7 @@ def main():
     ap.add_argument("--size", type=int, default=16384)
     ap.add_argument("--mode", default="x2", choices=["x1", "x2", "x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fused-gather", action="store_true", help="N > 1: use NCCL all-gather instead of peer stores")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -50,6 +50,8 @@ SIGNATURES = {
     "tbn_quant_pack_ternary": (_i32, [_vp, _i64, _i64, _i64, _i32, _f32, _f32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "tbn_gemm_workspace_bytes": (_sz, [_i64, _i64, _i32]),
     "tbn_gemm_fxb": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _i32, _u32, _vp, _sz, _vp]),
+    "tbn_gemm_fxb_multi": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _f32, _vp, C.POINTER(_vp), _i32, _i64, _i32, _u32,
+                                  _vp, _sz, _vp]),
     "tbn_gemm_tbn": (_i32, [_vp, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _u32, _vp, _sz, _vp]),
 }
 
@@ -238,6 +240,20 @@ class _Lib:
         check(self.h.tbn_gemm_fxb(_ptr(a), M, K, a.stride(0), _ptr(neg), _ptr(pos), N, _ptr(alpha), scale, _ptr(bias),
                                   _ptr(out), out.stride(0), mode, epilogue, _ptr(workspace), nbytes, _stream()))
         return out
+
+    def gemm_fxb_multi(self, a, neg, N, dest_ptrs, ldc, pos=None, alpha=None, scale=1.0, bias=None,
+                       mode=MODE_TC_BF16X2, epilogue=0, workspace=None):
+        """Column-slab GEMM whose epilogue stores the slab to every address in `dest_ptrs` (ints: device
+        pointers, local and peer-mapped, already offset to the slab's first column; row stride `ldc`)."""
+        self.init()
+        M, K = a.shape
+        if workspace is None:
+            workspace, nbytes = self.gemm_workspace(M, K, mode, a.device)
+        else:
+            nbytes = workspace.numel() * workspace.element_size()
+        arr = (_vp * len(dest_ptrs))(*[int(p) for p in dest_ptrs])
+        check(self.h.tbn_gemm_fxb_multi(_ptr(a), M, K, a.stride(0), _ptr(neg), _ptr(pos), N, _ptr(alpha), scale, _ptr(bias),
+                                        arr, len(dest_ptrs), ldc, mode, epilogue, _ptr(workspace), nbytes, _stream()))
 
     def gemm_tbn(self, a, neg, N, lo=-0.1, hi=0.1, alpha=None, scale=1.0, bias=None, epilogue=0, out=None,
                  workspace=None):

@@ -172,7 +172,8 @@ int32_t launch_split(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_
 // Tensor-core path: split (or ternarise) A into the workspace, then the tcgen05 kernel.
 int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bool ternarise_act, float act_lo,
                          float act_hi, int npass, const uint32_t* d_neg, const uint32_t* d_pos, int64_t N,
-                         const Epilogue& ep, float* d_c, int64_t ldc, void* d_ws, size_t ws_bytes, cudaStream_t st) {
+                         const Epilogue& ep, float* d_c, int64_t ldc, void* d_ws, size_t ws_bytes, cudaStream_t st,
+                         float* const* outs = nullptr, int num_out = 0) {
     const int64_t M_pad = round_up(M, tc::BM), K_pad = round_up(K, 128), N_pad = round_up(N, 8);
     const size_t split_bytes = static_cast<size_t>(npass) * M_pad * K_pad * sizeof(__nv_bfloat16);
     const size_t need = split_bytes + scratch_bytes();
@@ -226,6 +227,8 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.c_vec_ok = (ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(d_c) % 16 == 0);
     set_segments(p, npass);
     p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(d_ws) + split_bytes);
+    p.num_out = num_out;
+    for (int i = 0; i < num_out; ++i) p.out_list[i] = outs[i];
     const bool ternary_w = d_pos != nullptr;
     if (npass == 1)
         return ternary_w ? dispatch_bn<1, true, false, false>(bn, maps, p, st)
@@ -297,6 +300,25 @@ int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const 
         return gemm_simt(d_a, M, K, lda, false, 0.f, 0.f, d_neg, d_pos, N, ep, d_c, ldc, as_stream(stream));
     return gemm_tensor_core(d_a, M, K, lda, false, 0.f, 0.f, npass_of(mode), d_neg, d_pos, N, ep, d_c, ldc, d_workspace,
                             workspace_bytes, as_stream(stream));
+}
+
+int32_t tbn_gemm_fxb_multi(const float* d_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,
+                           const uint32_t* d_pos, int64_t N, const float* d_alpha, float scale, const float* d_bias,
+                           float* const* d_c_list, int32_t num_out, int64_t ldc, int32_t mode, uint32_t epilogue,
+                           void* d_workspace, size_t workspace_bytes, void* stream) {
+    TBN_REQUIRE(d_c_list != nullptr && num_out >= 1 && num_out <= tc::kMaxOutputs, TBN_INVALID_ARGUMENT,
+                "tbn_gemm_fxb_multi: between 1 and 8 destinations are required");
+    for (int i = 0; i < num_out; ++i)
+        TBN_REQUIRE(d_c_list[i] != nullptr && reinterpret_cast<uintptr_t>(d_c_list[i]) % 16 == 0, TBN_INVALID_ARGUMENT,
+                    "tbn_gemm_fxb_multi: destinations must be non-null and 16-byte aligned");
+    TBN_REQUIRE(N % 4 == 0 && ldc % 4 == 0, TBN_INVALID_SHAPE, "tbn_gemm_fxb_multi: N and ldc must be multiples of 4");
+    int32_t rc = check_gemm_args(d_a, M, K, lda, d_neg, N, d_c_list[0], ldc);
+    if (rc) return rc;
+    if (mode == TBN_MODE_AUTO) mode = TBN_MODE_TC_BF16X2;
+    TBN_REQUIRE(npass_of(mode) != 0, TBN_INVALID_ARGUMENT, "tbn_gemm_fxb_multi: a tensor-core mode is required");
+    const Epilogue ep{d_alpha, d_bias, nullptr, scale, epilogue & ~TBN_EPI_ADD_RESIDUAL};
+    return gemm_tensor_core(d_a, M, K, lda, false, 0.f, 0.f, npass_of(mode), d_neg, d_pos, N, ep, d_c_list[0], ldc,
+                            d_workspace, workspace_bytes, as_stream(stream), d_c_list, num_out);
 }
 
 int32_t tbn_gemm_tbn(const float* d_a, int64_t M, int64_t K, int64_t lda, float lo, float hi, const uint32_t* d_neg,

@@ -87,6 +87,8 @@ constexpr int kThreads = 64 + kBuildThreads + kEpilogueThreads;
 constexpr int kGroupM = 8;      // rasterisation: 8 m-tiles share a sweep over n for L2 reuse
 constexpr int kWordStages = 2;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
 constexpr int kAuxBarrierBytes = 1024;
+constexpr int kMaxOutputs = 8;           // destinations of the multi-destination epilogue (GPUs of one box)
+constexpr int kStageOutBytes = 4 * 2048;  // per epilogue warp: 32 rows x 16 fp32 transposition buffer
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 // Accumulation steps (k elements x passes) after which a fresh accumulator is started.
 constexpr int kMaxAccumSteps = 4096;
@@ -96,8 +98,8 @@ struct Cfg {
     static constexpr int B_TILE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = B_TILE_BYTES + NPASS * A_TILE_BYTES;
     static constexpr int WORD_TILE_BYTES = BN * 16 * (TERNARY ? 2 : 1);  // 4 words per column and plane
-    // barriers + alpha/bias staging (x2 buffers) + packed-word ring
-    static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4 + kWordStages * WORD_TILE_BYTES;
+    // barriers + alpha/bias staging (x2 buffers) + packed-word ring + epilogue transposition buffers
+    static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4 + kWordStages * WORD_TILE_BYTES + kStageOutBytes;
     static constexpr int RAW_STAGES = (kSmemLimit - 1024 - AUX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = RAW_STAGES > 6 ? 6 : RAW_STAGES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;  // + alignment slack
@@ -134,6 +136,11 @@ struct Params {
     int num_seg;           // K segments per tile, each with a fresh accumulator
     int kb_per_seg;        // k-blocks per segment (the last one may be shorter)
     float4* scratch;       // [gridDim.x][BN/4][128] partial sums, used when num_seg > 1
+    // Multi-destination epilogue (column-sharded multi-GPU GEMM): when num_out > 0 the finished tile is
+    // written, with full-line stores, to every out_list[i] (same row stride ldc) -- the local result
+    // buffer and the peers' buffers mapped into this GPU's address space -- instead of p.c.
+    int num_out;
+    float* out_list[kMaxOutputs];
     ConvGeom conv;
 };
 
@@ -172,6 +179,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     float* alpha_s = reinterpret_cast<float*>(aux_ptr + kAuxBarrierBytes);  // [2][BN]
     float* bias_s = alpha_s + 2 * BN;                                       // [2][BN]
     const uint32_t word_ring = aux + kAuxBarrierBytes + 4 * BN * 4;         // [kWordStages][planes][BN][4 words]
+    float* stage_out = reinterpret_cast<float*>(aux_ptr + kAuxBarrierBytes + 4 * BN * 4 + kWordStages * C::WORD_TILE_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -483,6 +491,42 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         for (int j4 = 0; j4 < 8; ++j4)
                             __stcg(scratch + (c * 8 + j4) * kEpilogueThreads,
                                    make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]));
+                    } else if (p.num_out > 0) {
+                        const int64_t nc = n0 + c * 32;
+                        const float* as = alpha_s + sbuf * BN + c * 32;
+                        const float* bs = bias_s + sbuf * BN + c * 32;
+                        float* tbuf = stage_out + (warp & 3) * (kStageOutBytes / 16);  // 512 floats per warp
+                        const int64_t m_warp = static_cast<int64_t>(tm) * BM + quarter * 32;
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            // lane = row: write this row's 16 columns as 4 float4 at swizzled positions.
+#pragma unroll
+                            for (int j4 = 0; j4 < 4; ++j4) {
+                                const int j = half * 16 + j4 * 4;
+                                float4 o;
+                                o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags, 0.0f);
+                                o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags, 0.0f);
+                                o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags, 0.0f);
+                                o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags, 0.0f);
+                                *reinterpret_cast<float4*>(tbuf + lane * 16 + ((j4 ^ (lane & 3)) << 2)) = o;
+                            }
+                            __syncwarp();
+                            // 4 lanes per row (16 floats = 64 bytes), 8 rows per instruction.
+#pragma unroll
+                            for (int rr = 0; rr < 4; ++rr) {
+                                const int row = rr * 8 + (lane >> 2);
+                                const int q4 = lane & 3;
+                                const float4 o = *reinterpret_cast<const float4*>(tbuf + row * 16 + ((q4 ^ (row & 3)) << 2));
+                                const int64_t mm = m_warp + row;
+                                const int64_t col = nc + half * 16 + q4 * 4;
+                                if (mm < p.M && col + 4 <= p.N) {
+                                    const int64_t idx = mm * p.ldc + col;
+#pragma unroll 1
+                                    for (int d = 0; d < p.num_out; ++d) *reinterpret_cast<float4*>(p.out_list[d] + idx) = o;
+                                }
+                            }
+                            __syncwarp();
+                        }
                     } else if (m < p.M) {
                         const int64_t nc = n0 + c * 32;
                         const float* as = alpha_s + sbuf * BN + c * 32;

@@ -180,6 +180,19 @@ int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const 
                      const float* d_bias, float* d_c, int64_t ldc, int32_t mode, uint32_t epilogue,
                      void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* tbn_gemm_fxb whose epilogue writes the finished C tile to SEVERAL destinations with the same row
+ * stride: d_c_list[0..num_out) is a HOST array of device pointers (1..8), e.g. this GPU's result buffer
+ * and the peers' buffers mapped into this GPU's address space, each already offset to the column slab
+ * this call produces.  This is the compute + all-gather step of the column-sharded multi-GPU GEMM done
+ * in one kernel: the tile is transposed through shared memory and leaves as full 64-byte row segments
+ * (plain st.global; no TMA multicast).  The caller synchronises the GPUs before anyone reads the result.
+ * Tensor-core modes only; N and ldc multiples of 4.  (New: the reference is single-device.) */
+int32_t tbn_gemm_fxb_multi(const float* d_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,
+                           const uint32_t* d_pos, int64_t N, const float* d_alpha, float scale,
+                           const float* d_bias, float* const* d_c_list, int32_t num_out, int64_t ldc,
+                           int32_t mode, uint32_t epilogue, void* d_workspace, size_t workspace_bytes,
+                           void* stream);
+
 /* "TBN mode": activations ternarised at (lo, hi) x binary weights, exact integer accumulation,
  * C = float(acc) * scale (then alpha/bias per the epilogue flags).  Bit-equal to
  * tbn::qlinear_matmul_binary (quantized_gemm_neon.cpp:165-243, 380-430) and to the GEMM inside

@@ -168,6 +168,31 @@ def test_repeated_runs_are_bitwise_identical(tbn, mode):
         assert float((first.double() - exact).abs().max()) < 1e-2
 
 
+def test_multi_destination_epilogue(tbn):
+    """tbn_gemm_fxb_multi writes the column slab into several buffers (the multi-GPU epilogue); on one GPU
+    the destinations are two local matrices.  Every copy equals the single-destination result bit for bit and
+    nothing outside the slab is touched."""
+    import torch
+    M, K, Nc, ldc = 300, 640, 256, 1024
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A = torch.randn((M, K), generator=g, device="cuda")
+    W = torch.randn((K, Nc), generator=g, device="cuda")
+    bias = torch.randn(Nc, generator=g, device="cuda")
+    words, alpha = tbn.lib.quant_pack_binary(W)
+    expect = tbn.lib.gemm_fxb(A, words, Nc, alpha=alpha, bias=bias, mode=tbn.MODE_TC_BF16X2)
+    c0 = torch.full((M, ldc), -3.0, device="cuda")
+    c1 = torch.full((M, ldc), -3.0, device="cuda")
+    off = 512  # this "rank" owns columns [512, 768)
+    dests = [c0.data_ptr() + off * 4, c1.data_ptr() + off * 4]
+    tbn.lib.gemm_fxb_multi(A, words, Nc, dests, ldc, alpha=alpha, bias=bias)
+    tbn.lib.sync()
+    for c in (c0, c1):
+        assert torch.equal(c[:, off:off + Nc], expect)
+        assert float(c[:, :off].min()) == -3.0 and float(c[:, off + Nc:].max()) == -3.0
+    with pytest.raises(tbn.TbnError):
+        tbn.lib.gemm_fxb_multi(A, words, Nc, [], ldc)
+
+
 def test_argument_errors(tbn):
     import torch
     a = torch.zeros((4, 8), device="cuda")
