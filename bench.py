@@ -303,7 +303,15 @@ def run_ours(args):
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     a_bytes, c_bytes = A_pin.numel() * 4, C_pin.numel() * 4
 
+    host_ws = None
+    if world == 1:
+        host_ws = torch.empty(h.tbn_gemm_fxb_host_workspace_bytes(n, n, nc, mode), dtype=torch.uint8, device=dev)
+
     def e2e_step():
+        if world == 1:
+            # One C-ABI call on host buffers: chunked upload / multiply / download, overlapped.
+            L.gemm_fxb_host(A_pin, words, nc, C_pin, alpha=alpha, mode=mode, workspace=host_ws)
+            return
         capi.check(h.tbn_cuda_h2d(C.c_void_p(A_d.data_ptr()), C.c_void_p(A_pin.data_ptr()), a_bytes, stream))
         step()
         capi.check(h.tbn_cuda_d2h(C.c_void_p(C_pin.data_ptr()), C.c_void_p(C_out_view.data_ptr()), c_bytes, stream))

@@ -52,6 +52,8 @@ SIGNATURES = {
     "tbn_gemm_fxb": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _i32, _u32, _vp, _sz, _vp]),
     "tbn_gemm_fxb_multi": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _f32, _vp, C.POINTER(_vp), _i32, _i64, _i32, _u32,
                                   _vp, _sz, _vp]),
+    "tbn_gemm_fxb_host_workspace_bytes": (_sz, [_i64, _i64, _i64, _i32]),
+    "tbn_gemm_fxb_host": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _i32, _u32, _vp, _sz, _vp]),
     "tbn_gemm_tbn": (_i32, [_vp, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _vp, _f32, _vp, _vp, _i64, _u32, _vp, _sz, _vp]),
 }
 
@@ -254,6 +256,21 @@ class _Lib:
         arr = (_vp * len(dest_ptrs))(*[int(p) for p in dest_ptrs])
         check(self.h.tbn_gemm_fxb_multi(_ptr(a), M, K, a.stride(0), _ptr(neg), _ptr(pos), N, _ptr(alpha), scale, _ptr(bias),
                                         arr, len(dest_ptrs), ldc, mode, epilogue, _ptr(workspace), nbytes, _stream()))
+
+    def gemm_fxb_host(self, a_host, neg, N, out_host, pos=None, alpha=None, scale=1.0, bias=None, mode=MODE_TC_BF16X2,
+                      epilogue=0, workspace=None, device=None):
+        """Host tensors in and out (torch CPU tensors, ideally pinned); weights on the device.  Asynchronous:
+        synchronise the current stream before reading `out_host`."""
+        import torch
+        self.init()
+        M, K = a_host.shape
+        nbytes = self.h.tbn_gemm_fxb_host_workspace_bytes(M, K, N, mode)
+        if workspace is None:
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=device or neg.device)
+        check(self.h.tbn_gemm_fxb_host(_ptr(a_host), M, K, a_host.stride(0), _ptr(neg), _ptr(pos), N, _ptr(alpha), scale,
+                                       _ptr(bias), _ptr(out_host), out_host.stride(0), mode, epilogue, _ptr(workspace),
+                                       workspace.numel(), _stream()))
+        return out_host
 
     def gemm_tbn(self, a, neg, N, lo=-0.1, hi=0.1, alpha=None, scale=1.0, bias=None, epilogue=0, out=None,
                  workspace=None):

@@ -193,6 +193,19 @@ int32_t tbn_gemm_fxb_multi(const float* d_a, int64_t M, int64_t K, int64_t lda, 
                            int32_t mode, uint32_t epilogue, void* d_workspace, size_t workspace_bytes,
                            void* stream);
 
+/* tbn_gemm_fxb for callers whose activations and result live in HOST memory, as with the reference's
+ * operators (tbn::qlinear_matmul_binary takes and returns host tensors,
+ * tbn-runtime/include/tbn/operators/quantized_gemm.hpp:48-57).  h_a [M,K] and h_c [M,N] are host pointers
+ * (page-locked memory gives full PCIe speed; pageable memory works, slower); the packed weights, alpha and
+ * bias stay on the device.  Rows are processed in chunks so that upload, multiply and download overlap on
+ * three internal streams.  All of it is ordered after the work already queued on `stream`, and `stream`
+ * waits for the last download: synchronise `stream` before reading h_c. */
+size_t tbn_gemm_fxb_host_workspace_bytes(int64_t M, int64_t K, int64_t N, int32_t mode);
+int32_t tbn_gemm_fxb_host(const float* h_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,
+                          const uint32_t* d_pos, int64_t N, const float* d_alpha, float scale,
+                          const float* d_bias, float* h_c, int64_t ldc, int32_t mode, uint32_t epilogue,
+                          void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* "TBN mode": activations ternarised at (lo, hi) x binary weights, exact integer accumulation,
  * C = float(acc) * scale (then alpha/bias per the epilogue flags).  Bit-equal to
  * tbn::qlinear_matmul_binary (quantized_gemm_neon.cpp:165-243, 380-430) and to the GEMM inside

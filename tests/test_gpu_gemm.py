@@ -193,6 +193,28 @@ def test_multi_destination_epilogue(tbn):
         tbn.lib.gemm_fxb_multi(A, words, Nc, [], ldc)
 
 
+@pytest.mark.parametrize("M,K,N", [(100, 200, 64), (1500, 384, 520), (4096, 1024, 1024)])
+def test_host_buffer_gemm_matches_device_gemm(tbn, M, K, N):
+    """tbn_gemm_fxb_host (chunked upload / multiply / download) == tbn_gemm_fxb on resident data, bit for bit,
+    with pinned and with pageable host memory, and twice in a row (slot reuse)."""
+    import torch
+    g = torch.Generator().manual_seed(8)
+    A = torch.randn((M, K), generator=g)
+    W = torch.randn((K, N), generator=g).cuda()
+    bias = torch.randn(N, generator=g).cuda()
+    words, alpha = tbn.lib.quant_pack_binary(W)
+    expect = tbn.lib.gemm_fxb(A.cuda(), words, N, alpha=alpha, bias=bias, mode=tbn.MODE_TC_BF16X2).cpu()
+    for pinned in (True, False):
+        a_h = A.pin_memory() if pinned else A
+        out = torch.full((M, N), float("nan"))
+        out = out.pin_memory() if pinned else out
+        for _ in range(2):
+            tbn.lib.gemm_fxb_host(a_h, words, N, out, alpha=alpha, bias=bias)
+            tbn.lib.sync()
+            assert torch.equal(out, expect)
+            out.fill_(float("nan"))
+
+
 def test_argument_errors(tbn):
     import torch
     a = torch.zeros((4, 8), device="cuda")
