@@ -30,6 +30,11 @@ SIGNATURES = {
     "tbn_cuda_launch_count": (_i64, []),
     "tbn_cuda_profile_enable": (_i32, [_i32]),
     "tbn_cuda_profile_read": (_i32, [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(_i64)]),
+    "tbn_dense_pack_bytes": (_sz, [_i64, _i64]),
+    "tbn_dense_pack": (_i32, [_vp, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "tbn_gemm_f32": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _f32, _vp, _vp, _i64, _u32, _vp, _sz, _vp]),
+    "tbn_conv2d_f32": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp,
+                              _vp, _u32, _vp, _sz, _vp]),
     "tbn_conv2d_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "tbn_conv2d_fxb": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
                               _vp, _f32, _vp, _vp, _vp, _i32, _u32, _vp, _sz, _vp]),
@@ -341,6 +346,50 @@ class _Lib:
         check(self.h.tbn_conv2d_tbn(_ptr(x), N, Cc, H, W, lo, hi, _ptr(neg), M_out, kh, kw, *[int(v) for v in p],
                                     _ptr(alpha), scale, _ptr(bias), _ptr(out), epilogue, _ptr(workspace), nbytes,
                                     _stream()))
+        return out
+
+    # ---- float weights ----------------------------------------------------------------------------
+    def dense_pack(self, w, layout=LAYOUT_KN):
+        """fp32 weights [K,N] (KN) or [N,K] (NK) -> split bf16 buffer (uint8 tensor)."""
+        import torch
+        self.init()
+        assert w.dim() == 2 and w.dtype == torch.float32 and w.stride(1) == 1
+        K, N = (w.shape if layout == LAYOUT_KN else (w.shape[1], w.shape[0]))
+        buf = torch.empty(self.h.tbn_dense_pack_bytes(K, N), dtype=torch.uint8, device=w.device)
+        check(self.h.tbn_dense_pack(_ptr(w), K, N, w.stride(0), layout, _ptr(buf), _stream()))
+        return buf
+
+    def gemm_f32(self, a, packed_w, N, alpha=1.0, bias=None, epilogue=0, out=None, workspace=None):
+        import torch
+        self.init()
+        M, K = a.shape
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        if workspace is None:
+            workspace, nbytes = self.gemm_workspace(M, K, MODE_TC_BF16X2, a.device)
+        else:
+            nbytes = workspace.numel()
+        check(self.h.tbn_gemm_f32(_ptr(a), M, K, a.stride(0), _ptr(packed_w), N, alpha, _ptr(bias), _ptr(out), out.stride(0),
+                                  epilogue, _ptr(workspace), nbytes, _stream()))
+        return out
+
+    def conv2d_f32(self, x, packed_w, wshape, p, bias=None, residual=None, epilogue=0, out=None, workspace=None):
+        import torch
+        self.init()
+        x = x.contiguous()
+        N, Cc, H, W = x.shape
+        M_out, _, kh, kw = wshape
+        oh, ow = self.conv_out_hw(H, W, kh, kw, p)
+        if out is None:
+            out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
+        if workspace is None:
+            workspace, nbytes = self.conv_workspace(Cc, kh, kw, x.device)
+        else:
+            nbytes = workspace.numel()
+        if residual is not None:
+            epilogue |= EPI_ADD_RESIDUAL
+        check(self.h.tbn_conv2d_f32(_ptr(x), N, Cc, H, W, _ptr(packed_w), M_out, kh, kw, *[int(v) for v in p], _ptr(bias),
+                                    _ptr(residual), _ptr(out), epilogue, _ptr(workspace), nbytes, _stream()))
         return out
 
     def relu(self, x):

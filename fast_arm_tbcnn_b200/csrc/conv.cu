@@ -28,6 +28,7 @@ __global__ void conv_tap_table_kernel(int2* __restrict__ table, int K, int K_pad
 }
 
 struct ConvArgs {
+    const void* dense_w = nullptr;  // split dense weights (float filters) instead of packed planes
     const float* x;
     int64_t N, C, H, W;
     const uint32_t* neg;
@@ -55,7 +56,7 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     TBN_REQUIRE(a.H + 2 * a.ph - a.dh * (a.kh - 1) - 1 >= 0 && a.W + 2 * a.pw - a.dw * (a.kw - 1) - 1 >= 0 && OH > 0 &&
                     OW > 0,
                 TBN_INVALID_SHAPE, "conv2d: invalid output dimensions");
-    TBN_REQUIRE(a.x && a.neg && a.y, TBN_INVALID_ARGUMENT, "conv2d: null pointer");
+    TBN_REQUIRE(a.x && (a.neg || a.dense_w) && a.y, TBN_INVALID_ARGUMENT, "conv2d: null pointer");
     TBN_REQUIRE(a.H < 32000 && a.W < 32000 && a.dh * (a.kh - 1) < 32000 && a.dw * (a.kw - 1) < 32000, TBN_INVALID_SHAPE,
                 "conv2d: image or dilated kernel too large");
     const int64_t K = a.C * a.kh * a.kw, M = a.N * OH * OW, N = a.M_out;
@@ -67,8 +68,9 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                 "conv2d: workspace too small (see tbn_conv2d_workspace_bytes)");
     TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.ws) % 128 == 0, TBN_INVALID_ARGUMENT,
                 "conv2d: workspace must be 128-byte aligned");
-    TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.neg) % 16 == 0 && (!a.pos || reinterpret_cast<uintptr_t>(a.pos) % 16 == 0),
-                TBN_INVALID_ARGUMENT, "conv2d: packed weight planes must be 16-byte aligned");
+    TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.neg) % 16 == 0 && (!a.pos || reinterpret_cast<uintptr_t>(a.pos) % 16 == 0) &&
+                    reinterpret_cast<uintptr_t>(a.dense_w) % 16 == 0,
+                TBN_INVALID_ARGUMENT, "conv2d: weights must be 16-byte aligned");
     TBN_REQUIRE(!(a.ep.flags & TBN_EPI_ADD_RESIDUAL) || a.ep.residual, TBN_INVALID_ARGUMENT,
                 "conv2d: TBN_EPI_ADD_RESIDUAL needs a residual tensor");
     EncodeTiledFn encode = encode_tiled_fn();
@@ -83,10 +85,16 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
 
     const int bn = pick_bn(N);
     TensorMaps maps;
-    rc = make_word_map(encode, a.neg, K_pad / 32, N_pad, bn, &maps.neg);
-    if (rc) return rc;
-    rc = make_word_map(encode, a.pos ? a.pos : a.neg, K_pad / 32, N_pad, bn, &maps.pos);
-    if (rc) return rc;
+    if (a.dense_w) {
+        rc = make_split_map(encode, a.dense_w, K_pad, N_pad, 2, bn, &maps.neg);
+        if (rc) return rc;
+        maps.pos = maps.neg;
+    } else {
+        rc = make_word_map(encode, a.neg, K_pad / 32, N_pad, bn, &maps.neg);
+        if (rc) return rc;
+        rc = make_word_map(encode, a.pos ? a.pos : a.neg, K_pad / 32, N_pad, bn, &maps.pos);
+        if (rc) return rc;
+    }
     maps.a = maps.neg;  // unused in CONV mode
 
     tc::Params p = {};
@@ -117,6 +125,10 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.conv.pw = a.pw;
     p.conv.act_lo = lo;
     p.conv.act_hi = hi;
+    if (a.dense_w) {
+        set_segments(p, 3);
+        return dispatch_bn<2, false, true, false, true>(bn, maps, p, a.st);
+    }
     const bool ternary_w = a.pos != nullptr;
     if (tern_act) return dispatch_bn<1, false, true, true>(bn, maps, p, a.st);
     if (npass == 1)
@@ -145,7 +157,7 @@ int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                        size_t workspace_bytes, void* stream) {
     TBN_REQUIRE(mode == TBN_MODE_AUTO || mode == TBN_MODE_TC_BF16X1 || mode == TBN_MODE_TC_BF16X2, TBN_NOT_IMPLEMENTED,
                 "tbn_conv2d_fxb: modes are AUTO (= two bf16 terms), TC_BF16X1 and TC_BF16X2");
-    const ConvArgs a{d_x, N, C, H, W, d_neg, d_pos, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+    const ConvArgs a{nullptr, d_x, N, C, H, W, d_neg, d_pos, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
                      Epilogue{d_alpha, d_bias, d_residual, scale, epilogue}, d_y, d_workspace, workspace_bytes,
                      as_stream(stream)};
     return conv_common(a, mode == TBN_MODE_TC_BF16X1 ? 1 : 2, false, 0.f, 0.f);
@@ -155,10 +167,21 @@ int32_t tbn_conv2d_tbn(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                        const uint32_t* d_neg, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph,
                        int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale, const float* d_bias,
                        float* d_y, uint32_t epilogue, void* d_workspace, size_t workspace_bytes, void* stream) {
-    const ConvArgs a{d_x, N, C, H, W, d_neg, nullptr, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+    const ConvArgs a{nullptr, d_x, N, C, H, W, d_neg, nullptr, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
                      Epilogue{d_alpha, d_bias, nullptr, scale, epilogue & ~TBN_EPI_ADD_RESIDUAL}, d_y, d_workspace,
                      workspace_bytes, as_stream(stream)};
     return conv_common(a, 1, true, lo, hi);
+}
+
+int32_t tbn_conv2d_f32(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, const void* d_packed_w, int64_t M_out,
+                       int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw,
+                       const float* d_bias, const float* d_residual, float* d_y, uint32_t epilogue, void* d_workspace,
+                       size_t workspace_bytes, void* stream) {
+    TBN_REQUIRE(d_packed_w != nullptr, TBN_INVALID_ARGUMENT, "tbn_conv2d_f32: null weights");
+    const ConvArgs a{d_packed_w, d_x, N, C, H, W, nullptr, nullptr, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+                     Epilogue{nullptr, d_bias, d_residual, 1.0f, epilogue}, d_y, d_workspace, workspace_bytes,
+                     as_stream(stream)};
+    return conv_common(a, 2, false, 0.f, 0.f);
 }
 
 }  // extern "C"

@@ -79,6 +79,36 @@ __global__ void __launch_bounds__(256) split_activations_kernel(const float* __r
     }
 }
 
+// Dense weights stored [K, N] (Gemm B, transB = 0): two bf16 terms of W^T, i.e. out[q][n][k], so that the
+// kernel finds K-major rows per output column.  Lanes run along n (coalesced reads); one thread handles
+// 8 consecutive k of one column and writes one 16-byte vector per term.  One-time weight preparation.
+__global__ void __launch_bounds__(256) split_dense_kn_kernel(const float* __restrict__ w, int64_t K, int64_t N, int64_t ldw,
+                                                             int64_t N_pad, int64_t K_pad, __nv_bfloat16* __restrict__ out) {
+    const int64_t k8_total = K_pad / 8;
+    const int64_t total = N_pad * k8_total;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int64_t n = idx % N_pad;
+        const int64_t k = (idx / N_pad) * 8;
+        uint32_t packed[2][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float v = (n < N && k + i < K) ? __ldg(w + (k + i) * ldw + n) : 0.0f;
+            uint16_t term[2];
+            split_terms<2, false>(v, 0.f, 0.f, term);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                if (i & 1) packed[q][i >> 1] |= static_cast<uint32_t>(term[q]) << 16;
+                else packed[q][i >> 1] = term[q];
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+            *reinterpret_cast<uint4*>(out + (static_cast<int64_t>(q) * N_pad + n) * K_pad + k) =
+                make_uint4(packed[q][0], packed[q][1], packed[q][2], packed[q][3]);
+    }
+}
+
 // =====================================================================================
 // CUDA-core kernel: add / subtract by sign, k ascending
 // =====================================================================================
@@ -173,7 +203,7 @@ int32_t launch_split(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_
 int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bool ternarise_act, float act_lo,
                          float act_hi, int npass, const uint32_t* d_neg, const uint32_t* d_pos, int64_t N,
                          const Epilogue& ep, float* d_c, int64_t ldc, void* d_ws, size_t ws_bytes, cudaStream_t st,
-                         float* const* outs = nullptr, int num_out = 0) {
+                         float* const* outs = nullptr, int num_out = 0, const void* dense_w = nullptr) {
     const int64_t M_pad = round_up(M, tc::BM), K_pad = round_up(K, 128), N_pad = round_up(N, 8);
     const size_t split_bytes = static_cast<size_t>(npass) * M_pad * K_pad * sizeof(__nv_bfloat16);
     const size_t need = split_bytes + scratch_bytes();
@@ -208,12 +238,20 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
                 "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(cr)));
 
     const int bn = pick_bn(N);
-    TBN_REQUIRE(reinterpret_cast<uintptr_t>(d_neg) % 16 == 0 && (!d_pos || reinterpret_cast<uintptr_t>(d_pos) % 16 == 0),
-                TBN_INVALID_ARGUMENT, "gemm: packed weight planes must be 16-byte aligned");
-    rc = make_word_map(encode, d_neg, K_pad / 32, N_pad, bn, &maps.neg);
-    if (rc) return rc;
-    rc = make_word_map(encode, d_pos ? d_pos : d_neg, K_pad / 32, N_pad, bn, &maps.pos);
-    if (rc) return rc;
+    if (dense_w) {
+        TBN_REQUIRE(reinterpret_cast<uintptr_t>(dense_w) % 16 == 0, TBN_INVALID_ARGUMENT,
+                    "gemm: split dense weights must be 16-byte aligned");
+        rc = make_split_map(encode, dense_w, K_pad, N_pad, 2, bn, &maps.neg);
+        if (rc) return rc;
+        maps.pos = maps.neg;
+    } else {
+        TBN_REQUIRE(reinterpret_cast<uintptr_t>(d_neg) % 16 == 0 && (!d_pos || reinterpret_cast<uintptr_t>(d_pos) % 16 == 0),
+                    TBN_INVALID_ARGUMENT, "gemm: packed weight planes must be 16-byte aligned");
+        rc = make_word_map(encode, d_neg, K_pad / 32, N_pad, bn, &maps.neg);
+        if (rc) return rc;
+        rc = make_word_map(encode, d_pos ? d_pos : d_neg, K_pad / 32, N_pad, bn, &maps.pos);
+        if (rc) return rc;
+    }
     tc::Params p = {};
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
@@ -229,6 +267,11 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(d_ws) + split_bytes);
     p.num_out = num_out;
     for (int i = 0; i < num_out; ++i) p.out_list[i] = outs[i];
+    if (dense_w) {
+        p.num_kb = static_cast<int>(K_pad / tc::BK);
+        set_segments(p, 3);  // three MMA passes per k-block
+        return dispatch_bn<2, false, false, false, true>(bn, maps, p, st);
+    }
     const bool ternary_w = d_pos != nullptr;
     if (npass == 1)
         return ternary_w ? dispatch_bn<1, true, false, false>(bn, maps, p, st)
@@ -300,6 +343,38 @@ int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const 
         return gemm_simt(d_a, M, K, lda, false, 0.f, 0.f, d_neg, d_pos, N, ep, d_c, ldc, as_stream(stream));
     return gemm_tensor_core(d_a, M, K, lda, false, 0.f, 0.f, npass_of(mode), d_neg, d_pos, N, ep, d_c, ldc, d_workspace,
                             workspace_bytes, as_stream(stream));
+}
+
+size_t tbn_dense_pack_bytes(int64_t K, int64_t N) {
+    if (K <= 0 || N <= 0) return 0;
+    return static_cast<size_t>(2) * round_up(N, 8) * round_up(K, 128) * sizeof(__nv_bfloat16);
+}
+
+int32_t tbn_dense_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout, void* d_packed, void* stream) {
+    TBN_REQUIRE(K > 0 && N > 0, TBN_INVALID_SHAPE, "tbn_dense_pack: K and N must be positive");
+    TBN_REQUIRE(d_w && d_packed && reinterpret_cast<uintptr_t>(d_packed) % 16 == 0, TBN_INVALID_ARGUMENT,
+                "tbn_dense_pack: null or misaligned pointer");
+    TBN_REQUIRE(layout == TBN_LAYOUT_KN || layout == TBN_LAYOUT_NK, TBN_INVALID_ARGUMENT, "tbn_dense_pack: bad layout");
+    TBN_REQUIRE(ldw >= (layout == TBN_LAYOUT_KN ? N : K), TBN_INVALID_ARGUMENT, "tbn_dense_pack: ldw too small");
+    const int64_t K_pad = round_up(K, 128), N_pad = round_up(N, 8);
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(d_packed);
+    if (layout == TBN_LAYOUT_NK)  // rows of W are the output columns: the activation split does the job
+        return launch_split<2, false>(d_w, N, K, ldw, N_pad, K_pad, out, 0.f, 0.f, as_stream(stream));
+    const int64_t total = N_pad * (K_pad / 8);
+    const int grid = static_cast<int>(std::max<int64_t>(1, std::min((total + 255) / 256, static_cast<int64_t>(sm_count()) * 16)));
+    split_dense_kn_kernel<<<grid, 256, 0, as_stream(stream)>>>(d_w, K, N, ldw, N_pad, K_pad, out);
+    return launched("split_dense_kn_kernel");
+}
+
+int32_t tbn_gemm_f32(const float* d_a, int64_t M, int64_t K, int64_t lda, const void* d_packed_w, int64_t N, float alpha,
+                     const float* d_bias, float* d_c, int64_t ldc, uint32_t epilogue, void* d_workspace,
+                     size_t workspace_bytes, void* stream) {
+    TBN_REQUIRE(d_packed_w != nullptr, TBN_INVALID_ARGUMENT, "tbn_gemm_f32: null weights");
+    int32_t rc = check_gemm_args(d_a, M, K, lda, reinterpret_cast<const uint32_t*>(d_packed_w), N, d_c, ldc);
+    if (rc) return rc;
+    const Epilogue ep{nullptr, d_bias, nullptr, alpha, epilogue & ~TBN_EPI_ADD_RESIDUAL};
+    return gemm_tensor_core(d_a, M, K, lda, false, 0.f, 0.f, 2, nullptr, nullptr, N, ep, d_c, ldc, d_workspace,
+                            workspace_bytes, as_stream(stream), nullptr, 0, d_packed_w);
 }
 
 int32_t tbn_gemm_fxb_multi(const float* d_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,

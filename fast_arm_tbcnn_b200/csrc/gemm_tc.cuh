@@ -18,6 +18,10 @@
 // accumulator, and the epilogue adds the segments in fp32 (round to nearest) through a per-CTA scratch
 // tile that stays resident in L2.
 //
+// DENSE mode (float weights: the float x float Gemm / Conv of the CNN graphs): the weight operand is not
+// unpacked from bits but arrives by TMA as two pre-split bf16 terms, and the MMA issuer forms
+// hi*hi + hi*lo + lo*hi.
+//
 // Every wait is bounded and reports through the library's device error word.
 #pragma once
 
@@ -93,10 +97,12 @@ constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 // Accumulation steps (k elements x passes) after which a fresh accumulator is started.
 constexpr int kMaxAccumSteps = 4096;
 
-template <int BN, int NPASS, bool TERNARY>
+template <int BN, int NPASS, bool TERNARY, bool DENSE = false>
 struct Cfg {
     static constexpr int B_TILE_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = B_TILE_BYTES + NPASS * A_TILE_BYTES;
+    static constexpr int B_TERMS = DENSE ? 2 : 1;  // dense weights: hi and lo bf16 terms
+    static constexpr int B_BYTES = B_TERMS * B_TILE_BYTES;
+    static constexpr int STAGE_BYTES = B_BYTES + NPASS * A_TILE_BYTES;
     static constexpr int WORD_TILE_BYTES = BN * 16 * (TERNARY ? 2 : 1);  // 4 words per column and plane
     // barriers + alpha/bias staging (x2 buffers) + packed-word ring + epilogue transposition buffers
     static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4 + kWordStages * WORD_TILE_BYTES + kStageOutBytes;
@@ -154,12 +160,18 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gm;
 }
 
-template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT>
+// tmap_a: split activations (GEMM mode).  tmap_neg / tmap_pos: packed word planes; in DENSE mode tmap_neg is
+// the map of the split weights [2][N_pad][K_pad] instead.
+template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT, bool DENSE>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_neg,
                                                               const __grid_constant__ CUtensorMap tmap_pos,
                                                               const Params p) {
-    using C = Cfg<BN, NPASS, TERNARY>;
+    using C = Cfg<BN, NPASS, TERNARY, DENSE>;
+    static_assert(!DENSE || (NPASS == 2 && !TERNARY && !TERN_ACT), "dense weights use the two-term split on both sides");
+    // Which operands arrive by TMA (signalled on full_a) and which are built by the build warps (full_b).
+    constexpr bool kTmaOperands = !CONV || DENSE;
+    constexpr bool kBuiltOperands = CONV || !DENSE;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -223,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 int tm, tn;
                 tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if ((kb & 1) == 0) {
+                    if (!DENSE && (kb & 1) == 0) {
                         // Packed words of k-blocks kb and kb+1 for the BN columns of this tile
                         // (rows past the end of the plane are zero-filled by TMA).
                         if (!ptx::mbar_wait(bar_empty_w + 8 * wstage, wphase ^ 1u, p.err_word, kErrWaitEmpty)) {
@@ -240,17 +252,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             wphase ^= 1u;
                         }
                     }
-                    if (!CONV) {
+                    if (kTmaOperands) {
                         if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, p.err_word, kErrWaitEmpty)) {
                             ok = false;
                             break;
                         }
                         const uint32_t bar = bar_full_a + 8 * stage;
-                        ptx::mbar_arrive_expect_tx(bar, NPASS * A_TILE_BYTES);
-                        const uint32_t a_dst = base + stage * C::STAGE_BYTES + C::B_TILE_BYTES;
+                        ptx::mbar_arrive_expect_tx(bar, (CONV ? 0 : NPASS * A_TILE_BYTES) + (DENSE ? C::B_BYTES : 0));
+                        const uint32_t b_dst = base + stage * C::STAGE_BYTES;
+                        const uint32_t a_dst = b_dst + C::B_BYTES;
+                        if (DENSE) {
 #pragma unroll
-                        for (int q = 0; q < NPASS; ++q)
-                            ptx::tma_load_3d(a_dst + q * A_TILE_BYTES, &tmap_a, kb * BK, tm * BM, q, bar);
+                            for (int q = 0; q < 2; ++q)
+                                ptx::tma_load_3d(b_dst + q * C::B_TILE_BYTES, &tmap_neg, kb * BK, tn * BN, q, bar);
+                        }
+                        if (!CONV) {
+#pragma unroll
+                            for (int q = 0; q < NPASS; ++q)
+                                ptx::tma_load_3d(a_dst + q * A_TILE_BYTES, &tmap_a, kb * BK, tm * BM, q, bar);
+                        }
                         if (++stage == C::STAGES) {
                             stage = 0;
                             phase ^= 1u;
@@ -280,23 +300,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     const int kb_begin = seg * p.kb_per_seg;
                     const int kb_end = min(p.num_kb, kb_begin + p.kb_per_seg);
                     for (int kb = kb_begin; kb < kb_end; ++kb) {
-                        // CONV mode: the build warps write both operands and signal on full_b only.
-                        if ((!CONV && !ptx::mbar_wait(bar_full_a + 8 * stage, phase, p.err_word, kErrWaitFullA)) ||
-                            !ptx::mbar_wait(bar_full_b + 8 * stage, phase, p.err_word, kErrWaitFullB)) {
+                        // TMA-delivered operands signal on full_a, operands written by the build warps on full_b.
+                        if ((kTmaOperands && !ptx::mbar_wait(bar_full_a + 8 * stage, phase, p.err_word, kErrWaitFullA)) ||
+                            (kBuiltOperands && !ptx::mbar_wait(bar_full_b + 8 * stage, phase, p.err_word, kErrWaitFullB))) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after_sync();
                         const uint32_t b_addr = base + stage * C::STAGE_BYTES;
-                        const uint32_t a_addr = b_addr + C::B_TILE_BYTES;
+                        const uint32_t a_addr = b_addr + C::B_BYTES;
+                        // Binary/ternary weights: every activation term against the one exact weight tile.
+                        // Dense weights: hi*hi + hi*lo + lo*hi (the lo*lo term is below fp32 resolution).
+                        constexpr int kPairs = DENSE ? 3 : NPASS;
 #pragma unroll
-                        for (int q = 0; q < NPASS; ++q) {
+                        for (int pr = 0; pr < kPairs; ++pr) {
+                            const int qa = DENSE ? (pr == 2 ? 1 : 0) : pr;
+                            const int qb = DENSE ? (pr == 1 ? 1 : 0) : 0;
 #pragma unroll
                             for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
                                 const uint64_t a_desc =
-                                    ptx::umma_desc_k_sw128(a_addr + q * A_TILE_BYTES + k4 * UMMA_K * 2);
-                                const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * UMMA_K * 2);
-                                ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || q != 0 || k4 != 0) ? 1u : 0u);
+                                    ptx::umma_desc_k_sw128(a_addr + qa * A_TILE_BYTES + k4 * UMMA_K * 2);
+                                const uint64_t b_desc =
+                                    ptx::umma_desc_k_sw128(b_addr + qb * C::B_TILE_BYTES + k4 * UMMA_K * 2);
+                                ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb != kb_begin || pr != 0 || k4 != 0) ? 1u : 0u);
                             }
                         }
                         ptx::umma_commit(bar_empty + 8 * stage);  // smem stage free once these MMAs retire
@@ -320,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         uint32_t phase = 0, wphase = 0;
         bool ok = true;
         uint4 wn = make_uint4(0u, 0u, 0u, 0u), wp = make_uint4(0u, 0u, 0u, 0u);
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int t = blockIdx.x; kBuiltOperands && t < total_tiles && ok; t += gridDim.x) {
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
             // Window origin of this thread's output pixel (CONV mode).
@@ -340,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                        static_cast<int64_t>(ih0) * p.conv.W + iw0;
             }
             for (int kb = 0; kb < p.num_kb; ++kb) {
-                if ((kb & 1) == 0) {
+                if (!DENSE && (kb & 1) == 0) {
                     // Words of this and the next k-block: shared memory -> registers, then free the slot.
                     if (!ptx::mbar_wait(bar_full_w + 8 * wstage, wphase, p.err_word, kErrWaitFullB)) {
                         ok = false;
@@ -382,7 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     break;
                 }
                 uint8_t* stage_ptr = base_ptr + stage * C::STAGE_BYTES;
-                if (r < BN) {
+                if (!DENSE && r < BN) {
                     uint8_t* row = stage_ptr + r * 128;
                     const uint32_t nw[2] = {(kb & 1) ? wn.z : wn.x, (kb & 1) ? wn.w : wn.y};
                     const uint32_t pw[2] = {(kb & 1) ? wp.z : wp.x, (kb & 1) ? wp.w : wp.y};
@@ -395,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     }
                 }
                 if (CONV) {
-                    uint8_t* a_tile = stage_ptr + C::B_TILE_BYTES + a_row * 128;
+                    uint8_t* a_tile = stage_ptr + C::B_BYTES + a_row * 128;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t packed[NPASS][4];
@@ -635,10 +661,10 @@ inline void set_segments(tc::Params& p, int npass) {
     p.kb_per_seg = (p.num_kb + p.num_seg - 1) / p.num_seg;
 }
 
-template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT>
+template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT, bool DENSE = false>
 int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
-    using C = tc::Cfg<BN, NPASS, TERNARY>;
-    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, CONV, TERN_ACT>;
+    using C = tc::Cfg<BN, NPASS, TERNARY, DENSE>;
+    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, CONV, TERN_ACT, DENSE>;
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
@@ -648,13 +674,30 @@ int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) 
     return launched(CONV ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
 }
 
-template <int NPASS, bool TERNARY, bool CONV, bool TERN_ACT>
+template <int NPASS, bool TERNARY, bool CONV, bool TERN_ACT, bool DENSE = false>
 int32_t dispatch_bn(int bn, const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
     switch (bn) {
-        case 256: return launch_tc<256, NPASS, TERNARY, CONV, TERN_ACT>(maps, p, st);
-        case 128: return launch_tc<128, NPASS, TERNARY, CONV, TERN_ACT>(maps, p, st);
-        default: return launch_tc<64, NPASS, TERNARY, CONV, TERN_ACT>(maps, p, st);
+        case 256: return launch_tc<256, NPASS, TERNARY, CONV, TERN_ACT, DENSE>(maps, p, st);
+        case 128: return launch_tc<128, NPASS, TERNARY, CONV, TERN_ACT, DENSE>(maps, p, st);
+        default: return launch_tc<64, NPASS, TERNARY, CONV, TERN_ACT, DENSE>(maps, p, st);
     }
+}
+
+// Tensor map over bf16 terms laid out [terms][rows_pad][K_pad] (split activations or split dense weights):
+// box = 64 k x `box_rows` rows x 1 term, 128-byte swizzle.
+inline int32_t make_split_map(EncodeTiledFn encode, const void* base, int64_t K_pad, int64_t rows_pad, int terms,
+                              int box_rows, CUtensorMap* out) {
+    const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(K_pad), static_cast<cuuint64_t>(rows_pad),
+                                static_cast<cuuint64_t>(terms)};
+    const cuuint64_t gstride[2] = {static_cast<cuuint64_t>(K_pad) * 2, static_cast<cuuint64_t>(rows_pad) * K_pad * 2};
+    const cuuint32_t box[3] = {tc::BK, static_cast<cuuint32_t>(box_rows), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult cr = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstride, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
+                "cuTensorMapEncodeTiled (bf16 terms) failed with CUresult " + std::to_string(static_cast<int>(cr)));
+    return TBN_SUCCESS;
 }
 
 }  // namespace

@@ -35,10 +35,16 @@ class Session:
         self.inputs = {}
         self.values = {}
         self.weights = {}
+        conv_w = {n["inputs"][1] for n in graph["nodes"] if n["op"] == "Conv"}
+        gemm_w = {n["inputs"][1] for n in graph["nodes"] if n["op"] == "Gemm"}
         for name, arr in graph["inits"].items():
             t = torch.from_numpy(np.ascontiguousarray(arr, dtype=np.float32)).to(self.device)
             if name in graph["binary"]:
                 self.weights[name] = self._pack(t)
+            elif name in conv_w:   # float filters: split once into two bf16 terms
+                self.weights[name] = {"shape": tuple(t.shape), "split": self.L.dense_pack(t.reshape(t.shape[0], -1), capi.LAYOUT_NK)}
+            elif name in gemm_w:   # float Gemm B [K, N]
+                self.weights[name] = {"shape": tuple(t.shape), "split": self.L.dense_pack(t, capi.LAYOUT_KN)}
             else:
                 self.weights[name] = {"dense": t}
         self._ws = {}
@@ -137,11 +143,9 @@ class Session:
         x = vals[n["inputs"][0]]
         w = self.weights[n["inputs"][1]]
         bias = self.weights[n["inputs"][2]]["dense"] if len(n["inputs"]) > 2 else None
-        if "words" not in w:
-            raise NotImplementedError("float-weight Conv is not on the accelerated path yet")
         out_name = n["outputs"][0]
         ws = self._workspace("conv", L.h.tbn_conv2d_workspace_bytes(w["shape"][1], w["shape"][2], w["shape"][3]))
-        if self.quantization:
+        if self.quantization and "words" in w:
             y = L.conv2d_tbn(x, w["words"], w["shape"], p, alpha=w["alpha_tbn"], bias=bias,
                              epilogue=capi.EPI_BIAS_BEFORE_ALPHA, workspace=ws)
             return out_name, y
@@ -162,8 +166,11 @@ class Session:
                     epilogue |= capi.EPI_RELU
                     skip.update((idx + 1, idx + 2))
                     out_name = nodes[idx + 2]["outputs"][0]
-        y = L.conv2d_fxb(x, w["words"], w["shape"], p, alpha=w["alpha"], bias=bias, residual=residual,
-                         epilogue=epilogue, workspace=ws)
+        if "words" in w:
+            y = L.conv2d_fxb(x, w["words"], w["shape"], p, alpha=w["alpha"], bias=bias, residual=residual,
+                             epilogue=epilogue, workspace=ws)
+        else:
+            y = L.conv2d_f32(x, w["split"], w["shape"], p, bias=bias, residual=residual, epilogue=epilogue, workspace=ws)
         return out_name, y
 
     def _gemm(self, n, vals):
@@ -174,12 +181,13 @@ class Session:
         x = vals[n["inputs"][0]]
         w = self.weights[n["inputs"][1]]
         bias = self.weights[n["inputs"][2]]["dense"] if len(n["inputs"]) > 2 else None
-        if "words" not in w:
-            raise NotImplementedError("float-weight Gemm is not on the accelerated path yet")
         N = w["shape"][1]
         alpha_attr, beta = float(a.get("alpha", 1.0)), float(a.get("beta", 1.0))
         if bias is not None and beta != 1.0:
             bias = bias * beta
+        if "words" not in w:
+            ws, _ = L.gemm_workspace(x.shape[0], x.shape[1], capi.MODE_TC_BF16X2, self.device)
+            return L.gemm_f32(x.contiguous(), w["split"], N, alpha=alpha_attr, bias=bias, workspace=ws)
         if self.quantization:
             # Weights alpha*sign(w) are not exactly +-1, so the reference quantises them on the fly and runs
             # qlinear_matmul_binary with scale 1 (model.hpp:839-841), then alpha and beta*C (:845-869).

@@ -215,6 +215,20 @@ int32_t tbn_gemm_tbn(const float* d_a, int64_t M, int64_t K, int64_t lda, float 
                      const float* d_bias, float* d_c, int64_t ldc, uint32_t epilogue,
                      void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* ---- float weights (the float layers of the CNN graphs) --------------------------------- */
+
+/* Dense fp32 weights are split once into two bf16 terms, stored K-major per output column:
+ * [2][ceil8(N)][ceil128(K)] bf16.  Layouts as for the packers (KN: Gemm B [K,N]; NK: filters [M_out, C*kh*kw]). */
+size_t tbn_dense_pack_bytes(int64_t K, int64_t N);
+int32_t tbn_dense_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout, void* d_packed,
+                       void* stream);
+/* Float x float GEMM  C = alpha * A W + bias  in fp32 accuracy (two bf16 terms on both sides:
+ * hi*hi + hi*lo + lo*hi on the tensor cores).  Stands in for tbn::gemm (tbn-runtime/src/operators/gemm.cpp:35-129,
+ * 349-360) with transA = transB = 0 and a 1-D C; workspace as tbn_gemm_workspace_bytes(M, K, TBN_MODE_TC_BF16X2). */
+int32_t tbn_gemm_f32(const float* d_a, int64_t M, int64_t K, int64_t lda, const void* d_packed_w, int64_t N,
+                     float alpha, const float* d_bias, float* d_c, int64_t ldc, uint32_t epilogue,
+                     void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* ---- convolution (implicit GEMM) ----------------------------------------------------- */
 
 /* Bytes of scratch the convolution entry points need (tap table + partial-sum tiles). */
@@ -245,6 +259,13 @@ int32_t tbn_conv2d_tbn(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                        int32_t ph, int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale,
                        const float* d_bias, float* d_y, uint32_t epilogue, void* d_workspace,
                        size_t workspace_bytes, void* stream);
+
+/* Float-filter Conv2D (stem and 1x1 shortcut convolutions): stands in for tbn::conv2d
+ * (tbn-runtime/src/operators/conv2d.cpp:78-192); filters from tbn_dense_pack (TBN_LAYOUT_NK). */
+int32_t tbn_conv2d_f32(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, const void* d_packed_w,
+                       int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw,
+                       int32_t dh, int32_t dw, const float* d_bias, const float* d_residual, float* d_y,
+                       uint32_t epilogue, void* d_workspace, size_t workspace_bytes, void* stream);
 
 /* ---- glue operators of the CNN graphs (device resident, fp32) --------------------------- */
 

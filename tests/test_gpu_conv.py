@@ -222,3 +222,55 @@ def test_conv_full_batch_properties(tbn):
     y_pos = tbn.lib.conv2d_fxb(x, words, w.shape, p, alpha=alpha)
     tbn.lib.sync()
     assert torch.equal(y_neg, -y_pos)
+
+
+# ------------------------------------------------------------------ float weights (dense path)
+
+@pytest.mark.parametrize("M,K,N", [(128, 128, 128), (200, 300, 77), (64, 512, 1000), (1000, 147, 64), (3, 4608, 10)])
+def test_gemm_f32_vs_reference_float_gemm(tbn, oracle, M, K, N):
+    """tbn_gemm_f32 (bf16 hi/lo on both operands) against tbn::gemm's blocked fp32 loop."""
+    import torch
+    rng = np.random.default_rng(M + K + N)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    W = rng.standard_normal((K, N), dtype=np.float32) * np.float32(0.1)
+    bias = rng.standard_normal(N, dtype=np.float32)
+    pw = tbn.lib.dense_pack(torch.from_numpy(W).cuda(), tbn.LAYOUT_KN)
+    out = tbn.lib.gemm_f32(torch.from_numpy(A).cuda(), pw, N, alpha=0.7, bias=torch.from_numpy(bias).cuda())
+    tbn.lib.sync()
+    expect = oracle.gemm_f32(A, W, bias, 0.7, 1.0)
+    assert rel_l2(out.cpu().numpy(), expect) <= TOL_FP32
+    # the NK layout packs the same operand from the transposed matrix
+    pw_t = tbn.lib.dense_pack(torch.from_numpy(np.ascontiguousarray(W.T)).cuda(), tbn.LAYOUT_NK)
+    assert torch.equal(pw, pw_t)
+
+
+@pytest.mark.parametrize("case", [CONV_CASES[1], CONV_CASES[2], CONV_CASES[6], CONV_CASES[7], CONV_CASES[9]])
+def test_conv_f32_vs_reference_float_conv(tbn, oracle, case):
+    import torch
+    x, w, b, p = _conv_inputs(case, seed=9)
+    pw = tbn.lib.dense_pack(torch.from_numpy(w).cuda().reshape(w.shape[0], -1), tbn.LAYOUT_NK)
+    y = tbn.lib.conv2d_f32(torch.from_numpy(x).cuda(), pw, w.shape, p, bias=torch.from_numpy(b).cuda())
+    tbn.lib.sync()
+    assert rel_l2(y.cpu().numpy(), oracle.conv2d_f32(x, w, b, p)) <= TOL_FP32
+
+
+@pytest.mark.parametrize("batch,image", [(2, 64), (1, 224)])
+def test_resnet18_session(tbn, oracle, batch, image):
+    """Binary ResNet-18-style CNN (fp32 stem / shortcut convolutions / classifier, binary 3x3 convolutions,
+    residual adds) against the reference's float path on the dequantised weights: logits within 1e-5 and the
+    predicted class identical; fused (Conv+ReLU, Conv+Add+ReLU epilogues) and unfused execution agree."""
+    from fast_arm_tbcnn_b200.session import Session
+    from oracle import graphs
+    net = graphs.resnet18(batch=batch, seed=2, image=image, classes=1000 if image == 224 else 100)
+    x = np.random.default_rng(0).standard_normal((batch, 3, image, image), dtype=np.float32)
+    expect = graphs.run_float(net, x, oracle)
+    outs = []
+    for fuse in (True, False):
+        s = Session(net, fuse=fuse)
+        s.set_input("input", x)
+        s.run()
+        tbn.lib.sync()
+        outs.append(s.get_output("output").cpu().numpy())
+        assert rel_l2(outs[-1], expect) <= TOL_FP32
+        assert np.array_equal(outs[-1].argmax(axis=1), expect.argmax(axis=1))
+    assert rel_l2(outs[0], outs[1]) <= 1e-6
