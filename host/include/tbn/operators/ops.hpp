@@ -35,6 +35,16 @@ PackedWeights pack_ternary_weights(const Tensor& weights, float threshold_low, f
 // A BINARY-dtype tensor (1 = +1, 0 = -1), as produced by quantize_to_binary.
 PackedWeights pack_binary_tensor(const Tensor& binary_weights);
 
+// Float (non-quantised) weights split once into two bf16 terms for the tensor-core float path.
+struct DenseWeights {
+    Tensor split;        // [2][ceil8(N)][ceil128(K)] bf16
+    int64_t K = 0, N = 0;
+    Shape weight_shape;
+};
+DenseWeights pack_dense_weights(const Tensor& weights);  // [K,N] matrix or [M,C,kh,kw] filter bank
+// C = alpha * A W + bias and the float-filter convolution, fp32 accuracy.
+Tensor matmul_float_dense(const Tensor& a, const DenseWeights& w, const Tensor* bias = nullptr, float alpha = 1.0f);
+
 // ---- GEMM ------------------------------------------------------------------------------------
 // Reference "TBN mode" (activations ternarised at +-0.1, exact integer accumulation), bit-equal to
 // the reference functions of the same name (quantized_gemm.hpp:42-84).
@@ -49,8 +59,8 @@ Tensor qlinear_matmul_binary_packed(const Tensor& a, const PackedWeights& w, flo
 //   C = (A * sign(W)) * alpha * scale + bias      (what the reference's float tbn::gemm gives on alpha*sign(W)).
 Tensor matmul_float_packed(const Tensor& a, const PackedWeights& w, const Tensor* bias = nullptr, float scale = 1.0f,
                            bool relu = false);
-// tbn::gemm (gemm.hpp:11-12).  Supported when B is a scaled-binary matrix (every column is +-alpha);
-// general float x float products are not on the accelerated path.
+// tbn::gemm (gemm.hpp:11-12): alpha * A B + beta * C with a 1-D C, transA = transB = 0.  A scaled-binary B
+// (+-alpha per column) runs on the packed-weight kernel, any other B on the float path.
 Tensor gemm(const Tensor& A, const Tensor& B, const Tensor* C = nullptr, float alpha = 1.0f, float beta = 0.0f,
             bool transA = false, bool transB = false);
 
@@ -77,7 +87,9 @@ Tensor conv2d_float_packed(const Tensor& input, const PackedWeights& w, const Te
 // TBN-mode convolution on packed weights with the Session's epilogue (acc + bias) * alpha.
 Tensor conv2d_tbn_packed(const Tensor& input, const PackedWeights& w, const Tensor* alpha, const Tensor* bias,
                          const Conv2DParams& params, bool bias_before_alpha);
-// tbn::conv2d (conv2d.hpp:40-41): supported when the filters are scaled-binary (each is +-alpha).
+Tensor conv2d_float_dense(const Tensor& input, const DenseWeights& w, const Tensor* bias, const Conv2DParams& params,
+                          const Tensor* residual = nullptr, bool relu = false);
+// tbn::conv2d (conv2d.hpp:40-41): scaled-binary filters run on the packed-weight kernel, others on the float path.
 Tensor conv2d(const Tensor& input, const Tensor& weights, const Tensor* bias = nullptr,
               const Conv2DParams& params = Conv2DParams());
 

@@ -10,10 +10,10 @@
 // every node runs a CUDA kernel through the C ABI.
 //
 // Numeric modes, selected by the reference's own switch:
-//   set_quantization(false)  Conv/Gemm evaluate y = x * W in fp32 accuracy.  Accelerated when W is a
-//                            scaled-binary tensor (+-alpha per output channel, i.e. a dequantised TBN model)
-//                            or when the weight name was declared with mark_binary() (raw fp32 weights, sign
-//                            and alpha = mean|w| derived here).  Other float weights: NotImplementedError.
+//   set_quantization(false)  Conv/Gemm evaluate y = x * W in fp32 accuracy.  A scaled-binary W (+-alpha per
+//                            output channel, i.e. a dequantised TBN model) or one declared with mark_binary()
+//                            (raw fp32 weights; sign and alpha = mean|w| derived here) runs on the packed-weight
+//                            kernels; any other float W runs on the float path (two bf16 terms per operand).
 //   set_quantization(true)   the reference's TBN mode, bit-equal: activations ternarised at +-0.1, exact
 //                            integer GEMM, Conv epilogue (acc + bias) * alpha, Gemm quantised on the fly.
 #pragma once
@@ -84,6 +84,8 @@ public:
             PackedWeights packed;   // sign planes (+ alpha for the float x binary mode)
             Tensor alpha_tbn;       // sequentially summed scale of the dequantised weights (TBN-mode Conv)
             bool scaled_binary = false;
+            bool dense = false;     // plain float weights: `dense_w` is used instead of `packed`
+            DenseWeights dense_w;
         };
         const CachedWeights* weights_for(const std::string& name, const Tensor& w, bool conv);
         void execute_node(const ModelNode& node);

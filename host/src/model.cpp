@@ -94,7 +94,11 @@ const TBNModel::Session::CachedWeights* TBNModel::Session::weights_for(const std
     if (conv) {
         std::vector<float> scales;
         cw.scaled_binary = scaled_binary_channel_scales(w, &scales);
-        if (!cw.scaled_binary && !declared) return nullptr;
+        if (!cw.scaled_binary && !declared) {
+            cw.dense = true;
+            cw.dense_w = pack_dense_weights(w);
+            return &weight_cache_.emplace(name, std::move(cw)).first->second;
+        }
         // Scaled-binary: sign by >= 0 (model.hpp:433).  Declared raw weights: quantize_to_binary's w > 0.
         cw.packed = pack_binary_weights(w, 0.0f, cw.scaled_binary);
         if (cw.scaled_binary) cw.alpha_tbn = make_tensor(Shape{static_cast<int64_t>(scales.size())}, scales);
@@ -107,7 +111,11 @@ const TBNModel::Session::CachedWeights* TBNModel::Session::weights_for(const std
         for (int64_t k = 0; k < K; ++k)
             for (int64_t n = 0; n < N; ++n) t[n * K + k] = b[k * N + n];
         cw.scaled_binary = scaled_binary_channel_scales(bt, nullptr);
-        if (!cw.scaled_binary && !declared) return nullptr;
+        if (!cw.scaled_binary && !declared) {
+            cw.dense = true;
+            cw.dense_w = pack_dense_weights(w);
+            return &weight_cache_.emplace(name, std::move(cw)).first->second;
+        }
         cw.packed = pack_binary_weights(w, 0.0f, false);  // w > 0, as quantize_to_binary (model.hpp:840)
     }
     return &weight_cache_.emplace(name, std::move(cw)).first->second;
@@ -157,7 +165,9 @@ void TBNModel::Session::execute_conv(const ModelNode& node) {
         result = conv2d_ternary(X, W, B, p);
     } else {
         const CachedWeights* cw = weights_for(node.inputs[1], W, true);
-        if (use_quantization_) {
+        if (cw && cw->dense && !use_quantization_) {
+            result = conv2d_float_dense(X, cw->dense_w, B, p);
+        } else if (use_quantization_) {
             if (cw && cw->scaled_binary) {
                 result = conv2d_tbn_packed(X, cw->packed, &cw->alpha_tbn, B, p, true);  // (acc + bias) * alpha
             } else {
@@ -210,9 +220,12 @@ void TBNModel::Session::execute_gemm(const ModelNode& node) {
         }
     }
     Tensor result;
-    if (use_quantization_) {
-        // model.hpp:835-869: binary GEMM with scale 1, then * alpha, + beta * C.
-        result = qlinear_matmul_binary_packed(A, cw->packed, alpha);
+    if (cw->dense && !use_quantization_) {
+        result = matmul_float_dense(A, cw->dense_w, bias.empty() ? nullptr : &bias, alpha);
+    } else if (use_quantization_) {
+        // model.hpp:835-869: binary GEMM with scale 1, then * alpha, + beta * C.  Plain float weights are
+        // binarised on the fly by sign, as the reference does (model.hpp:839-841).
+        result = qlinear_matmul_binary_packed(A, cw->dense ? pack_binary_weights(Bw, 0.0f, false) : cw->packed, alpha);
         if (!bias.empty()) result = add(result, bias);
     } else {
         result = matmul_float_packed(A, cw->packed, bias.empty() ? nullptr : &bias, alpha);

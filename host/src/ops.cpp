@@ -137,6 +137,40 @@ PackedWeights pack_binary_tensor(const Tensor& b) {
     return pack_impl(f, false, 0.0f, 0.0f, false);
 }
 
+DenseWeights pack_dense_weights(const Tensor& weights) {
+    detail::ensure_runtime();
+    TBN_CHECK(weights.dtype() == DataType::FLOAT32, InvalidArgumentError, "weights must be FLOAT32");
+    const auto& d = weights.shape().dims;
+    TBN_CHECK(d.size() == 2 || d.size() == 4, InvalidShapeError, "weights must be [K,N] or [M,C,kh,kw]");
+    DenseWeights w;
+    w.weight_shape = weights.shape();
+    int layout;
+    int64_t ldw;
+    if (d.size() == 2) {
+        w.K = d[0]; w.N = d[1]; layout = TBN_LAYOUT_KN; ldw = w.N;
+    } else {
+        w.N = d[0]; w.K = d[1] * d[2] * d[3]; layout = TBN_LAYOUT_NK; ldw = w.K;
+    }
+    w.split = Tensor(Shape{static_cast<int64_t>(tbn_dense_pack_bytes(w.K, w.N))}, DataType::UINT8, DeviceType::CUDA);
+    check(tbn_dense_pack(dptr(weights), w.K, w.N, ldw, layout, w.split.device_data(), nullptr));
+    w.split.mark_device_written();
+    return w;
+}
+
+Tensor matmul_float_dense(const Tensor& a, const DenseWeights& w, const Tensor* bias, float alpha) {
+    require_f32_2d(a, "Input A");
+    const int64_t M = a.shape().dims[0], K = a.shape().dims[1];
+    if (K != w.K) throw InvalidShapeError("Matrix dimensions incompatible: A cols (" + std::to_string(K) + ") != B rows (" +
+                                          std::to_string(w.K) + ")");
+    if (bias) TBN_CHECK(bias->num_elements() == w.N, InvalidShapeError, "bias must have one entry per output column");
+    Tensor out = device_f32(Shape{M, w.N});
+    const size_t ws_bytes = tbn_gemm_workspace_bytes(M, K, TBN_MODE_TC_BF16X2);
+    check(tbn_gemm_f32(dptr(a), M, K, K, w.split.device_data(), w.N, alpha, dptr_or_null(bias),
+                       static_cast<float*>(out.device_data()), w.N, 0u, workspace().get(ws_bytes), ws_bytes, nullptr));
+    out.mark_device_written();
+    return out;
+}
+
 // ---------------------------------------------------------------- GEMM
 
 Tensor qlinear_matmul_binary_packed(const Tensor& a, const PackedWeights& w, float scale, float lo, float hi) {
@@ -227,9 +261,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const Tensor* C, float alpha, floa
     float* t = bt.typed_data<float>();
     for (int64_t k = 0; k < K; ++k)
         for (int64_t n = 0; n < N; ++n) t[n * K + k] = b[k * N + n];
-    if (!scaled_binary_channel_scales(bt, nullptr))
-        throw NotImplementedError("gemm: general float x float products are not on the accelerated path; "
-                                  "B must be scaled-binary (+-alpha per column)");
+    const bool binary = scaled_binary_channel_scales(bt, nullptr);
     Tensor bias;
     if (C && beta != 0.0f) {
         TBN_CHECK(C->shape().dims.size() == 1, NotImplementedError, "gemm: only a 1-D C (bias) is accelerated");
@@ -237,6 +269,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const Tensor* C, float alpha, floa
         float* p = bias.typed_data<float>();
         for (int64_t i = 0; i < bias.num_elements(); ++i) p[i] *= beta;
     }
+    if (!binary) return matmul_float_dense(A, pack_dense_weights(B), bias.empty() ? nullptr : &bias, alpha);
     return matmul_float_packed(A, pack_binary_weights(B, 0.0f, true), bias.empty() ? nullptr : &bias, alpha);
 }
 
@@ -337,10 +370,25 @@ Tensor conv2d_ternary(const Tensor& x, const Tensor& tw, const Tensor* bias, con
 Tensor conv2d(const Tensor& x, const Tensor& w, const Tensor* bias, const Conv2DParams& p) {
     TBN_CHECK(w.dtype() == DataType::FLOAT32, InvalidArgumentError, "Conv2D requires float32 weights");
     TBN_CHECK(w.shape().dims.size() == 4, InvalidShapeError, "Conv2D weights must be 4D (MCHW), got " + shape_to_string(w.shape()));
-    if (!scaled_binary_channel_scales(w, nullptr))
-        throw NotImplementedError("conv2d: general float filters are not on the accelerated path; "
-                                  "filters must be scaled-binary (+-alpha per output channel)");
+    if (!scaled_binary_channel_scales(w, nullptr)) return conv2d_float_dense(x, pack_dense_weights(w), bias, p);
     return conv2d_float_packed(x, pack_binary_weights(w, 0.0f, true), bias, p);
+}
+
+Tensor conv2d_float_dense(const Tensor& x, const DenseWeights& w, const Tensor* bias, const Conv2DParams& p,
+                          const Tensor* residual, bool relu_flag) {
+    const ConvDims d = conv_dims(x, w.weight_shape, p);
+    check_bias(bias, d.M);
+    Tensor y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
+    if (residual) TBN_CHECK(residual->shape() == y.shape(), InvalidShapeError, "residual must have the output's shape");
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.C, d.kh, d.kw);
+    const uint32_t epi = (relu_flag ? TBN_EPI_RELU : 0u) | (residual ? TBN_EPI_ADD_RESIDUAL : 0u);
+    check(tbn_conv2d_f32(dptr(x), d.N, d.C, d.H, d.W, w.split.device_data(), d.M, d.kh, d.kw, static_cast<int32_t>(p.stride_h),
+                         static_cast<int32_t>(p.stride_w), static_cast<int32_t>(p.pad_h), static_cast<int32_t>(p.pad_w),
+                         static_cast<int32_t>(p.dilation_h), static_cast<int32_t>(p.dilation_w), dptr_or_null(bias),
+                         dptr_or_null(residual), static_cast<float*>(y.device_data()), epi, workspace().get(ws_bytes), ws_bytes,
+                         nullptr));
+    y.mark_device_written();
+    return y;
 }
 
 // ---------------------------------------------------------------- pooling / elementwise

@@ -75,3 +75,17 @@ def test_conv_layer_through_cpp_session(host, oracle, tmp_path):
     got_q = _run(host[1], tmp_path, net, x, True, (3, 128, 14, 14), True)
     wq = graphs.dequantise(net["inits"]["w"])
     assert np.array_equal(got_q, oracle.conv2d_tbn_session(x, wq, net["inits"]["b"], (1, 1, 1, 1, 1, 1)))
+
+
+@pytest.mark.gpu
+def test_resnet18_through_cpp_session(host, oracle, tmp_path):
+    """Float stem / shortcut convolutions / classifier on the float path, binary 3x3 convolutions on the packed
+    path, all through tbn::TBNModel::Session."""
+    from oracle import graphs
+    net = graphs.resnet18(batch=1, seed=2, image=64, classes=100)
+    x = np.random.default_rng(0).standard_normal((1, 3, 64, 64), dtype=np.float32)
+    expect = graphs.run_float(net, x, oracle)
+    for dequantised in (False, True):
+        got = _run(host[1], tmp_path, net, x, False, (1, 100), dequantised)
+        assert rel_l2(got, expect) <= 1e-5
+        assert got.argmax() == expect.argmax()
