@@ -145,6 +145,63 @@ def cpu_reference_arm(n, steps, warmup, threads, rows_per_thread):
     }
 
 
+def cnn_block(args, L, capi, torch, dist, dev, rank, world):
+    """Binary-CNN throughput, batch-sharded over the ranks with no collective: the 64x14x14 -> 128 3x3 conv
+    layer at batch 4096 and the binary ResNet-18-style network at 224x224 (micro-batches of 128 images per
+    GPU).  Whole-job images/s = images of all ranks / max-over-ranks device time."""
+    from fast_arm_tbcnn_b200 import sharding
+    from fast_arm_tbcnn_b200.session import Session
+    from oracle import graphs  # graph recipes only (plain dicts); nothing of the checker runs here
+    out = {}
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ev0.record()
+        for _ in range(reps):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([ev0.elapsed_time(ev1) / reps], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- single conv layer, batch 4096 split across the ranks
+    b0, b1 = sharding.batch_block(rank, world, 4096)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn((b1 - b0, 64, 14, 14), generator=g, device=dev)
+    w = torch.randn((128, 64, 3, 3), generator=g, device=dev) * 0.05
+    bias = torch.randn(128, generator=g, device=dev) * 0.05
+    words, alpha = L.quant_pack_binary(w.reshape(128, -1), capi.LAYOUT_NK)
+    ws, _ = L.conv_workspace(64, 3, 3, dev)
+    y = torch.empty((b1 - b0, 128, 14, 14), device=dev)
+    p = (1, 1, 1, 1, 1, 1)
+    ms = timed(lambda: L.conv2d_fxb(x, words, w.shape, p, alpha=alpha, bias=bias, workspace=ws, out=y), 10)
+    flops = 2.0 * 4096 * 196 * 128 * 576
+    out["conv_layer_64x14x14_to_128_batch4096"] = {
+        "images_per_s": 4096 / (ms * 1e-3), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+        "algorithmic_gbs": 4096 * (64 + 128) * 196 * 4 / (ms * 1e-3) / 1e9}
+    del x, y
+
+    # ---- binary ResNet-18-style CNN, 3x224x224
+    micro = 128
+    net = graphs.resnet18(batch=micro, seed=2, image=224, classes=1000)
+    sess = Session(net)
+    sess.keep_intermediates = False
+    xin = torch.randn((micro, 3, 224, 224), generator=g, device=dev)
+    sess.set_input("input", xin)
+    ms = timed(sess.run, 3)
+    out["resnet18_binary_224"] = {"images_per_s": micro * world / (ms * 1e-3), "ms_per_microbatch": ms,
+                                  "microbatch_per_gpu": micro, "tflops": 3.63e9 * micro * world / (ms * 1e-3) / 1e12,
+                                  "topology": "fp32 stem 7x7/2 + maxpool; 4 stages x 2 basic blocks (64/128/256/512), "
+                                              "stride 2 + fp32 1x1 shortcut at the entry of stages 2-4; GAP; fp32 FC 1000"}
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -329,6 +386,12 @@ def run_ours(args):
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_ms.item())
 
+    cnn = None
+    if not args.no_cnn:
+        try:
+            cnn = cnn_block(args, L, capi, torch, dist, dev, rank, world)
+        except Exception as exc:  # noqa: BLE001  -- the GEMM line must still be printed
+            cnn = {"error": repr(exc)}
     if rank == 0:
         peaks = load_peaks()
         flops_step = 2.0 * n * n * n
@@ -368,6 +431,7 @@ def run_ours(args):
                             "frac_of_hbm": pack_bytes / (pack_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                             "peak_source": f"{peaks['source']} copy {peaks['hbm_gbs']} GB/s"},
         }
+        line["cnn"] = cnn
         if world == 1 and not args.no_cpu_baseline:
             from oracle import cpu_oracle
             if cpu_oracle.reference_available():
@@ -395,6 +459,7 @@ def main():
     ap.add_argument("--size", type=int, default=16384)
     ap.add_argument("--mode", default="x2", choices=["x1", "x2", "x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cnn", action="store_true", help="skip the binary-CNN images/s block")
     ap.add_argument("--no-fused-gather", action="store_true", help="N > 1: use NCCL all-gather instead of peer stores")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -100,8 +100,20 @@ class Session:
         for n in nodes:
             for i in n["inputs"]:
                 consumers[i] = consumers.get(i, 0) + 1
+        # Index of the last node that reads each value: intermediates are released right after it, so a
+        # large batch only ever holds the tensors that are still needed.
+        last_use = {}
+        for idx, n in enumerate(nodes):
+            for i in n["inputs"]:
+                last_use[i] = idx
+        keep_all = getattr(self, "keep_intermediates", True)
         skip = set()
         for idx, n in enumerate(nodes):
+            if not keep_all:
+                for name in [k for k, last in last_use.items() if last < idx and k in vals and k not in self.graph["outputs"]
+                             and k not in self.inputs]:
+                    del vals[name]
+                    del last_use[name]
             if idx in skip:
                 continue
             op = n["op"]
