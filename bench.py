@@ -176,11 +176,12 @@ def cnn_block(args, L, capi, torch, dist, dev, rank, world):
     x = torch.randn((b1 - b0, 64, 14, 14), generator=g, device=dev)
     w = torch.randn((128, 64, 3, 3), generator=g, device=dev) * 0.05
     bias = torch.randn(128, generator=g, device=dev) * 0.05
-    words, alpha = L.quant_pack_binary(w.reshape(128, -1), capi.LAYOUT_NK)
-    ws, _ = L.conv_workspace(64, 3, 3, dev)
+    order = capi.CONV_WEIGHTS_TAP_MAJOR
+    words, alpha = L.quant_pack_binary(L.permute_filters(w), capi.LAYOUT_NK)
+    ws, _ = L.conv_workspace(x.shape, 3, 3, dev, order)
     y = torch.empty((b1 - b0, 128, 14, 14), device=dev)
     p = (1, 1, 1, 1, 1, 1)
-    ms = timed(lambda: L.conv2d_fxb(x, words, w.shape, p, alpha=alpha, bias=bias, workspace=ws, out=y), 10)
+    ms = timed(lambda: L.conv2d_fxb(x, words, w.shape, p, alpha=alpha, bias=bias, workspace=ws, out=y, order=order), 10)
     flops = 2.0 * 4096 * 196 * 128 * 576
     out["conv_layer_64x14x14_to_128_batch4096"] = {
         "images_per_s": 4096 / (ms * 1e-3), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,

@@ -13,6 +13,7 @@ EPI_ADD_RESIDUAL = 4
 MODE_AUTO, MODE_TC_BF16X1, MODE_TC_BF16X2, MODE_TC_BF16X3, MODE_SIMT = 0, 1, 2, 3, 4
 EPI_RELU, EPI_BIAS_BEFORE_ALPHA = 1, 2
 LAYOUT_KN, LAYOUT_NK = 0, 1
+CONV_WEIGHTS_REFERENCE, CONV_WEIGHTS_TAP_MAJOR = 0, 1
 
 _vp, _i64, _i32, _f32, _u32, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_uint32, C.c_size_t
 
@@ -34,12 +35,13 @@ SIGNATURES = {
     "tbn_dense_pack": (_i32, [_vp, _i64, _i64, _i64, _i32, _vp, _vp]),
     "tbn_gemm_f32": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _f32, _vp, _vp, _i64, _u32, _vp, _sz, _vp]),
     "tbn_conv2d_f32": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp,
-                              _vp, _u32, _vp, _sz, _vp]),
-    "tbn_conv2d_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+                              _vp, _u32, _i32, _vp, _sz, _vp]),
+    "tbn_conv2d_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64, _i32]),
+    "tbn_permute_filters": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp]),
     "tbn_conv2d_fxb": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
-                              _vp, _f32, _vp, _vp, _vp, _i32, _u32, _vp, _sz, _vp]),
+                              _vp, _f32, _vp, _vp, _vp, _i32, _u32, _i32, _vp, _sz, _vp]),
     "tbn_conv2d_tbn": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
-                              _i32, _vp, _f32, _vp, _vp, _u32, _vp, _sz, _vp]),
+                              _i32, _vp, _f32, _vp, _vp, _u32, _i32, _vp, _sz, _vp]),
     "tbn_relu": (_i32, [_vp, _i64, _vp, _vp]),
     "tbn_add": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp, _vp]),
     "tbn_pool2d": (_i32, [_i32, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
@@ -302,13 +304,24 @@ class _Lib:
             return 0, 0  # the library rejects the call; the output shape does not matter
         return (H + 2 * ph - dh * (kh - 1) - 1) // sh + 1, (W + 2 * pw - dw * (kw - 1) - 1) // sw + 1
 
-    def conv_workspace(self, C_in, kh, kw, device):
+    def conv_workspace(self, xshape, kh, kw, device, order=CONV_WEIGHTS_REFERENCE):
         import torch
-        nbytes = self.h.tbn_conv2d_workspace_bytes(C_in, kh, kw)
+        N, Cc, H, W = xshape
+        nbytes = self.h.tbn_conv2d_workspace_bytes(N, Cc, H, W, kh, kw, order)
         return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device), nbytes
 
+    def permute_filters(self, w):
+        """[M, C, kh, kw] -> [M, kh*kw*C] in tap-major order (for CONV_WEIGHTS_TAP_MAJOR)."""
+        import torch
+        self.init()
+        w = w.contiguous()
+        M, Cc, kh, kw = w.shape
+        out = torch.empty((M, kh * kw * Cc), dtype=torch.float32, device=w.device)
+        check(self.h.tbn_permute_filters(_ptr(w), M, Cc, kh * kw, _ptr(out), _stream()))
+        return out
+
     def conv2d_fxb(self, x, neg, wshape, p, pos=None, alpha=None, scale=1.0, bias=None, residual=None, mode=MODE_AUTO,
-                   epilogue=0, out=None, workspace=None):
+                   epilogue=0, out=None, workspace=None, order=CONV_WEIGHTS_REFERENCE):
         """x [N,C,H,W]; packed weights of shape wshape = (M_out, C, kh, kw); p = (sh, sw, ph, pw, dh, dw)."""
         import torch
         self.init()
@@ -319,18 +332,18 @@ class _Lib:
         if out is None:
             out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
         if workspace is None:
-            workspace, nbytes = self.conv_workspace(Cc, kh, kw, x.device)
+            workspace, nbytes = self.conv_workspace(x.shape, kh, kw, x.device, order)
         else:
             nbytes = workspace.numel()
         if residual is not None:
             epilogue |= EPI_ADD_RESIDUAL
         check(self.h.tbn_conv2d_fxb(_ptr(x), N, Cc, H, W, _ptr(neg), _ptr(pos), M_out, kh, kw, *[int(v) for v in p],
-                                    _ptr(alpha), scale, _ptr(bias), _ptr(residual), _ptr(out), mode, epilogue,
+                                    _ptr(alpha), scale, _ptr(bias), _ptr(residual), _ptr(out), mode, epilogue, order,
                                     _ptr(workspace), nbytes, _stream()))
         return out
 
     def conv2d_tbn(self, x, neg, wshape, p, lo=-0.1, hi=0.1, alpha=None, scale=1.0, bias=None, epilogue=0, out=None,
-                   workspace=None):
+                   workspace=None, order=CONV_WEIGHTS_REFERENCE):
         import torch
         self.init()
         x = x.contiguous()
@@ -340,11 +353,11 @@ class _Lib:
         if out is None:
             out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
         if workspace is None:
-            workspace, nbytes = self.conv_workspace(Cc, kh, kw, x.device)
+            workspace, nbytes = self.conv_workspace(x.shape, kh, kw, x.device, order)
         else:
             nbytes = workspace.numel()
         check(self.h.tbn_conv2d_tbn(_ptr(x), N, Cc, H, W, lo, hi, _ptr(neg), M_out, kh, kw, *[int(v) for v in p],
-                                    _ptr(alpha), scale, _ptr(bias), _ptr(out), epilogue, _ptr(workspace), nbytes,
+                                    _ptr(alpha), scale, _ptr(bias), _ptr(out), epilogue, order, _ptr(workspace), nbytes,
                                     _stream()))
         return out
 
@@ -373,7 +386,8 @@ class _Lib:
                                   epilogue, _ptr(workspace), nbytes, _stream()))
         return out
 
-    def conv2d_f32(self, x, packed_w, wshape, p, bias=None, residual=None, epilogue=0, out=None, workspace=None):
+    def conv2d_f32(self, x, packed_w, wshape, p, bias=None, residual=None, epilogue=0, out=None, workspace=None,
+                   order=CONV_WEIGHTS_REFERENCE):
         import torch
         self.init()
         x = x.contiguous()
@@ -383,13 +397,13 @@ class _Lib:
         if out is None:
             out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
         if workspace is None:
-            workspace, nbytes = self.conv_workspace(Cc, kh, kw, x.device)
+            workspace, nbytes = self.conv_workspace(x.shape, kh, kw, x.device, order)
         else:
             nbytes = workspace.numel()
         if residual is not None:
             epilogue |= EPI_ADD_RESIDUAL
         check(self.h.tbn_conv2d_f32(_ptr(x), N, Cc, H, W, _ptr(packed_w), M_out, kh, kw, *[int(v) for v in p], _ptr(bias),
-                                    _ptr(residual), _ptr(out), epilogue, _ptr(workspace), nbytes, _stream()))
+                                    _ptr(residual), _ptr(out), epilogue, order, _ptr(workspace), nbytes, _stream()))
         return out
 
     def relu(self, x):

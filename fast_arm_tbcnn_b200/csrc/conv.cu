@@ -27,6 +27,56 @@ __global__ void conv_tap_table_kernel(int2* __restrict__ table, int K, int K_pad
     table[k] = make_int2(c * H * W + i * dh * W + j * dw, ((i * dh) << 16) | ((j * dw) & 0xffff));
 }
 
+// NCHW fp32 -> channels-last bf16 terms xs[q][n][h][w][c] (or the ternarised activation as one exact term).
+// One block transposes a 64-channel x 32-pixel tile of one image row through shared memory: reads are
+// coalesced along w, writes along c (128 bytes per pixel).  HBM bound: 4 B read + 2 NPASS B written per element.
+template <int NPASS, bool TERNARISE>
+__global__ void __launch_bounds__(256) nhwc_split_kernel(const float* __restrict__ x, int C, int H, int W,
+                                                         __nv_bfloat16* __restrict__ xs, int64_t term_stride, float lo,
+                                                         float hi) {
+    __shared__ float tile[64][33];
+    const int w0 = blockIdx.x * 32, c0 = blockIdx.y * 64;
+    const int64_t nh = blockIdx.z;  // n * H + h
+    const int64_t n = nh / H;
+    const int h = static_cast<int>(nh - n * H);
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = ty + 8 * i, w = w0 + tx;
+        tile[c][tx] = (w < W) ? __ldg(x + ((n * C + c0 + c) * H + h) * static_cast<int64_t>(W) + w) : 0.0f;
+    }
+    __syncthreads();
+    const int chunk = threadIdx.x & 7, pw = threadIdx.x >> 3;  // 8 channels of pixel (w0 + pw)
+    if (w0 + pw >= W) return;
+    uint32_t packed[NPASS][4];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        uint16_t term[NPASS];
+        split_terms<NPASS, TERNARISE>(tile[chunk * 8 + e][pw], lo, hi, term);
+#pragma unroll
+        for (int q = 0; q < NPASS; ++q) {
+            if (e & 1) packed[q][e >> 1] |= static_cast<uint32_t>(term[q]) << 16;
+            else packed[q][e >> 1] = term[q];
+        }
+    }
+    const int64_t off = ((n * H + h) * static_cast<int64_t>(W) + w0 + pw) * C + c0 + chunk * 8;
+#pragma unroll
+    for (int q = 0; q < NPASS; ++q)
+        *reinterpret_cast<uint4*>(xs + q * term_stride + off) = make_uint4(packed[q][0], packed[q][1], packed[q][2], packed[q][3]);
+}
+
+// [M][C][taps] -> [M][taps][C]: filters in tap-major order for the channels-last path.
+__global__ void permute_filters_kernel(const float* __restrict__ w, int64_t M, int C, int taps, float* __restrict__ out) {
+    const int64_t total = M * C * taps;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int c = static_cast<int>(i % C);
+        const int t = static_cast<int>((i / C) % taps);
+        const int64_t m = i / (static_cast<int64_t>(C) * taps);
+        out[i] = __ldg(w + (m * C + c) * taps + t);
+    }
+}
+
 struct ConvArgs {
     const void* dense_w = nullptr;  // split dense weights (float filters) instead of packed planes
     const float* x;
@@ -40,7 +90,12 @@ struct ConvArgs {
     void* ws;
     size_t ws_bytes;
     cudaStream_t st;
+    int32_t weight_order = 0;  // TBN_CONV_WEIGHTS_*
 };
+
+size_t xs_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int npass) {
+    return static_cast<size_t>(round_up(static_cast<int64_t>(npass) * N * H * W * C * 2, 256));
+}
 
 size_t table_bytes(int64_t K_pad) { return static_cast<size_t>(round_up(K_pad * static_cast<int64_t>(sizeof(int2)), 256)); }
 
@@ -63,7 +118,11 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     TBN_REQUIRE(K < (1LL << 24) && a.C * a.H * a.W < (1LL << 31) && M < (1LL << 31) && OH * OW < (1LL << 31),
                 TBN_INVALID_SHAPE, "conv2d: problem too large");
     const int64_t K_pad = round_up(K, 128), N_pad = round_up(N, 8), M_pad = round_up(M, tc::BM);
-    const size_t need = table_bytes(K_pad) + scratch_bytes();
+    const bool fast = a.weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR;
+    TBN_REQUIRE(a.weight_order == TBN_CONV_WEIGHTS_REFERENCE || fast, TBN_INVALID_ARGUMENT, "conv2d: unknown weight order");
+    TBN_REQUIRE(!fast || a.C % 64 == 0, TBN_INVALID_ARGUMENT,
+                "conv2d: tap-major weights need a channel count that is a multiple of 64");
+    const size_t need = (fast ? xs_bytes(a.N, a.C, a.H, a.W, npass) : table_bytes(K_pad)) + scratch_bytes();
     TBN_REQUIRE(a.ws && a.ws_bytes >= need, TBN_INVALID_ARGUMENT,
                 "conv2d: workspace too small (see tbn_conv2d_workspace_bytes)");
     TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.ws) % 128 == 0, TBN_INVALID_ARGUMENT,
@@ -77,10 +136,27 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     TBN_REQUIRE(encode != nullptr, TBN_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
 
     int2* table = static_cast<int2*>(a.ws);
-    conv_tap_table_kernel<<<static_cast<unsigned>((K_pad + 127) / 128), 128, 0, a.st>>>(
-        table, static_cast<int>(K), static_cast<int>(K_pad), static_cast<int>(a.H), static_cast<int>(a.W),
-        static_cast<int>(a.kh), static_cast<int>(a.kw), a.dh, a.dw);
-    int32_t rc = launched("conv_tap_table_kernel");
+    __nv_bfloat16* xs = static_cast<__nv_bfloat16*>(a.ws);
+    const int64_t term_stride = a.N * a.H * a.W * a.C;
+    int32_t rc;
+    if (fast) {
+        TBN_REQUIRE(a.H * a.N < (1LL << 31) && a.W <= 65535LL * 32, TBN_INVALID_SHAPE, "conv2d: input too large for the pre-pass grid");
+        dim3 grid(static_cast<unsigned>((a.W + 31) / 32), static_cast<unsigned>(a.C / 64), static_cast<unsigned>(a.N * a.H));
+        profile_begin(kProfSplit, a.st);
+        if (tern_act) nhwc_split_kernel<1, true><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(a.H),
+                                                                        static_cast<int>(a.W), xs, term_stride, lo, hi);
+        else if (npass == 1) nhwc_split_kernel<1, false><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(a.H),
+                                                                               static_cast<int>(a.W), xs, term_stride, 0.f, 0.f);
+        else nhwc_split_kernel<2, false><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(a.H),
+                                                               static_cast<int>(a.W), xs, term_stride, 0.f, 0.f);
+        profile_end(kProfSplit, a.st);
+        rc = launched("nhwc_split_kernel");
+    } else {
+        conv_tap_table_kernel<<<static_cast<unsigned>((K_pad + 127) / 128), 128, 0, a.st>>>(
+            table, static_cast<int>(K), static_cast<int>(K_pad), static_cast<int>(a.H), static_cast<int>(a.W),
+            static_cast<int>(a.kh), static_cast<int>(a.kw), a.dh, a.dw);
+        rc = launched("conv_tap_table_kernel");
+    }
     if (rc) return rc;
 
     const int bn = pick_bn(N);
@@ -111,7 +187,15 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.err_word = device_error_word();
     p.c_vec_ok = 0;
     set_segments(p, npass);
-    p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.ws) + table_bytes(K_pad));
+    p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.ws) +
+                                          (fast ? xs_bytes(a.N, a.C, a.H, a.W, npass) : table_bytes(K_pad)));
+    p.conv.xs = xs;
+    p.conv.xs_term_stride = term_stride;
+    p.conv.kw = static_cast<int>(a.kw);
+    p.conv.taps = static_cast<int>(a.kh * a.kw);
+    p.conv.dh = a.dh;
+    p.conv.dw = a.dw;
+    p.conv.cblocks = static_cast<int>(a.C / 64);
     p.conv.x = a.x;
     p.conv.table = table;
     p.conv.C = static_cast<int>(a.C);
@@ -125,17 +209,24 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.conv.pw = a.pw;
     p.conv.act_lo = lo;
     p.conv.act_hi = hi;
+    const bool ternary_w = a.pos != nullptr;
+    if (fast) {
+        if (a.dense_w) {
+            set_segments(p, 3);
+            return dispatch_bn<2, false, 2, false, true>(bn, maps, p, a.st);
+        }
+        if (tern_act || npass == 1)
+            return ternary_w ? dispatch_bn<1, true, 2, false>(bn, maps, p, a.st) : dispatch_bn<1, false, 2, false>(bn, maps, p, a.st);
+        return ternary_w ? dispatch_bn<2, true, 2, false>(bn, maps, p, a.st) : dispatch_bn<2, false, 2, false>(bn, maps, p, a.st);
+    }
     if (a.dense_w) {
         set_segments(p, 3);
-        return dispatch_bn<2, false, true, false, true>(bn, maps, p, a.st);
+        return dispatch_bn<2, false, 1, false, true>(bn, maps, p, a.st);
     }
-    const bool ternary_w = a.pos != nullptr;
-    if (tern_act) return dispatch_bn<1, false, true, true>(bn, maps, p, a.st);
+    if (tern_act) return dispatch_bn<1, false, 1, true>(bn, maps, p, a.st);
     if (npass == 1)
-        return ternary_w ? dispatch_bn<1, true, true, false>(bn, maps, p, a.st)
-                         : dispatch_bn<1, false, true, false>(bn, maps, p, a.st);
-    return ternary_w ? dispatch_bn<2, true, true, false>(bn, maps, p, a.st)
-                     : dispatch_bn<2, false, true, false>(bn, maps, p, a.st);
+        return ternary_w ? dispatch_bn<1, true, 1, false>(bn, maps, p, a.st) : dispatch_bn<1, false, 1, false>(bn, maps, p, a.st);
+    return ternary_w ? dispatch_bn<2, true, 1, false>(bn, maps, p, a.st) : dispatch_bn<2, false, 1, false>(bn, maps, p, a.st);
 }
 
 }  // namespace
@@ -145,42 +236,54 @@ using namespace tbn_cuda;
 
 extern "C" {
 
-size_t tbn_conv2d_workspace_bytes(int64_t C, int64_t kh, int64_t kw) {
-    if (C <= 0 || kh <= 0 || kw <= 0) return 0;
-    return table_bytes(round_up(C * kh * kw, 128)) + static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float);
+size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t kh, int64_t kw, int32_t weight_order) {
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0) return 0;
+    const size_t front = weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR ? xs_bytes(N, C, H, W, 2) : table_bytes(round_up(C * kh * kw, 128));
+    return front + static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float);
+}
+
+int32_t tbn_permute_filters(const float* d_w, int64_t M, int64_t C, int64_t taps, float* d_out, void* stream) {
+    TBN_REQUIRE(M > 0 && C > 0 && taps > 0 && C < (1LL << 31) && taps < (1LL << 31), TBN_INVALID_SHAPE,
+                "tbn_permute_filters: bad dimensions");
+    TBN_REQUIRE(d_w && d_out && d_w != d_out, TBN_INVALID_ARGUMENT, "tbn_permute_filters: null or aliased pointers");
+    const int64_t total = M * C * taps;
+    const int grid = static_cast<int>(std::max<int64_t>(1, std::min((total + 255) / 256, static_cast<int64_t>(std::max(sm_count(), 1)) * 16)));
+    permute_filters_kernel<<<grid, 256, 0, as_stream(stream)>>>(d_w, M, static_cast<int>(C), static_cast<int>(taps), d_out);
+    return launched("permute_filters_kernel");
 }
 
 int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, const uint32_t* d_neg,
                        const uint32_t* d_pos, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph,
                        int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale, const float* d_bias,
-                       const float* d_residual, float* d_y, int32_t mode, uint32_t epilogue, void* d_workspace,
-                       size_t workspace_bytes, void* stream) {
+                       const float* d_residual, float* d_y, int32_t mode, uint32_t epilogue, int32_t weight_order,
+                       void* d_workspace, size_t workspace_bytes, void* stream) {
     TBN_REQUIRE(mode == TBN_MODE_AUTO || mode == TBN_MODE_TC_BF16X1 || mode == TBN_MODE_TC_BF16X2, TBN_NOT_IMPLEMENTED,
                 "tbn_conv2d_fxb: modes are AUTO (= two bf16 terms), TC_BF16X1 and TC_BF16X2");
     const ConvArgs a{nullptr, d_x, N, C, H, W, d_neg, d_pos, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
                      Epilogue{d_alpha, d_bias, d_residual, scale, epilogue}, d_y, d_workspace, workspace_bytes,
-                     as_stream(stream)};
+                     as_stream(stream), weight_order};
     return conv_common(a, mode == TBN_MODE_TC_BF16X1 ? 1 : 2, false, 0.f, 0.f);
 }
 
 int32_t tbn_conv2d_tbn(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float lo, float hi,
                        const uint32_t* d_neg, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph,
                        int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale, const float* d_bias,
-                       float* d_y, uint32_t epilogue, void* d_workspace, size_t workspace_bytes, void* stream) {
+                       float* d_y, uint32_t epilogue, int32_t weight_order, void* d_workspace, size_t workspace_bytes,
+                       void* stream) {
     const ConvArgs a{nullptr, d_x, N, C, H, W, d_neg, nullptr, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
                      Epilogue{d_alpha, d_bias, nullptr, scale, epilogue & ~TBN_EPI_ADD_RESIDUAL}, d_y, d_workspace,
-                     workspace_bytes, as_stream(stream)};
+                     workspace_bytes, as_stream(stream), weight_order};
     return conv_common(a, 1, true, lo, hi);
 }
 
 int32_t tbn_conv2d_f32(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, const void* d_packed_w, int64_t M_out,
                        int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw,
-                       const float* d_bias, const float* d_residual, float* d_y, uint32_t epilogue, void* d_workspace,
-                       size_t workspace_bytes, void* stream) {
+                       const float* d_bias, const float* d_residual, float* d_y, uint32_t epilogue, int32_t weight_order,
+                       void* d_workspace, size_t workspace_bytes, void* stream) {
     TBN_REQUIRE(d_packed_w != nullptr, TBN_INVALID_ARGUMENT, "tbn_conv2d_f32: null weights");
     const ConvArgs a{d_packed_w, d_x, N, C, H, W, nullptr, nullptr, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
                      Epilogue{nullptr, d_bias, d_residual, 1.0f, epilogue}, d_y, d_workspace, workspace_bytes,
-                     as_stream(stream)};
+                     as_stream(stream), weight_order};
     return conv_common(a, 2, false, 0.f, 0.f);
 }
 

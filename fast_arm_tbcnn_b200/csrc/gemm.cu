@@ -270,17 +270,17 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     if (dense_w) {
         p.num_kb = static_cast<int>(K_pad / tc::BK);
         set_segments(p, 3);  // three MMA passes per k-block
-        return dispatch_bn<2, false, false, false, true>(bn, maps, p, st);
+        return dispatch_bn<2, false, 0, false, true>(bn, maps, p, st);
     }
     const bool ternary_w = d_pos != nullptr;
     if (npass == 1)
-        return ternary_w ? dispatch_bn<1, true, false, false>(bn, maps, p, st)
-                         : dispatch_bn<1, false, false, false>(bn, maps, p, st);
+        return ternary_w ? dispatch_bn<1, true, 0, false>(bn, maps, p, st)
+                         : dispatch_bn<1, false, 0, false>(bn, maps, p, st);
     if (npass == 2)
-        return ternary_w ? dispatch_bn<2, true, false, false>(bn, maps, p, st)
-                         : dispatch_bn<2, false, false, false>(bn, maps, p, st);
-    return ternary_w ? dispatch_bn<3, true, false, false>(bn, maps, p, st)
-                     : dispatch_bn<3, false, false, false>(bn, maps, p, st);
+        return ternary_w ? dispatch_bn<2, true, 0, false>(bn, maps, p, st)
+                         : dispatch_bn<2, false, 0, false>(bn, maps, p, st);
+    return ternary_w ? dispatch_bn<3, true, 0, false>(bn, maps, p, st)
+                     : dispatch_bn<3, false, 0, false>(bn, maps, p, st);
 }
 
 int32_t gemm_simt(const float* d_a, int64_t M, int64_t K, int64_t lda, bool ternarise_act, float act_lo, float act_hi,

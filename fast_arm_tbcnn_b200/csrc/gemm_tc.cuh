@@ -8,9 +8,12 @@
 //               term against the same unpacked weight tile, fp32 accumulators double-buffered in
 //               tensor memory
 //   warps 2-9   operand build: packed words smem -> registers -> +-1/0 bf16 written into the swizzled
-//               K-major operand tile; -- CONV mode -- also the activation operand: gather from the
-//               NCHW fp32 input (the im2col matrix is never materialised), split into bf16 terms (or
-//               ternarise), write the swizzled tile
+//               K-major operand tile; -- CONV modes -- also the activation operand (the im2col matrix is
+//               never materialised): either gathered element-wise from the NCHW fp32 input, split into
+//               bf16 terms (or ternarised) and written to the swizzled tile (any geometry), or -- when the
+//               channel count is a multiple of 64 -- copied with 16-byte cp.async from a channels-last
+//               bf16 copy of the input that a cheap pre-pass has already split (one filter tap and 64
+//               channels per k-block)
 //   warps 10-13 epilogue: tcgen05.ld, alpha / scale / bias / residual / ReLU, store (row-major or NCHW)
 //
 // The tensor cores add into the fp32 accumulator with truncation, an error that grows linearly with the
@@ -89,7 +92,7 @@ constexpr int kProducerWarp = 0, kMmaWarp = 1;
 constexpr int kBuildThreads = 256, kEpilogueThreads = 128;
 constexpr int kThreads = 64 + kBuildThreads + kEpilogueThreads;
 constexpr int kGroupM = 8;      // rasterisation: 8 m-tiles share a sweep over n for L2 reuse
-constexpr int kWordStages = 2;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
+constexpr int kWordStages = 4;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
 constexpr int kAuxBarrierBytes = 1024;
 constexpr int kMaxOutputs = 8;           // destinations of the multi-destination epilogue (GPUs of one box)
 constexpr int kStageOutBytes = 4 * 2048;  // per epilogue warp: 32 rows x 16 fp32 transposition buffer
@@ -126,6 +129,11 @@ struct ConvGeom {
     int C, H, W, OH, OW;
     int sh, sw, ph, pw;
     float act_lo, act_hi;  // thresholds when the activations are ternarised (TBN mode)
+    // Channels-last fast path (AMODE 2): xs[term][img][h][w][c] bf16, K ordered tap-major:
+    // k = (i*kw + j)*C + c, so k-block kb covers tap kb / cblocks and channels [64*(kb % cblocks), +64).
+    const __nv_bfloat16* xs;
+    int64_t xs_term_stride;  // elements between the bf16 terms
+    int kw, taps, dh, dw, cblocks;
 };
 
 struct Params {
@@ -162,12 +170,17 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 
 // tmap_a: split activations (GEMM mode).  tmap_neg / tmap_pos: packed word planes; in DENSE mode tmap_neg is
 // the map of the split weights [2][N_pad][K_pad] instead.
-template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT, bool DENSE>
+// AMODE: source of the activation operand.  0 = TMA from pre-split [terms][M][K] (plain GEMM);
+// 1 = element-wise gather from NCHW fp32 (any convolution geometry); 2 = cp.async from the channels-last
+// bf16 copy (convolutions with C % 64 == 0).
+template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_neg,
                                                               const __grid_constant__ CUtensorMap tmap_pos,
                                                               const Params p) {
     using C = Cfg<BN, NPASS, TERNARY, DENSE>;
+    constexpr bool CONV = AMODE != 0;
+    constexpr bool FAST = AMODE == 2;
     static_assert(!DENSE || (NPASS == 2 && !TERNARY && !TERN_ACT), "dense weights use the two-term split on both sides");
     // Which operands arrive by TMA (signalled on full_a) and which are built by the build warps (full_b).
     constexpr bool kTmaOperands = !CONV || DENSE;
@@ -346,14 +359,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         uint32_t phase = 0, wphase = 0;
         bool ok = true;
         uint4 wn = make_uint4(0u, 0u, 0u, 0u), wp = make_uint4(0u, 0u, 0u, 0u);
+        // FAST: oldest stage whose copies are in flight and whose arrive is still owed, and how many are owed.
+        constexpr int kCopyLag = C::STAGES >= 4 ? 2 : 1;
+        int pending_stage = 0, pending_count = 0;
         for (int t = blockIdx.x; kBuiltOperands && t < total_tiles && ok; t += gridDim.x) {
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-            // Window origin of this thread's output pixel (CONV mode).
+            // Window origin of this thread's output pixel (CONV modes).  Element-wise gather: one pixel per
+            // thread (lanes = consecutive pixels).  Channels-last copy: four pixels per thread, rows
+            // (r >> 3) + 32*j, and ONE 16-byte chunk r & 7, so that 8 lanes cover one pixel's 128 bytes and a
+            // warp reads 512 contiguous bytes.
             int ih0 = 0, iw0 = 0;
             bool row_valid = false;
             const float* xwin = nullptr;
-            if (CONV) {
+            int f_ih0[4], f_iw0[4];
+            int64_t f_img[4];
+            bool f_valid[4];
+            if (CONV && !FAST) {
                 const int64_t m = static_cast<int64_t>(tm) * BM + a_row;
                 row_valid = m < p.M;
                 const int hw = p.conv.OH * p.conv.OW;
@@ -364,6 +386,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 iw0 = ow * p.conv.sw - p.conv.pw;
                 xwin = p.conv.x + img * p.conv.C * p.conv.H * p.conv.W +
                        static_cast<int64_t>(ih0) * p.conv.W + iw0;
+            }
+            if (FAST) {
+                const int hw = p.conv.OH * p.conv.OW;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t m = static_cast<int64_t>(tm) * BM + (r >> 3) + 32 * j;
+                    f_valid[j] = m < p.M;
+                    const int64_t img = m / hw;
+                    const int pix = static_cast<int>(m - img * hw);
+                    const int oh = pix / p.conv.OW, ow = pix - oh * p.conv.OW;
+                    f_ih0[j] = oh * p.conv.sh - p.conv.ph;
+                    f_iw0[j] = ow * p.conv.sw - p.conv.pw;
+                    f_img[j] = img * p.conv.H * p.conv.W;
+                }
             }
             for (int kb = 0; kb < p.num_kb; ++kb) {
                 if (!DENSE && (kb & 1) == 0) {
@@ -386,7 +422,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     }
                 }
                 float av[32];
-                if (CONV) {
+                if (CONV && !FAST) {
                     // Issue this k-block's 32 gathers before waiting for the stage, so that their latency
                     // overlaps the wait.  Lanes hold consecutive output pixels: coalesced for stride 1.
 #pragma unroll
@@ -420,6 +456,50 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8<TERNARY>(nb, pb);
                     }
                 }
+                if (FAST) {
+                    // One filter tap and 64 channels per k-block: this thread copies its 16-byte chunk (8 channels)
+                    // of four pixels per term, or zeros where the tap falls outside the image.
+                    const int tap = kb / p.conv.cblocks;
+                    const int c0 = (kb - tap * p.conv.cblocks) * BK + (r & 7) * 8;
+                    const int ti = tap / p.conv.kw, tj = tap - ti * p.conv.kw;
+                    const int dy = ti * p.conv.dh, dx = tj * p.conv.dw;
+                    const bool tap_valid = tap < p.conv.taps;
+                    const uint32_t a_base = base + stage * C::STAGE_BYTES + C::B_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int row = (r >> 3) + 32 * j;
+                        const int ih = f_ih0[j] + dy, iw = f_iw0[j] + dx;
+                        const bool inside = f_valid[j] && tap_valid &&
+                                            static_cast<unsigned>(ih) < static_cast<unsigned>(p.conv.H) &&
+                                            static_cast<unsigned>(iw) < static_cast<unsigned>(p.conv.W);
+                        const __nv_bfloat16* src =
+                            inside ? p.conv.xs + (f_img[j] + static_cast<int64_t>(ih) * p.conv.W + iw) * p.conv.C + c0
+                                   : p.conv.xs;
+                        const uint32_t dst = a_base + row * 128 + (((r & 7) ^ (row & 7)) << 4);
+#pragma unroll
+                        for (int q = 0; q < NPASS; ++q)
+                            ptx::cp_async_16(dst + q * A_TILE_BYTES, src + q * p.conv.xs_term_stride, inside ? 16u : 0u);
+                    }
+                    ptx::cp_async_commit();
+                    // The arrive for a stage is deferred by kCopyLag k-blocks, so that several stages of copies
+                    // are in flight and their latency overlaps: wait_group leaves the newest kCopyLag groups
+                    // pending, i.e. the group of the stage being released has landed; the writer then fences
+                    // and signals.
+                    if (pending_count == kCopyLag) {
+                        ptx::cp_async_wait<kCopyLag>();
+                        ptx::fence_proxy_async_smem();
+                        ptx::mbar_arrive(bar_full_b + 8 * pending_stage);
+                        if (++pending_stage == C::STAGES) pending_stage = 0;
+                    } else {
+                        if (pending_count == 0) pending_stage = stage;
+                        ++pending_count;
+                    }
+                    if (++stage == C::STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                    continue;
+                }
                 if (CONV) {
                     uint8_t* a_tile = stage_ptr + C::B_BYTES + a_row * 128;
 #pragma unroll
@@ -448,6 +528,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     stage = 0;
                     phase ^= 1u;
                 }
+            }
+        }
+        if (FAST && ok && pending_count > 0) {  // the deferred arrives of the last stages
+            ptx::cp_async_wait<0>();
+            ptx::fence_proxy_async_smem();
+            for (; pending_count > 0; --pending_count) {
+                ptx::mbar_arrive(bar_full_b + 8 * pending_stage);
+                if (++pending_stage == C::STAGES) pending_stage = 0;
             }
         }
     } else {
@@ -661,25 +749,25 @@ inline void set_segments(tc::Params& p, int npass) {
     p.kb_per_seg = (p.num_kb + p.num_seg - 1) / p.num_seg;
 }
 
-template <int BN, int NPASS, bool TERNARY, bool CONV, bool TERN_ACT, bool DENSE = false>
+template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE = false>
 int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
     using C = tc::Cfg<BN, NPASS, TERNARY, DENSE>;
-    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, CONV, TERN_ACT, DENSE>;
+    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>;
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
     profile_begin(kProfGemm, st);
     kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, p);
     profile_end(kProfGemm, st);
-    return launched(CONV ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
+    return launched(AMODE ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
 }
 
-template <int NPASS, bool TERNARY, bool CONV, bool TERN_ACT, bool DENSE = false>
+template <int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE = false>
 int32_t dispatch_bn(int bn, const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
     switch (bn) {
-        case 256: return launch_tc<256, NPASS, TERNARY, CONV, TERN_ACT, DENSE>(maps, p, st);
-        case 128: return launch_tc<128, NPASS, TERNARY, CONV, TERN_ACT, DENSE>(maps, p, st);
-        default: return launch_tc<64, NPASS, TERNARY, CONV, TERN_ACT, DENSE>(maps, p, st);
+        case 256: return launch_tc<256, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>(maps, p, st);
+        case 128: return launch_tc<128, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>(maps, p, st);
+        default: return launch_tc<64, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>(maps, p, st);
     }
 }
 

@@ -84,6 +84,76 @@ __global__ void __launch_bounds__(128) pack_kn_kernel(const float* __restrict__ 
     }
 }
 
+// Layout KN, wide variant (rows 16-byte aligned, N % 4 == 0): each lane owns FOUR adjacent columns and reads
+// them as one float4, so a warp reads 512 contiguous bytes per weight row -- wide enough for DRAM to run
+// near its streaming rate -- and packs a 128(k) x 128(n) tile.
+template <bool TERNARY>
+__global__ void __launch_bounds__(128) pack_kn_vec4_kernel(const float* __restrict__ w, int64_t K, int64_t N,
+                                                           int64_t ldw, float lo, float hi, int ge,
+                                                           uint32_t* __restrict__ neg_words,
+                                                           uint32_t* __restrict__ pos_words, int64_t KW,
+                                                           int64_t N_pad, float* __restrict__ part_sum,
+                                                           float* __restrict__ part_cnt) {
+    const int lane = threadIdx.x & 31;
+    const int64_t chunk = static_cast<int64_t>(blockIdx.y) * 4 + (threadIdx.x >> 5);
+    const int64_t n = static_cast<int64_t>(blockIdx.x) * 128 + lane * 4;
+    if (chunk * kChunkK >= KW * 32 || n >= N_pad) return;
+    const int64_t k0 = chunk * kChunkK;
+    uint32_t negw[4][4], posw[4][4];
+    float sum[4] = {0.f, 0.f, 0.f, 0.f}, cnt[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) negw[j][wi] = posw[j][wi] = 0u;
+    if (n < N) {
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float4 v[16];
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const int64_t k = k0 + wi * 32 + half * 16 + r;
+                    v[r] = (k < K) ? __ldg(reinterpret_cast<const float4*>(w + k * ldw + n))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const int64_t k = k0 + wi * 32 + half * 16 + r;
+                    if (k < K) {
+                        const float e[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t c = classify<TERNARY>(e[j], lo, hi, ge);
+                            negw[j][wi] |= (c & 1u) << (half * 16 + r);
+                            if (TERNARY) {
+                                posw[j][wi] |= (c >> 1) << (half * 16 + r);
+                                if (c) {
+                                    sum[j] += fabsf(e[j]);
+                                    cnt[j] += 1.0f;
+                                }
+                            } else {
+                                sum[j] += fabsf(e[j]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (n + j >= N_pad) break;
+        const int64_t widx = (n + j) * KW + chunk * 4;
+        *reinterpret_cast<uint4*>(neg_words + widx) = make_uint4(negw[j][0], negw[j][1], negw[j][2], negw[j][3]);
+        if (TERNARY) *reinterpret_cast<uint4*>(pos_words + widx) = make_uint4(posw[j][0], posw[j][1], posw[j][2], posw[j][3]);
+    }
+    if (part_sum && n < N) {
+        *reinterpret_cast<float4*>(part_sum + chunk * N + n) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+        if (TERNARY) *reinterpret_cast<float4*>(part_cnt + chunk * N + n) = make_float4(cnt[0], cnt[1], cnt[2], cnt[3]);
+    }
+}
+
 // Layout NK: W[n*ldw + k] (k contiguous).  One warp packs one 128-k chunk of one column:
 // four coalesced 128 B reads, four ballots.
 template <bool TERNARY>
@@ -221,7 +291,13 @@ int32_t quant_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t 
         if (TERNARY) part_cnt = part_sum + chunks * N;
     }
     const unsigned gy = static_cast<unsigned>((chunks + 3) / 4);
-    if (layout == TBN_LAYOUT_KN) {
+    const bool wide = layout == TBN_LAYOUT_KN && N % 4 == 0 && ldw % 4 == 0 && reinterpret_cast<uintptr_t>(d_w) % 16 == 0 &&
+                      (!part_sum || reinterpret_cast<uintptr_t>(part_sum) % 16 == 0) && N >= 128;
+    if (wide) {
+        dim3 grid(static_cast<unsigned>((N_pad + 127) / 128), gy);
+        pack_kn_vec4_kernel<TERNARY><<<grid, 128, 0, st>>>(d_w, K, N, ldw, lo, hi, ge, d_neg, d_pos, KW, N_pad, part_sum,
+                                                           part_cnt);
+    } else if (layout == TBN_LAYOUT_KN) {
         dim3 grid(static_cast<unsigned>((N_pad + 31) / 32), gy);
         pack_kn_kernel<TERNARY><<<grid, 128, 0, st>>>(d_w, K, N, ldw, lo, hi, ge, d_neg, d_pos, KW, N_pad, part_sum,
                                                       part_cnt);

@@ -24,7 +24,7 @@ from . import capi
 
 
 class Session:
-    def __init__(self, graph, device=None, fuse=True):
+    def __init__(self, graph, device=None, fuse=True, fast=True):
         import torch
         self.torch = torch
         self.graph = graph
@@ -32,6 +32,7 @@ class Session:
         self.device = torch.device("cuda", self.L.init(device))
         self.quantization = False
         self.fuse = fuse
+        self.fast = fast  # channels-last convolution path where the channel count allows it
         self.inputs = {}
         self.values = {}
         self.weights = {}
@@ -42,7 +43,10 @@ class Session:
             if name in graph["binary"]:
                 self.weights[name] = self._pack(t)
             elif name in conv_w:   # float filters: split once into two bf16 terms
-                self.weights[name] = {"shape": tuple(t.shape), "split": self.L.dense_pack(t.reshape(t.shape[0], -1), capi.LAYOUT_NK)}
+                order = capi.CONV_WEIGHTS_TAP_MAJOR if (fast and t.shape[1] % 64 == 0) else capi.CONV_WEIGHTS_REFERENCE
+                flat = self.L.permute_filters(t) if order else t.reshape(t.shape[0], -1)
+                self.weights[name] = {"shape": tuple(t.shape), "order": order,
+                                      "split": self.L.dense_pack(flat, capi.LAYOUT_NK)}
             elif name in gemm_w:   # float Gemm B [K, N]
                 self.weights[name] = {"shape": tuple(t.shape), "split": self.L.dense_pack(t, capi.LAYOUT_KN)}
             else:
@@ -53,13 +57,14 @@ class Session:
     def _pack(self, w):
         L = self.L
         if w.dim() == 4:  # conv [M, C, kh, kw] -> K = C*kh*kw along the row: layout NK
-            flat = w.reshape(w.shape[0], -1)
+            order = capi.CONV_WEIGHTS_TAP_MAJOR if (self.fast and w.shape[1] % 64 == 0) else capi.CONV_WEIGHTS_REFERENCE
+            flat = L.permute_filters(w) if order else w.reshape(w.shape[0], -1)
             words_gt, alpha = L.quant_pack_binary(flat, capi.LAYOUT_NK, 0.0, False)
             # TBN mode uses the scale summed sequentially over the given weights, exactly as the reference
             # Session does (model.hpp:388-394); given a dequantised model (+-alpha weights) the whole Conv is
             # then bit-equal to the reference.
             alpha_seq = L.channel_abs_mean(flat.contiguous())
-            return {"shape": tuple(w.shape), "words": words_gt, "alpha": alpha, "alpha_tbn": alpha_seq}
+            return {"shape": tuple(w.shape), "words": words_gt, "alpha": alpha, "alpha_tbn": alpha_seq, "order": order}
         words_gt, alpha = L.quant_pack_binary(w, capi.LAYOUT_KN, 0.0, False)  # Gemm B [K, N]
         return {"shape": tuple(w.shape), "words": words_gt, "alpha": alpha}
 
@@ -156,10 +161,12 @@ class Session:
         w = self.weights[n["inputs"][1]]
         bias = self.weights[n["inputs"][2]]["dense"] if len(n["inputs"]) > 2 else None
         out_name = n["outputs"][0]
-        ws = self._workspace("conv", L.h.tbn_conv2d_workspace_bytes(w["shape"][1], w["shape"][2], w["shape"][3]))
+        order = w.get("order", capi.CONV_WEIGHTS_REFERENCE)
+        ws = self._workspace("conv", L.h.tbn_conv2d_workspace_bytes(x.shape[0], x.shape[1], x.shape[2], x.shape[3],
+                                                                    w["shape"][2], w["shape"][3], order))
         if self.quantization and "words" in w:
             y = L.conv2d_tbn(x, w["words"], w["shape"], p, alpha=w["alpha_tbn"], bias=bias,
-                             epilogue=capi.EPI_BIAS_BEFORE_ALPHA, workspace=ws)
+                             epilogue=capi.EPI_BIAS_BEFORE_ALPHA, workspace=ws, order=order)
             return out_name, y
         # float x binary: fold a following Relu (and Add + Relu of a residual block) into the epilogue.
         epilogue, residual = 0, None
@@ -180,9 +187,10 @@ class Session:
                     out_name = nodes[idx + 2]["outputs"][0]
         if "words" in w:
             y = L.conv2d_fxb(x, w["words"], w["shape"], p, alpha=w["alpha"], bias=bias, residual=residual,
-                             epilogue=epilogue, workspace=ws)
+                             epilogue=epilogue, workspace=ws, order=order)
         else:
-            y = L.conv2d_f32(x, w["split"], w["shape"], p, bias=bias, residual=residual, epilogue=epilogue, workspace=ws)
+            y = L.conv2d_f32(x, w["split"], w["shape"], p, bias=bias, residual=residual, epilogue=epilogue, workspace=ws,
+                             order=order)
         return out_name, y
 
     def _gemm(self, n, vals):

@@ -27,6 +27,7 @@ struct PackedWeights {
     int64_t K = 0, N = 0;
     Shape weight_shape;  // original shape ([K,N] matrix or [M,C,kh,kw] filter bank)
     bool ternary = false;
+    bool tap_major = false;  // filter banks with C % 64 == 0 are packed in (i, j, c) order for the channels-last path
 };
 // fp32 weights: a [K,N] matrix (Gemm B) or a [M,C,kh,kw] filter bank.  `ge_zero` selects the Session's
 // sign rule (w >= thr is +1) instead of quantize_to_binary's (w > thr).
@@ -40,6 +41,7 @@ struct DenseWeights {
     Tensor split;        // [2][ceil8(N)][ceil128(K)] bf16
     int64_t K = 0, N = 0;
     Shape weight_shape;
+    bool tap_major = false;
 };
 DenseWeights pack_dense_weights(const Tensor& weights);  // [K,N] matrix or [M,C,kh,kw] filter bank
 // C = alpha * A W + bias and the float-filter convolution, fp32 accuracy.

@@ -92,10 +92,19 @@ PackedWeights pack_impl(const Tensor& weights, bool ternary, float lo, float hi,
     p.ternary = ternary;
     int layout;
     int64_t ldw;
+    Tensor reordered;
+    const float* src = dptr(weights);
     if (d.size() == 2) {
         p.K = d[0]; p.N = d[1]; layout = TBN_LAYOUT_KN; ldw = p.N;
     } else {
         p.N = d[0]; p.K = d[1] * d[2] * d[3]; layout = TBN_LAYOUT_NK; ldw = p.K;
+        if (d[1] % 64 == 0) {  // channels-last fast path: K ordered (i, j, c)
+            reordered = device_f32(Shape{p.N, p.K});
+            check(tbn_permute_filters(src, d[0], d[1], d[2] * d[3], static_cast<float*>(reordered.device_data()), nullptr));
+            reordered.mark_device_written();
+            src = dptr(reordered);
+            p.tap_major = true;
+        }
     }
     int64_t Kp = 0, Np = 0;
     check(tbn_packed_dims(p.K, p.N, &Kp, &Np));
@@ -105,12 +114,12 @@ PackedWeights pack_impl(const Tensor& weights, bool ternary, float lo, float hi,
     void* ws = workspace().get(ws_bytes);
     if (ternary) {
         p.pos = Tensor(Shape{Np, Kp / 32}, DataType::UINT32, DeviceType::CUDA);
-        check(tbn_quant_pack_ternary(dptr(weights), p.K, p.N, ldw, layout, lo, hi, nullptr,
+        check(tbn_quant_pack_ternary(src, p.K, p.N, ldw, layout, lo, hi, nullptr,
                                      static_cast<uint32_t*>(p.pos.device_data()), static_cast<uint32_t*>(p.neg.device_data()),
                                      static_cast<float*>(p.alpha.device_data()), ws, ws_bytes, nullptr));
         p.pos.mark_device_written();
     } else {
-        check(tbn_quant_pack_binary(dptr(weights), p.K, p.N, ldw, layout, lo, ge ? 1 : 0,
+        check(tbn_quant_pack_binary(src, p.K, p.N, ldw, layout, lo, ge ? 1 : 0,
                                     static_cast<uint32_t*>(p.neg.device_data()), static_cast<float*>(p.alpha.device_data()), ws,
                                     ws_bytes, nullptr));
     }
@@ -146,13 +155,22 @@ DenseWeights pack_dense_weights(const Tensor& weights) {
     w.weight_shape = weights.shape();
     int layout;
     int64_t ldw;
+    Tensor reordered;
+    const float* src = dptr(weights);
     if (d.size() == 2) {
         w.K = d[0]; w.N = d[1]; layout = TBN_LAYOUT_KN; ldw = w.N;
     } else {
         w.N = d[0]; w.K = d[1] * d[2] * d[3]; layout = TBN_LAYOUT_NK; ldw = w.K;
+        if (d[1] % 64 == 0) {
+            reordered = device_f32(Shape{w.N, w.K});
+            check(tbn_permute_filters(src, d[0], d[1], d[2] * d[3], static_cast<float*>(reordered.device_data()), nullptr));
+            reordered.mark_device_written();
+            src = dptr(reordered);
+            w.tap_major = true;
+        }
     }
     w.split = Tensor(Shape{static_cast<int64_t>(tbn_dense_pack_bytes(w.K, w.N))}, DataType::UINT8, DeviceType::CUDA);
-    check(tbn_dense_pack(dptr(weights), w.K, w.N, ldw, layout, w.split.device_data(), nullptr));
+    check(tbn_dense_pack(src, w.K, w.N, ldw, layout, w.split.device_data(), nullptr));
     w.split.mark_device_written();
     return w;
 }
@@ -311,14 +329,15 @@ Tensor conv2d_float_packed(const Tensor& x, const PackedWeights& w, const Tensor
     check_bias(bias, d.M);
     Tensor y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
     if (residual) TBN_CHECK(residual->shape() == y.shape(), InvalidShapeError, "residual must have the output's shape");
-    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.C, d.kh, d.kw);
+    const int32_t order = w.tap_major ? TBN_CONV_WEIGHTS_TAP_MAJOR : TBN_CONV_WEIGHTS_REFERENCE;
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.kh, d.kw, order);
     uint32_t epi = (relu_flag ? TBN_EPI_RELU : 0u) | (residual ? TBN_EPI_ADD_RESIDUAL : 0u);
     check(tbn_conv2d_fxb(dptr(x), d.N, d.C, d.H, d.W, static_cast<const uint32_t*>(w.neg.device_data()),
                          w.ternary ? static_cast<const uint32_t*>(w.pos.device_data()) : nullptr, d.M, d.kh, d.kw,
                          static_cast<int32_t>(p.stride_h), static_cast<int32_t>(p.stride_w), static_cast<int32_t>(p.pad_h),
                          static_cast<int32_t>(p.pad_w), static_cast<int32_t>(p.dilation_h), static_cast<int32_t>(p.dilation_w),
                          dptr(w.alpha), 1.0f, dptr_or_null(bias), dptr_or_null(residual), static_cast<float*>(y.device_data()),
-                         TBN_MODE_AUTO, epi, workspace().get(ws_bytes), ws_bytes, nullptr));
+                         TBN_MODE_AUTO, epi, order, workspace().get(ws_bytes), ws_bytes, nullptr));
     y.mark_device_written();
     return y;
 }
@@ -328,12 +347,13 @@ Tensor conv2d_tbn_packed(const Tensor& x, const PackedWeights& w, const Tensor* 
     const ConvDims d = conv_dims(x, w.weight_shape, p);
     check_bias(bias, d.M);
     Tensor y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
-    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.C, d.kh, d.kw);
+    const int32_t order = w.tap_major ? TBN_CONV_WEIGHTS_TAP_MAJOR : TBN_CONV_WEIGHTS_REFERENCE;
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.kh, d.kw, order);
     check(tbn_conv2d_tbn(dptr(x), d.N, d.C, d.H, d.W, -0.1f, 0.1f, static_cast<const uint32_t*>(w.neg.device_data()), d.M, d.kh,
                          d.kw, static_cast<int32_t>(p.stride_h), static_cast<int32_t>(p.stride_w), static_cast<int32_t>(p.pad_h),
                          static_cast<int32_t>(p.pad_w), static_cast<int32_t>(p.dilation_h), static_cast<int32_t>(p.dilation_w),
                          dptr_or_null(alpha), 1.0f, dptr_or_null(bias), static_cast<float*>(y.device_data()),
-                         bias_before_alpha ? TBN_EPI_BIAS_BEFORE_ALPHA : 0u, workspace().get(ws_bytes), ws_bytes, nullptr));
+                         bias_before_alpha ? TBN_EPI_BIAS_BEFORE_ALPHA : 0u, order, workspace().get(ws_bytes), ws_bytes, nullptr));
     y.mark_device_written();
     return y;
 }
@@ -380,13 +400,14 @@ Tensor conv2d_float_dense(const Tensor& x, const DenseWeights& w, const Tensor* 
     check_bias(bias, d.M);
     Tensor y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
     if (residual) TBN_CHECK(residual->shape() == y.shape(), InvalidShapeError, "residual must have the output's shape");
-    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.C, d.kh, d.kw);
+    const int32_t order = w.tap_major ? TBN_CONV_WEIGHTS_TAP_MAJOR : TBN_CONV_WEIGHTS_REFERENCE;
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.kh, d.kw, order);
     const uint32_t epi = (relu_flag ? TBN_EPI_RELU : 0u) | (residual ? TBN_EPI_ADD_RESIDUAL : 0u);
     check(tbn_conv2d_f32(dptr(x), d.N, d.C, d.H, d.W, w.split.device_data(), d.M, d.kh, d.kw, static_cast<int32_t>(p.stride_h),
                          static_cast<int32_t>(p.stride_w), static_cast<int32_t>(p.pad_h), static_cast<int32_t>(p.pad_w),
                          static_cast<int32_t>(p.dilation_h), static_cast<int32_t>(p.dilation_w), dptr_or_null(bias),
-                         dptr_or_null(residual), static_cast<float*>(y.device_data()), epi, workspace().get(ws_bytes), ws_bytes,
-                         nullptr));
+                         dptr_or_null(residual), static_cast<float*>(y.device_data()), epi, order, workspace().get(ws_bytes),
+                         ws_bytes, nullptr));
     y.mark_device_written();
     return y;
 }

@@ -231,8 +231,23 @@ int32_t tbn_gemm_f32(const float* d_a, int64_t M, int64_t K, int64_t lda, const 
 
 /* ---- convolution (implicit GEMM) ----------------------------------------------------- */
 
-/* Bytes of scratch the convolution entry points need (tap table + partial-sum tiles). */
-size_t tbn_conv2d_workspace_bytes(int64_t C, int64_t kh, int64_t kw);
+/* Order of K inside the packed / split conv weights handed to the convolution entry points:
+ *   REFERENCE  k = (c*kh + i)*kw + j, the reference's im2col order (filters [M_out, C, kh, kw] packed as they
+ *              are with TBN_LAYOUT_NK).  Works for every geometry; the activation operand is gathered
+ *              element by element from the NCHW input.
+ *   TAP_MAJOR  k = (i*kw + j)*C + c (filters first reordered with tbn_permute_filters).  Needs C % 64 == 0.
+ *              A pre-pass writes a channels-last bf16 copy of the input (same size as the input, not an
+ *              im2col matrix) and the kernel copies whole 64-channel runs with 16-byte asynchronous copies:
+ *              several times faster. */
+#define TBN_CONV_WEIGHTS_REFERENCE 0
+#define TBN_CONV_WEIGHTS_TAP_MAJOR 1
+
+/* [M, C, taps] fp32 -> [M, taps, C] fp32 (taps = kh*kw). */
+int32_t tbn_permute_filters(const float* d_w, int64_t M, int64_t C, int64_t taps, float* d_out, void* stream);
+
+/* Bytes of scratch the convolution entry points need (tap table or channels-last copy + partial-sum tiles). */
+size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t kh, int64_t kw,
+                                  int32_t weight_order);
 
 /* Float x binary / float x ternary Conv2D, NCHW fp32 in and out:
  *     y[n,m,oh,ow] = (sum_{c,i,j} x[n,c,oh*sh-ph+i*dh, ow*sw-pw+j*dw] * w[m,c,i,j]) * alpha[m] * scale
@@ -248,7 +263,8 @@ int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                        const uint32_t* d_pos, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw,
                        int32_t ph, int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale,
                        const float* d_bias, const float* d_residual, float* d_y, int32_t mode,
-                       uint32_t epilogue, void* d_workspace, size_t workspace_bytes, void* stream);
+                       uint32_t epilogue, int32_t weight_order, void* d_workspace, size_t workspace_bytes,
+                       void* stream);
 
 /* "TBN mode" Conv2D: activations ternarised at (lo, hi) while they are gathered, exact integer
  * accumulation.  With alpha, bias and TBN_EPI_BIAS_BEFORE_ALPHA it is bit-equal to the cached fast
@@ -257,15 +273,16 @@ int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
 int32_t tbn_conv2d_tbn(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float lo, float hi,
                        const uint32_t* d_neg, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw,
                        int32_t ph, int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale,
-                       const float* d_bias, float* d_y, uint32_t epilogue, void* d_workspace,
-                       size_t workspace_bytes, void* stream);
+                       const float* d_bias, float* d_y, uint32_t epilogue, int32_t weight_order,
+                       void* d_workspace, size_t workspace_bytes, void* stream);
 
 /* Float-filter Conv2D (stem and 1x1 shortcut convolutions): stands in for tbn::conv2d
  * (tbn-runtime/src/operators/conv2d.cpp:78-192); filters from tbn_dense_pack (TBN_LAYOUT_NK). */
 int32_t tbn_conv2d_f32(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, const void* d_packed_w,
                        int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw,
                        int32_t dh, int32_t dw, const float* d_bias, const float* d_residual, float* d_y,
-                       uint32_t epilogue, void* d_workspace, size_t workspace_bytes, void* stream);
+                       uint32_t epilogue, int32_t weight_order, void* d_workspace, size_t workspace_bytes,
+                       void* stream);
 
 /* ---- glue operators of the CNN graphs (device resident, fp32) --------------------------- */
 
