@@ -248,6 +248,14 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     L = capi.lib
     L.init(local)
+    if args.only_cnn:
+        # Profiling aid: only the binary-CNN block (conv layer batch 4096 + ResNet-18), one JSON line.
+        cnn = cnn_block(args, L, capi, torch, dist, dev, rank, world)
+        if rank == 0:
+            print(json.dumps({"metric": "binary-CNN images/s", "n_gpus": world, "cnn": cnn}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     n = args.size
     mode = {"x1": capi.MODE_TC_BF16X1, "x2": capi.MODE_TC_BF16X2, "x3": capi.MODE_TC_BF16X3}[args.mode]
     npass = {"x1": 1, "x2": 2, "x3": 3}[args.mode]
@@ -461,6 +469,7 @@ def main():
     ap.add_argument("--mode", default="x2", choices=["x1", "x2", "x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cnn", action="store_true", help="skip the binary-CNN images/s block")
+    ap.add_argument("--only-cnn", action="store_true", help="run only the binary-CNN images/s block")
     ap.add_argument("--no-fused-gather", action="store_true", help="N > 1: use NCCL all-gather instead of peer stores")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
