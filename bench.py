@@ -28,6 +28,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# DRAM bytes of one gemm_tc_kernel launch measured with ncu (a profiler cannot run inside the benchmark):
+# key = (size, mode, GPUs).
+MEASURED_TRAFFIC = {(16384, "x2", 1): 5.09e9, (8192, "x2", 1): 0.639e9}
+
 METRIC = "float x binary GEMM throughput (2*M*N*K / time)"
 UNIT = "TFLOP/s"
 
@@ -429,7 +433,10 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "roofline": {
                 "bound": "tensor", "kernel": "gemm_tc_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak, "traffic": MEASURED_TRAFFIC.get((n, args.mode, world)),
+                "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch at this size, one-pass ncu "
+                                "capture (profiles/gemm_tc_kernel_fxb_16384_x2_dram_traffic.md); algorithmic bytes "
+                                f"{(2.0 * npass * n * n + n * nc / 8.0 + 4.0 * nc + 4.0 * n * nc):.4g}",
                 "peak_source": f"{peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} "
                                f"{pipe_peak} TFLOP/s / {npass} passes",
                 "executed_tflops": achieved * npass, "frac_of_pipe_raw": achieved / pipe_peak,

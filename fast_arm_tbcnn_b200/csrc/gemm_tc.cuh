@@ -91,8 +91,14 @@ constexpr int A_TILE_BYTES = BM * BK * 2;
 constexpr int kProducerWarp = 0, kMmaWarp = 1;
 constexpr int kBuildThreads = 256, kEpilogueThreads = 128;
 constexpr int kThreads = 64 + kBuildThreads + kEpilogueThreads;
-constexpr int kGroupM = 8;      // rasterisation: 8 m-tiles share a sweep over n for L2 reuse
-constexpr int kWordStages = 4;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
+#ifndef TBN_GROUP_M
+#define TBN_GROUP_M 4
+#endif
+constexpr int kGroupM = TBN_GROUP_M;  // rasterisation: this many m-tiles share a sweep over n for L2 reuse
+#ifndef TBN_WORD_STAGES
+#define TBN_WORD_STAGES 4
+#endif
+constexpr int kWordStages = TBN_WORD_STAGES;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
 constexpr int kAuxBarrierBytes = 1024;
 constexpr int kMaxOutputs = 8;           // destinations of the multi-destination epilogue (GPUs of one box)
 constexpr int kStageOutBytes = 4 * 2048;  // per epilogue warp: 32 rows x 16 fp32 transposition buffer

@@ -245,6 +245,28 @@ def test_row_sampled_oracle(tbn, oracle, n):
     assert rel_l2(out[torch.from_numpy(rows).cuda()].cpu().numpy(), expect) <= TOL_FP32
 
 
+def test_ternary_projection_shape_row_sampled(tbn, oracle):
+    """Float x ternary GEMM of the MLP-projection shape (A 4096 x 4096, W 4096 x 11008, threshold
+    0.7 mean|W|, scale = mean |W| over the non-zero entries of each column): packed codes bit-exact against
+    the reference's 2-bit packer, 32 seeded rows of the product against the reference's float GEMM."""
+    import torch
+    M, K, N = 4096, 4096, 11008
+    A, _ = make_case(0, 1, M, K, 8)
+    W = np.random.default_rng(1).standard_normal((K, N), dtype=np.float32)
+    delta = float(np.float32(0.7) * np.abs(W).mean(dtype=np.float32))
+    codes, pos, neg, alpha = tbn.lib.quant_pack_ternary(torch.from_numpy(W).cuda(), -delta, delta)
+    out = tbn.lib.gemm_fxb(torch.from_numpy(A).cuda(), neg, N, pos=pos, alpha=alpha, mode=tbn.MODE_TC_BF16X2)
+    tbn.lib.sync()
+    t = oracle.quantize_to_ternary(W, -delta, delta)
+    assert np.array_equal(codes.cpu().numpy().view(np.uint8)[: (K * N + 3) // 4], oracle.ternary_codes(t))
+    assert 0.40 < float((t == 0).mean()) < 0.45  # P(|w| < 0.7 * E|w|) = 0.424 for N(0,1) weights
+    a_ref = oracle.column_abs_mean_nonzero(W, -delta, delta)
+    np.testing.assert_allclose(alpha.cpu().numpy(), a_ref, rtol=1e-5)
+    rows = np.random.default_rng(5).choice(M, size=32, replace=False)
+    expect = oracle.gemm_f32(A[rows], t.astype(np.float32) * a_ref[None, :])
+    assert rel_l2(out[torch.from_numpy(rows).cuda()].cpu().numpy(), expect) <= TOL_FP32
+
+
 def test_full_size_linearity_and_sampled_rows(tbn, oracle):
     """16384^3: sampled rows against the oracle, plus a size-independent property:
     the product is linear in A, so gemm(A) - gemm(A with one row block negated) cancels exactly
