@@ -46,28 +46,73 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs.
+
+    Reads only (NVML queries from a thread of this process every 5 ms, so that even a timed region of a few
+    tens of milliseconds is covered); when NVML cannot be loaded, an `nvidia-smi -lms` child is used instead."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20),
+                   ("hw_thermal_slowdown", 0x40))
 
-    def __init__(self, gpu_index):
+    def __init__(self, gpu_index, pci_bus_id=None):
         self.gpu = gpu_index
+        self.pci = pci_bus_id
         self.proc = None
         self.path = None
+        self.thread = None
+        self.stop_flag = threading.Event()
+        self.sm, self.reasons, self.sm_max = [], set(), None
+
+    def _nvml_loop(self, nv, handle):
+        while not self.stop_flag.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                for name, bit in self.REASON_BITS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = None
+            if self.pci:
+                try:
+                    handle = nv.nvmlDeviceGetHandleByPciBusId(self.pci.encode() if hasattr(self.pci, "encode") else self.pci)
+                except Exception:
+                    handle = None
+            if handle is None:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.sm_max = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         fd, self.path = tempfile.mkstemp(suffix=".csv")
         os.close(fd)
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": None}
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            if self.sm:
+                out.update(sm_mhz=float(np.median(self.sm)), sm_max_mhz=self.sm_max, reasons=sorted(self.reasons),
+                           samples=len(self.sm), source="nvml")
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -90,7 +135,8 @@ class ClockSampler:
                     reasons.add(name)
         os.unlink(self.path)
         if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm),
+                       source="nvidia-smi")
         return out
 
 
@@ -155,7 +201,7 @@ def cnn_block(args, L, capi, torch, dist, dev, rank, world):
     GPU).  Whole-job images/s = images of all ranks / max-over-ranks device time."""
     from fast_arm_tbcnn_b200 import sharding
     from fast_arm_tbcnn_b200.session import Session
-    from oracle import graphs  # graph recipes only (plain dicts); nothing of the checker runs here
+    from fast_arm_tbcnn_b200 import graphs
     out = {}
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
@@ -333,7 +379,12 @@ def run_ours(args):
     L.profile_enable(True)
     L.profile_read()
     barrier()
-    sampler = ClockSampler(local)
+    props = torch.cuda.get_device_properties(dev)
+    try:
+        pci = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+    except AttributeError:
+        pci = None
+    sampler = ClockSampler(local, pci)
     if rank == 0:
         sampler.start()
     launches0 = L.launch_count()

@@ -35,8 +35,8 @@ __global__ void __launch_bounds__(256) nhwc_split_kernel(const float* __restrict
                                                          __nv_bfloat16* __restrict__ xs, int64_t term_stride, float lo,
                                                          float hi) {
     __shared__ float tile[64][33];
-    const int w0 = blockIdx.x * 32, c0 = blockIdx.y * 64;
-    const int64_t nh = blockIdx.z;  // n * H + h
+    const int w0 = blockIdx.z * 32, c0 = blockIdx.y * 64;
+    const int64_t nh = blockIdx.x;  // n * H + h (grid.x: the only dimension that may exceed 65535)
     const int64_t n = nh / H;
     const int h = static_cast<int>(nh - n * H);
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -140,8 +140,9 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     const int64_t term_stride = a.N * a.H * a.W * a.C;
     int32_t rc;
     if (fast) {
-        TBN_REQUIRE(a.H * a.N < (1LL << 31) && a.W <= 65535LL * 32, TBN_INVALID_SHAPE, "conv2d: input too large for the pre-pass grid");
-        dim3 grid(static_cast<unsigned>((a.W + 31) / 32), static_cast<unsigned>(a.C / 64), static_cast<unsigned>(a.N * a.H));
+        TBN_REQUIRE(a.H * a.N < (1LL << 31) && a.W <= 65535LL * 32 && a.C / 64 <= 65535, TBN_INVALID_SHAPE,
+                    "conv2d: input too large for the pre-pass grid");
+        dim3 grid(static_cast<unsigned>(a.N * a.H), static_cast<unsigned>(a.C / 64), static_cast<unsigned>((a.W + 31) / 32));
         profile_begin(kProfSplit, a.st);
         if (tern_act) nhwc_split_kernel<1, true><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(a.H),
                                                                         static_cast<int>(a.W), xs, term_stride, lo, hi);

@@ -95,19 +95,19 @@ constexpr int kThreads = 64 + kBuildThreads + kEpilogueThreads;
 #define TBN_GROUP_M 4
 #endif
 constexpr int kGroupM = TBN_GROUP_M;  // rasterisation: this many m-tiles share a sweep over n for L2 reuse
-#ifndef TBN_WORD_STAGES
-#define TBN_WORD_STAGES 4
-#endif
-constexpr int kWordStages = TBN_WORD_STAGES;  // ring of packed-word tiles, each covering 2 k-blocks (128 k)
+// Ring of packed-word tiles, each covering 2 k-blocks (128 k): 2 slots keep the GEMM fed; the convolutions,
+// whose k-blocks are short-lived, run 4 slots ahead.
+constexpr int kWordStagesGemm = 2, kWordStagesConv = 4;
 constexpr int kAuxBarrierBytes = 1024;
 constexpr int kMaxOutputs = 8;           // destinations of the multi-destination epilogue (GPUs of one box)
-constexpr int kStageOutBytes = 4 * 2048;  // per epilogue warp: 32 rows x 16 fp32 transposition buffer
+constexpr int kStageOutBytes = 4 * 4096;  // per epilogue warp: 32 rows x 32 fp32 transposition buffer
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 // Accumulation steps (k elements x passes) after which a fresh accumulator is started.
 constexpr int kMaxAccumSteps = 4096;
 
-template <int BN, int NPASS, bool TERNARY, bool DENSE = false>
+template <int BN, int NPASS, bool TERNARY, bool DENSE = false, bool CONV = false>
 struct Cfg {
+    static constexpr int kWordStages = DENSE ? 1 : (CONV ? kWordStagesConv : kWordStagesGemm);  // dense weights use no words
     static constexpr int B_TILE_BYTES = BN * BK * 2;
     static constexpr int B_TERMS = DENSE ? 2 : 1;  // dense weights: hi and lo bf16 terms
     static constexpr int B_BYTES = B_TERMS * B_TILE_BYTES;
@@ -184,9 +184,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                                                               const __grid_constant__ CUtensorMap tmap_neg,
                                                               const __grid_constant__ CUtensorMap tmap_pos,
                                                               const Params p) {
-    using C = Cfg<BN, NPASS, TERNARY, DENSE>;
     constexpr bool CONV = AMODE != 0;
     constexpr bool FAST = AMODE == 2;
+    using C = Cfg<BN, NPASS, TERNARY, DENSE, CONV>;
+    constexpr int kWordStages = C::kWordStages;
     static_assert(!DENSE || (NPASS == 2 && !TERNARY && !TERN_ACT), "dense weights use the two-term split on both sides");
     // Which operands arrive by TMA (signalled on full_a) and which are built by the build warps (full_b).
     constexpr bool kTmaOperands = !CONV || DENSE;
@@ -615,38 +616,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         const int64_t nc = n0 + c * 32;
                         const float* as = alpha_s + sbuf * BN + c * 32;
                         const float* bs = bias_s + sbuf * BN + c * 32;
-                        float* tbuf = stage_out + (warp & 3) * (kStageOutBytes / 16);  // 512 floats per warp
+                        float* tbuf = stage_out + (warp & 3) * (kStageOutBytes / 16);  // 32 x 32 floats per warp
                         const int64_t m_warp = static_cast<int64_t>(tm) * BM + quarter * 32;
+                        // lane = row: write this row's 32 columns as 8 float4 at swizzled positions.
 #pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            // lane = row: write this row's 16 columns as 4 float4 at swizzled positions.
-#pragma unroll
-                            for (int j4 = 0; j4 < 4; ++j4) {
-                                const int j = half * 16 + j4 * 4;
-                                float4 o;
-                                o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags, 0.0f);
-                                o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags, 0.0f);
-                                o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags, 0.0f);
-                                o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags, 0.0f);
-                                *reinterpret_cast<float4*>(tbuf + lane * 16 + ((j4 ^ (lane & 3)) << 2)) = o;
-                            }
-                            __syncwarp();
-                            // 4 lanes per row (16 floats = 64 bytes), 8 rows per instruction.
-#pragma unroll
-                            for (int rr = 0; rr < 4; ++rr) {
-                                const int row = rr * 8 + (lane >> 2);
-                                const int q4 = lane & 3;
-                                const float4 o = *reinterpret_cast<const float4*>(tbuf + row * 16 + ((q4 ^ (row & 3)) << 2));
-                                const int64_t mm = m_warp + row;
-                                const int64_t col = nc + half * 16 + q4 * 4;
-                                if (mm < p.M && col + 4 <= p.N) {
-                                    const int64_t idx = mm * p.ldc + col;
-#pragma unroll 1
-                                    for (int d = 0; d < p.num_out; ++d) *reinterpret_cast<float4*>(p.out_list[d] + idx) = o;
-                                }
-                            }
-                            __syncwarp();
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const int j = j4 * 4;
+                            float4 o;
+                            o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags, 0.0f);
+                            o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags, 0.0f);
+                            o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags, 0.0f);
+                            o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags, 0.0f);
+                            *reinterpret_cast<float4*>(tbuf + lane * 32 + ((j4 ^ (lane & 7)) << 2)) = o;
                         }
+                        __syncwarp();
+                        // 8 lanes per row (32 floats = 128 bytes), 4 rows per instruction.
+#pragma unroll
+                        for (int rr = 0; rr < 8; ++rr) {
+                            const int row = rr * 4 + (lane >> 3);
+                            const int q8 = lane & 7;
+                            const float4 o = *reinterpret_cast<const float4*>(tbuf + row * 32 + ((q8 ^ (row & 7)) << 2));
+                            const int64_t mm = m_warp + row;
+                            const int64_t col = nc + q8 * 4;
+                            if (mm < p.M && col + 4 <= p.N) {
+                                const int64_t idx = mm * p.ldc + col;
+#pragma unroll 1
+                                for (int d = 0; d < p.num_out; ++d) *reinterpret_cast<float4*>(p.out_list[d] + idx) = o;
+                            }
+                        }
+                        __syncwarp();
                     } else if (m < p.M) {
                         const int64_t nc = n0 + c * 32;
                         const float* as = alpha_s + sbuf * BN + c * 32;
@@ -757,7 +755,7 @@ inline void set_segments(tc::Params& p, int npass) {
 
 template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE = false>
 int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
-    using C = tc::Cfg<BN, NPASS, TERNARY, DENSE>;
+    using C = tc::Cfg<BN, NPASS, TERNARY, DENSE, AMODE != 0>;
     auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>;
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;

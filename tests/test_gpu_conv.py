@@ -125,6 +125,24 @@ def test_conv_channels_last_path(tbn, oracle, case):
     assert torch.equal(yq, yr)
 
 
+def test_channels_last_prepass_beyond_65535_rows(tbn):
+    """batch x height above 65535 (the limit of two of the three launch-grid dimensions): the channels-last
+    path agrees with the element-wise path bit for bit in the integer mode."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((1200, 64, 56, 8), device="cuda", generator=g)
+    w = torch.randn((64, 64, 3, 3), device="cuda", generator=g)
+    p = (1, 1, 1, 1, 1, 1)
+    alpha = tbn.lib.channel_abs_mean(w)
+    words_t, _ = tbn.lib.quant_pack_binary(tbn.lib.permute_filters(w), tbn.LAYOUT_NK, 0.0, True, want_alpha=False)
+    words_r, _ = tbn.lib.quant_pack_binary(w.reshape(64, -1), tbn.LAYOUT_NK, 0.0, True, want_alpha=False)
+    yt = tbn.lib.conv2d_tbn(x, words_t, tuple(w.shape), p, alpha=alpha, order=tbn.CONV_WEIGHTS_TAP_MAJOR)
+    yr = tbn.lib.conv2d_tbn(x, words_r, tuple(w.shape), p, alpha=alpha)
+    tbn.lib.sync()
+    assert yt.shape == (1200, 64, 56, 8) and torch.equal(yt, yr)
+    assert float(yt.abs().sum()) > 0
+
+
 def test_tap_major_needs_64_channels(tbn):
     import torch
     x = torch.zeros((1, 48, 8, 8), device="cuda")
