@@ -450,6 +450,13 @@ def run_ours(args):
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_ms.item())
 
+    kernel_ms_ranks = None
+    if world > 1:
+        mine = torch.tensor([prof["gemm_ms"] / max(prof["gemm_launches"], 1)], device=dev)
+        every = torch.empty(world, device=dev)
+        dist.all_gather_into_tensor(every, mine)
+        kernel_ms_ranks = [round(float(v), 4) for v in every.tolist()]
+
     cnn = None
     if not args.no_cnn:
         try:
@@ -491,7 +498,9 @@ def run_ours(args):
                 "peak_source": f"{peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} "
                                f"{pipe_peak} TFLOP/s / {npass} passes",
                 "executed_tflops": achieved * npass, "frac_of_pipe_raw": achieved / pipe_peak,
-                "kernel_ms": gemm_ms, "split_kernel_ms": prof["split_ms"] / max(prof["split_launches"], 1),
+                "kernel_ms": gemm_ms, "kernel_ms_ranks": kernel_ms_ranks, "activation_split": (
+                    "separate kernel" if prof["split_launches"] else "inside the GEMM kernel (fp32 rows split in registers)"),
+                "split_kernel_ms": prof["split_ms"] / max(prof["split_launches"], 1),
                 "hbm_algorithmic_gbs": (4.0 * n * n + n * nc / 8.0 + 4.0 * n * nc) / (gemm_ms * 1e-3) / 1e9,
             },
             "weight_pack": {"ms": pack_ms, "algorithmic_gbs": pack_bytes / (pack_ms * 1e-3) / 1e9,

@@ -30,6 +30,7 @@ SIGNATURES = {
     "tbn_cuda_sync": (_i32, [_vp]),
     "tbn_cuda_launch_count": (_i64, []),
     "tbn_cuda_profile_enable": (_i32, [_i32]),
+    "tbn_cuda_set_fused_split": (_i32, [_i32]),
     "tbn_cuda_profile_read": (_i32, [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(_i64)]),
     "tbn_dense_pack_bytes": (_sz, [_i64, _i64]),
     "tbn_dense_pack": (_i32, [_vp, _i64, _i64, _i64, _i32, _vp, _vp]),
@@ -137,6 +138,11 @@ class _Lib:
 
     def launch_count(self):
         return int(self.h.tbn_cuda_launch_count())
+
+    def set_fused_split(self, value=1):
+        """0: always run the separate activation-split kernel; 1 (default): split inside the GEMM when N <= 256;
+        2: split inside the GEMM whenever A's alignment allows."""
+        check(self.h.tbn_cuda_set_fused_split(int(value)))
 
     def profile_enable(self, on=True):
         check(self.h.tbn_cuda_profile_enable(int(on)))

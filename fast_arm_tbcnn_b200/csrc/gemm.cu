@@ -29,6 +29,7 @@
 //                             scratch tile that stays resident in L2.
 //   gemm_simt_kernel          CUDA-core add/subtract-by-sign, fp32, k ascending (bit-equal to the
 //                             naive reference loop); used for tiny problems and as a cross-check.
+#include <atomic>
 #include "gemm_tc.cuh"
 
 namespace tbn_cuda {
@@ -199,6 +200,13 @@ int32_t launch_split(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_
     return launched("split_activations_kernel");
 }
 
+std::atomic<int> g_fused_split{1};
+// 0 never, 1 when the weights have a single column tile, 2 always.
+bool fused_split_wanted(int64_t N) {
+    const int v = g_fused_split.load(std::memory_order_relaxed);
+    return v == 2 || (v == 1 && N <= 256);
+}
+
 // Tensor-core path: split (or ternarise) A into the workspace, then the tcgen05 kernel.
 int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bool ternarise_act, float act_lo,
                          float act_hi, int npass, const uint32_t* d_neg, const uint32_t* d_pos, int64_t N,
@@ -217,8 +225,14 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     TBN_REQUIRE(encode != nullptr, TBN_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
     __nv_bfloat16* split = static_cast<__nv_bfloat16*>(d_ws);
 
-    int32_t rc;
-    if (ternarise_act) rc = launch_split<1, true>(d_a, M, K, lda, M_pad, K_pad, split, act_lo, act_hi, st);
+    // Two-term products whose A rows can be read as float4 may skip the split pass: the GEMM's build warps read
+    // the fp32 rows and split them in registers (same arithmetic, bit-identical operands) -- once per column
+    // tile of the weights, so by default only when there is a single one.
+    const bool fused_split = fused_split_wanted(N) && !ternarise_act && npass == 2 && !dense_w && K % 4 == 0 &&
+                             lda % 4 == 0 && reinterpret_cast<uintptr_t>(d_a) % 16 == 0;
+    int32_t rc = TBN_SUCCESS;
+    if (fused_split) {}
+    else if (ternarise_act) rc = launch_split<1, true>(d_a, M, K, lda, M_pad, K_pad, split, act_lo, act_hi, st);
     else if (npass == 1) rc = launch_split<1, false>(d_a, M, K, lda, M_pad, K_pad, split, 0.f, 0.f, st);
     else if (npass == 2) rc = launch_split<2, false>(d_a, M, K, lda, M_pad, K_pad, split, 0.f, 0.f, st);
     else rc = launch_split<3, false>(d_a, M, K, lda, M_pad, K_pad, split, 0.f, 0.f, st);
@@ -267,6 +281,11 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(d_ws) + split_bytes);
     p.num_out = num_out;
     for (int i = 0; i < num_out; ++i) p.out_list[i] = outs[i];
+    p.a_rows = d_a;
+    p.lda = lda;
+    p.K = static_cast<int>(K);
+    if (fused_split)
+        return d_pos ? dispatch_bn<2, true, 3, false>(bn, maps, p, st) : dispatch_bn<2, false, 3, false>(bn, maps, p, st);
     if (dense_w) {
         p.num_kb = static_cast<int>(K_pad / tc::BK);
         set_segments(p, 3);  // three MMA passes per k-block
@@ -319,6 +338,12 @@ bool prefer_simt(int64_t M, int64_t N, int64_t K) { return M <= 8 || M * N * K <
 using namespace tbn_cuda;
 
 extern "C" {
+
+int32_t tbn_cuda_set_fused_split(int32_t value) {
+    TBN_REQUIRE(value >= 0 && value <= 2, TBN_INVALID_ARGUMENT, "tbn_cuda_set_fused_split: value must be 0, 1 or 2");
+    g_fused_split.store(value, std::memory_order_relaxed);
+    return TBN_SUCCESS;
+}
 
 size_t tbn_gemm_workspace_bytes(int64_t M, int64_t K, int32_t mode) {
     if (M <= 0 || K <= 0) return 0;

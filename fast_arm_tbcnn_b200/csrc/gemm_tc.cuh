@@ -105,6 +105,9 @@ constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 // Accumulation steps (k elements x passes) after which a fresh accumulator is started.
 constexpr int kMaxAccumSteps = 4096;
 
+// Operand modes that lower a convolution (see AMODE at the kernel).
+__host__ __device__ constexpr bool is_conv_mode(int amode) { return amode == 1 || amode == 2; }
+
 template <int BN, int NPASS, bool TERNARY, bool DENSE = false, bool CONV = false>
 struct Cfg {
     static constexpr int kWordStages = DENSE ? 1 : (CONV ? kWordStagesConv : kWordStagesGemm);  // dense weights use no words
@@ -161,6 +164,10 @@ struct Params {
     // buffer and the peers' buffers mapped into this GPU's address space -- instead of p.c.
     int num_out;
     float* out_list[kMaxOutputs];
+    // AMODE 3: the fp32 activation rows themselves (16-byte aligned, lda % 4 == 0, K % 4 == 0).
+    const float* a_rows;
+    int64_t lda;
+    int K;
     ConvGeom conv;
 };
 
@@ -178,20 +185,24 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 // the map of the split weights [2][N_pad][K_pad] instead.
 // AMODE: source of the activation operand.  0 = TMA from pre-split [terms][M][K] (plain GEMM);
 // 1 = element-wise gather from NCHW fp32 (any convolution geometry); 2 = cp.async from the channels-last
-// bf16 copy (convolutions with C % 64 == 0).
+// bf16 copy (convolutions with C % 64 == 0); 3 = the fp32 rows of A read by the build warps and split in
+// registers (plain GEMM without the separate split pass; loads run two k-blocks ahead of their use).
 template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_neg,
                                                               const __grid_constant__ CUtensorMap tmap_pos,
                                                               const Params p) {
-    constexpr bool CONV = AMODE != 0;
+    constexpr bool CONV = is_conv_mode(AMODE);
     constexpr bool FAST = AMODE == 2;
+    constexpr bool ROWS = AMODE == 3;
+    constexpr bool BUILT_A = CONV || ROWS;  // the build warps write the activation operand
+    static_assert(!(ROWS && DENSE), "float weights take their activations by TMA or by the convolution gathers");
     using C = Cfg<BN, NPASS, TERNARY, DENSE, CONV>;
     constexpr int kWordStages = C::kWordStages;
     static_assert(!DENSE || (NPASS == 2 && !TERNARY && !TERN_ACT), "dense weights use the two-term split on both sides");
     // Which operands arrive by TMA (signalled on full_a) and which are built by the build warps (full_b).
-    constexpr bool kTmaOperands = !CONV || DENSE;
-    constexpr bool kBuiltOperands = CONV || !DENSE;
+    constexpr bool kTmaOperands = !BUILT_A || DENSE;
+    constexpr bool kBuiltOperands = BUILT_A || !DENSE;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -232,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             ptx::mbar_init(bar_empty_w + 8 * w, kBuildThreads);
         }
         ptx::fence_barrier_init();
-        if (!CONV) ptx::prefetch_tensormap(&tmap_a);
+        if (!BUILT_A) ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_neg);
         if (TERNARY) ptx::prefetch_tensormap(&tmap_pos);
     }
@@ -278,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             break;
                         }
                         const uint32_t bar = bar_full_a + 8 * stage;
-                        ptx::mbar_arrive_expect_tx(bar, (CONV ? 0 : NPASS * A_TILE_BYTES) + (DENSE ? C::B_BYTES : 0));
+                        ptx::mbar_arrive_expect_tx(bar, (BUILT_A ? 0 : NPASS * A_TILE_BYTES) + (DENSE ? C::B_BYTES : 0));
                         const uint32_t b_dst = base + stage * C::STAGE_BYTES;
                         const uint32_t a_dst = b_dst + C::B_BYTES;
                         if (DENSE) {
@@ -286,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             for (int q = 0; q < 2; ++q)
                                 ptx::tma_load_3d(b_dst + q * C::B_TILE_BYTES, &tmap_neg, kb * BK, tn * BN, q, bar);
                         }
-                        if (!CONV) {
+                        if (!BUILT_A) {
 #pragma unroll
                             for (int q = 0; q < NPASS; ++q)
                                 ptx::tma_load_3d(a_dst + q * A_TILE_BYTES, &tmap_a, kb * BK, tm * BM, q, bar);
@@ -369,6 +380,39 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         // FAST: oldest stage whose copies are in flight and whose arrive is still owed, and how many are owed.
         constexpr int kCopyLag = C::STAGES >= 4 ? 2 : 1;
         int pending_stage = 0, pending_count = 0;
+        // ROWS: this thread reads float4 number (r & 15) of the 64-float k-block slice of rows (r >> 4) + 16*j, so
+        // that 16 lanes cover one row's 256 bytes.  The loads run two k-blocks ahead of their use, across tile
+        // boundaries: pf_a holds the k-block consumed next, pf_b the one after.
+        int pf_t = blockIdx.x, pf_kb = 0, pf_tm = 0;
+        float4 pf_a[8], pf_b[8];
+        auto rows_load = [&](float4 (&dst)[8]) {
+            const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (pf_t < total_tiles) {
+                if (pf_kb == 0) {
+                    int tn_unused;
+                    tile_coords(pf_t, p.tiles_m, p.tiles_n, pf_tm, tn_unused);
+                }
+                const int k0 = pf_kb * BK + (r & 15) * 4;
+                const float* src = p.a_rows + (static_cast<int64_t>(pf_tm) * BM + (r >> 4)) * p.lda + k0;
+                const int rows_left = p.M - (pf_tm * BM + (r >> 4));
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    dst[j] = (k0 < p.K && 16 * j < rows_left)
+                                 ? __ldg(reinterpret_cast<const float4*>(src + static_cast<int64_t>(16 * j) * p.lda))
+                                 : zero;
+                if (++pf_kb == p.num_kb) {
+                    pf_kb = 0;
+                    pf_t += gridDim.x;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dst[j] = zero;
+            }
+        };
+        if (ROWS) {
+            rows_load(pf_a);
+            rows_load(pf_b);
+        }
         for (int t = blockIdx.x; kBuiltOperands && t < total_tiles && ok; t += gridDim.x) {
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -506,6 +550,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         phase ^= 1u;
                     }
                     continue;
+                }
+                if (ROWS) {
+                    uint8_t* a_tile = stage_ptr + C::B_BYTES;
+                    const int c16 = (r & 15) >> 1, half = (r & 1) * 8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int row = (r >> 4) + 16 * j;
+                        const float f[4] = {pf_a[j].x, pf_a[j].y, pf_a[j].z, pf_a[j].w};
+                        uint32_t packed[NPASS][2];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint16_t term[NPASS];
+                            split_terms<NPASS, TERN_ACT>(f[i], p.conv.act_lo, p.conv.act_hi, term);
+#pragma unroll
+                            for (int q = 0; q < NPASS; ++q) {
+                                if (i & 1) packed[q][i >> 1] |= static_cast<uint32_t>(term[q]) << 16;
+                                else packed[q][i >> 1] = term[q];
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < NPASS; ++q)
+                            *reinterpret_cast<uint2*>(a_tile + q * A_TILE_BYTES + row * 128 + ((c16 ^ (row & 7)) << 4) + half) =
+                                make_uint2(packed[q][0], packed[q][1]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) pf_a[j] = pf_b[j];
+                    rows_load(pf_b);
                 }
                 if (CONV) {
                     uint8_t* a_tile = stage_ptr + C::B_BYTES + a_row * 128;
@@ -755,7 +826,7 @@ inline void set_segments(tc::Params& p, int npass) {
 
 template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE = false>
 int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
-    using C = tc::Cfg<BN, NPASS, TERNARY, DENSE, AMODE != 0>;
+    using C = tc::Cfg<BN, NPASS, TERNARY, DENSE, tc::is_conv_mode(AMODE)>;
     auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>;
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
@@ -763,7 +834,7 @@ int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) 
     profile_begin(kProfGemm, st);
     kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, p);
     profile_end(kProfGemm, st);
-    return launched(AMODE ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
+    return launched(tc::is_conv_mode(AMODE) ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
 }
 
 template <int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE = false>

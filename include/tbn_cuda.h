@@ -93,6 +93,14 @@ int32_t tbn_cuda_profile_enable(int32_t enable);
 int32_t tbn_cuda_profile_read(double* gemm_ms, int64_t* gemm_launches, double* split_ms,
                               int64_t* split_launches);
 
+/* Tuning switch without a reference counterpart.  A two-term tbn_gemm_fxb / _multi / _host call whose A is
+ * 16-byte aligned with lda % 4 == 0 and K % 4 == 0 can let the GEMM kernel read the fp32 rows itself and split
+ * them in registers instead of running the activation-split kernel first.  The split is then repeated for every
+ * 256-column tile of the weights, so it only pays when there is one such tile (measured at 16384^3, 64 tiles:
+ * 23.2 ms fused against 11.4 + 0.35 ms separate).  value 1 (default): fuse when N <= 256; 0: never; 2: always.
+ * All three give bit-identical results.  Process-wide; not meant to be flipped while calls are in flight. */
+int32_t tbn_cuda_set_fused_split(int32_t value);
+
 /* Padded dims of the packed layouts: K_pad = ceil128(K), N_pad = ceil8(N)
  * (PaddedDimensions, tbn-runtime/src/operators/quantized_gemm_neon.cpp:38-58). */
 int32_t tbn_packed_dims(int64_t K, int64_t N, int64_t* K_pad, int64_t* N_pad);

@@ -168,6 +168,41 @@ def test_repeated_runs_are_bitwise_identical(tbn, mode):
         assert float((first.double() - exact).abs().max()) < 1e-2
 
 
+@pytest.mark.parametrize("shape", [(128, 128, 128), (300, 644, 200), (1000, 4100, 520), (77, 260, 1032),
+                                   (4096, 8192, 1024), (129, 64, 64)])
+@pytest.mark.parametrize("ternary", [False, True])
+def test_fused_split_equals_separate_split(tbn, shape, ternary):
+    """The GEMM that reads fp32 rows and splits them in registers produces the same bits as the GEMM fed by
+    the separate split kernel (ragged M, K with a partial last k-block, a row stride larger than K)."""
+    import torch
+    M, K, N = shape
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    buf = torch.randn((M, K + 8), generator=g, device="cuda")
+    A = buf[:, :K]  # lda = K + 8
+    W = torch.randn((K, N), generator=g, device="cuda")
+    if ternary:
+        _, pos, neg, _ = tbn.lib.quant_pack_ternary(W, -0.1, 0.1, want_alpha=False, want_codes=False)
+        run = lambda: tbn.lib.gemm_fxb(A, neg, N, pos=pos, mode=tbn.MODE_TC_BF16X2)
+    else:
+        words, alpha = tbn.lib.quant_pack_binary(W)
+        run = lambda: tbn.lib.gemm_fxb(A, words, N, alpha=alpha, mode=tbn.MODE_TC_BF16X2)
+    try:
+        tbn.lib.set_fused_split(0)
+        separate = run().clone()
+        tbn.lib.sync()
+        tbn.lib.set_fused_split(2)
+        fused = run()
+        tbn.lib.sync()
+    finally:
+        tbn.lib.set_fused_split(1)
+    assert torch.equal(fused, separate)
+    sign = torch.where(W > 0.1, 1.0, torch.where(W < -0.1, -1.0, 0.0)) if ternary else torch.where(W > 0, 1.0, -1.0)
+    exact = A.double() @ sign.double()
+    if not ternary:
+        exact = exact * alpha.double()[None, :]
+    assert float((fused.double() - exact).norm() / exact.norm()) <= 1e-5
+
+
 def test_multi_destination_epilogue(tbn):
     """tbn_gemm_fxb_multi writes the column slab into several buffers (the multi-GPU epilogue); on one GPU
     the destinations are two local matrices.  Every copy equals the single-destination result bit for bit and
