@@ -14,6 +14,7 @@ MODE_AUTO, MODE_TC_BF16X1, MODE_TC_BF16X2, MODE_TC_BF16X3, MODE_SIMT = 0, 1, 2, 
 EPI_RELU, EPI_BIAS_BEFORE_ALPHA = 1, 2
 LAYOUT_KN, LAYOUT_NK = 0, 1
 CONV_WEIGHTS_REFERENCE, CONV_WEIGHTS_TAP_MAJOR = 0, 1
+ELT_GREATER, ELT_LESS, ELT_SUB = 0, 1, 2
 
 _vp, _i64, _i32, _f32, _u32, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_uint32, C.c_size_t
 
@@ -47,6 +48,9 @@ SIGNATURES = {
     "tbn_add": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp, _vp]),
     "tbn_pool2d": (_i32, [_i32, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "tbn_global_avgpool2d": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "tbn_global_maxpool2d": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "tbn_binary_elementwise": (_i32, [_i32, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "tbn_transpose2d": (_i32, [_vp, _i64, _i64, _vp, _vp]),
     "tbn_gather_cols_permute": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tbn_packed_dims": (_i32, [_i64, _i64, C.POINTER(_i64), C.POINTER(_i64)]),
     "tbn_quantize_to_binary": (_i32, [_vp, _i64, _f32, _vp, _vp]),
@@ -452,6 +456,32 @@ class _Lib:
         N, Cc, H, W = x.shape
         out = torch.empty((N, Cc, 1, 1), dtype=torch.float32, device=x.device)
         check(self.h.tbn_global_avgpool2d(_ptr(x), N, Cc, H, W, _ptr(out), _stream()))
+        return out
+
+    def global_maxpool2d(self, x):
+        import torch
+        self.init()
+        x = x.contiguous()
+        N, Cc, H, W = x.shape
+        out = torch.empty((N, Cc, 1, 1), dtype=torch.float32, device=x.device)
+        check(self.h.tbn_global_maxpool2d(_ptr(x), N, Cc, H, W, _ptr(out), _stream()))
+        return out
+
+    def binary_elementwise(self, op, x, rhs):
+        """op: ELT_GREATER / ELT_LESS (float 0/1 result) or ELT_SUB; rhs is indexed modulo its length."""
+        import torch
+        self.init()
+        x, rhs = x.contiguous(), rhs.contiguous()
+        out = torch.empty_like(x)
+        check(self.h.tbn_binary_elementwise(op, _ptr(x), x.numel(), _ptr(rhs), rhs.numel(), _ptr(out), _stream()))
+        return out
+
+    def transpose2d(self, x):
+        import torch
+        self.init()
+        x = x.contiguous()
+        out = torch.empty((x.shape[1], x.shape[0]), dtype=torch.float32, device=x.device)
+        check(self.h.tbn_transpose2d(_ptr(x), x.shape[0], x.shape[1], _ptr(out), _stream()))
         return out
 
 

@@ -1,7 +1,9 @@
 // Glue operators of the CNN graphs, device resident (all HBM-bound, one pass over the data):
 // ReLU, Add (the broadcast forms the reference Session accepts), MaxPool / AveragePool,
-// GlobalAveragePool.  Stand in for Session::execute_relu / execute_add (tbn/runtime/model.hpp:905-1174)
-// and tbn-runtime/src/operators/pooling.cpp:10-216.
+// GlobalAveragePool / GlobalMaxPool, the Greater / Less / Sub trio of the exported ternary-activation subgraph,
+// and a 2-D transpose (Gemm with transA / transB).  Stand in for Session::execute_relu / execute_add /
+// execute_greater / execute_less / execute_sub (tbn/runtime/model.hpp:905-1316) and
+// tbn-runtime/src/operators/pooling.cpp:10-216.
 #include <algorithm>
 
 #include "common.cuh"
@@ -67,6 +69,47 @@ __global__ void global_avgpool_kernel(const float* __restrict__ x, int64_t NC, i
     if (lane == 0) y[plane] = __fdiv_rn(sum, static_cast<float>(HW));
 }
 
+// One warp per (n, c) plane; std::max semantics (a NaN element never replaces the running maximum).
+__global__ void global_maxpool_kernel(const float* __restrict__ x, int64_t NC, int64_t HW, float* __restrict__ y) {
+    const int64_t plane = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (plane >= NC) return;
+    const int lane = threadIdx.x & 31;
+    float best = -INFINITY;
+    for (int64_t i = lane; i < HW; i += 32) {
+        const float v = x[plane * HW + i];
+        best = best < v ? v : best;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float other = __shfl_down_sync(0xffffffffu, best, off);
+        best = best < other ? other : best;
+    }
+    if (lane == 0) y[plane] = best;
+}
+
+// op 0: y = x > rhs ? 1 : 0; op 1: y = x < rhs ? 1 : 0; op 2: y = x - rhs.  rhs is indexed modulo its length,
+// the flat broadcast of the reference Session (model.hpp:1213-1216, 1260-1263, 1309-1311).
+__global__ void binary_elementwise_kernel(int op, const float* __restrict__ x, int64_t n, const float* __restrict__ rhs,
+                                          int64_t rhs_n, float* __restrict__ y) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float a = x[i], b = rhs[rhs_n == n ? i : i % rhs_n];
+        y[i] = op == 0 ? (a > b ? 1.0f : 0.0f) : op == 1 ? (a < b ? 1.0f : 0.0f) : __fsub_rn(a, b);
+    }
+}
+
+// y[c][r] = x[r][c] through a 32 x 33 shared-memory tile (both sides coalesced).
+__global__ void transpose2d_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, float* __restrict__ y) {
+    __shared__ float tile[32][33];
+    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * 32, r0 = static_cast<int64_t>(blockIdx.y) * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
+    for (int i = ty; i < 32; i += 8)
+        if (r0 + i < rows && c0 + tx < cols) tile[i][tx] = x[(r0 + i) * cols + c0 + tx];
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8)
+        if (c0 + i < cols && r0 + tx < rows) y[(c0 + i) * rows + r0 + tx] = tile[tx][i];
+}
+
 int grid_for(int64_t n) {
     const int64_t cap = static_cast<int64_t>(sm_count() > 0 ? sm_count() : 148) * 16;
     return static_cast<int>(std::max<int64_t>(1, std::min((n + 255) / 256, cap)));
@@ -120,6 +163,33 @@ int32_t tbn_global_avgpool2d(const float* d_x, int64_t N, int64_t C, int64_t H, 
     const int64_t planes = N * C;
     global_avgpool_kernel<<<static_cast<unsigned>((planes + 7) / 8), 256, 0, as_stream(stream)>>>(d_x, planes, H * W, d_y);
     return launched("global_avgpool_kernel");
+}
+
+int32_t tbn_global_maxpool2d(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float* d_y, void* stream) {
+    TBN_REQUIRE(N > 0 && C > 0 && H > 0 && W > 0, TBN_INVALID_SHAPE, "tbn_global_maxpool2d: bad dimensions");
+    TBN_REQUIRE(d_x && d_y, TBN_INVALID_ARGUMENT, "tbn_global_maxpool2d: null pointer");
+    const int64_t planes = N * C;
+    global_maxpool_kernel<<<static_cast<unsigned>((planes + 7) / 8), 256, 0, as_stream(stream)>>>(d_x, planes, H * W, d_y);
+    return launched("global_maxpool_kernel");
+}
+
+int32_t tbn_binary_elementwise(int32_t op, const float* d_x, int64_t n, const float* d_rhs, int64_t rhs_n, float* d_y,
+                               void* stream) {
+    TBN_REQUIRE(op >= TBN_ELT_GREATER && op <= TBN_ELT_SUB, TBN_INVALID_ARGUMENT, "tbn_binary_elementwise: unknown operation");
+    TBN_REQUIRE(n >= 0 && rhs_n > 0, TBN_INVALID_ARGUMENT, "tbn_binary_elementwise: bad sizes");
+    if (n == 0) return TBN_SUCCESS;
+    TBN_REQUIRE(d_x && d_rhs && d_y, TBN_INVALID_ARGUMENT, "tbn_binary_elementwise: null pointer");
+    binary_elementwise_kernel<<<grid_for(n), 256, 0, as_stream(stream)>>>(op, d_x, n, d_rhs, rhs_n, d_y);
+    return launched("binary_elementwise_kernel");
+}
+
+int32_t tbn_transpose2d(const float* d_x, int64_t rows, int64_t cols, float* d_y, void* stream) {
+    TBN_REQUIRE(rows > 0 && cols > 0, TBN_INVALID_SHAPE, "tbn_transpose2d: bad dimensions");
+    TBN_REQUIRE(d_x && d_y && d_x != d_y, TBN_INVALID_ARGUMENT, "tbn_transpose2d: null or aliased pointers");
+    const int64_t gx = (cols + 31) / 32, gy = (rows + 31) / 32;
+    TBN_REQUIRE(gx < (1LL << 31) && gy <= 65535, TBN_INVALID_SHAPE, "tbn_transpose2d: matrix too large");
+    transpose2d_kernel<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), 256, 0, as_stream(stream)>>>(d_x, rows, cols, d_y);
+    return launched("transpose2d_kernel");
 }
 
 }  // extern "C"

@@ -128,11 +128,59 @@ def resnet18(batch=1, seed=2, image=224, classes=1000, width=64):
     }
 
 
+def exported_tbn_cnn(batch=1, seed=3, sigma=0.1):
+    """The MNIST TBN CNN as the reference's training script exports it to ONNX (tests/train/mnist:
+    Conv 1->16 5x5 pad 2, ReLU, MaxPool, Conv 16->32 5x5 pad 2, the ternary activation written as
+    Greater / Cast / Less / Cast / Sub against scalar thresholds, MaxPool 14 -> 4 by ceil-less 3x3 stride 3,
+    Reshape, Gemm with transB = 1).  Weights are scaled-binary (+-alpha per output channel), i.e. a trained
+    TBN model after dequantisation, so the Session recognises them in both modes."""
+    rng = np.random.default_rng(seed)
+
+    def scaled_binary(*shape):
+        w = (rng.standard_normal(shape, dtype=np.float32) * np.float32(sigma)).astype(np.float32)
+        flat = np.abs(w.reshape(shape[0], -1))
+        alpha = (flat.sum(axis=1, dtype=np.float32) / np.float32(flat.shape[1])).astype(np.float32)
+        sign = np.where(w > 0, np.float32(1), np.float32(-1))
+        return (sign * alpha.reshape((-1,) + (1,) * (len(shape) - 1))).astype(np.float32)
+
+    def draw(*shape):
+        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(sigma)).astype(np.float32)
+
+    w1, b1 = scaled_binary(16, 1, 5, 5), draw(16)
+    w2, b2 = scaled_binary(32, 16, 5, 5), draw(32)
+    wf, bf = scaled_binary(10, 512), draw(10)  # [N, K]: used with transB = 1
+    return {
+        "inputs": {"input": (batch, 1, 28, 28)},
+        "outputs": {"output": (batch, 10)},
+        "values": {},
+        "inits": {"conv1_w": w1, "conv1_b": b1, "conv2_w": w2, "conv2_b": b2, "fc_w": wf, "fc_b": bf,
+                  "thr_hi": np.array(0.05, dtype=np.float32), "thr_lo": np.array(-0.05, dtype=np.float32),
+                  "flat_shape": np.array([batch, 512], dtype=np.int64)},
+        "binary": set(),
+        "nodes": [
+            _node("Conv", "conv1", ["input", "conv1_w", "conv1_b"], ["c1"], group=1, pads=[2, 2, 2, 2], strides=[1, 1],
+                  auto_pad="NOTSET", dilations=[1, 1]),
+            _node("Relu", "relu1", ["c1"], ["r1"]),
+            _node("MaxPool", "pool1", ["r1"], ["p1"], ceil_mode=0, pads=[0, 0, 0, 0], kernel_shape=[2, 2], strides=[2, 2]),
+            _node("Conv", "conv2", ["p1", "conv2_w", "conv2_b"], ["c2"], group=1, pads=[2, 2, 2, 2], strides=[1, 1],
+                  auto_pad="NOTSET", dilations=[1, 1]),
+            _node("Greater", "gt", ["c2", "thr_hi"], ["gt_out"]),
+            _node("Cast", "cast_gt", ["gt_out"], ["gt_f"], to=1),
+            _node("Less", "lt", ["c2", "thr_lo"], ["lt_out"]),
+            _node("Cast", "cast_lt", ["lt_out"], ["lt_f"], to=1),
+            _node("Sub", "tern", ["gt_f", "lt_f"], ["t2"]),
+            _node("MaxPool", "pool2", ["t2"], ["p2"], ceil_mode=0, pads=[0, 0, 0, 0], kernel_shape=[3, 3], strides=[3, 3]),
+            _node("Reshape", "view", ["p2", "flat_shape"], ["flat"], allowzero=0),
+            _node("Gemm", "fc", ["flat", "fc_w", "fc_b"], ["output"], alpha=1.0, beta=1.0, transA=0, transB=1),
+        ],
+    }
+
+
 def to_spec(net, replace=None, mark_binary=True):
     """-> (spec text, fp32 blob, int64 blob).  ``replace`` maps initialiser names to arrays that are
     written instead of the network's own; ``mark_binary`` adds the line naming the binary weights."""
     replace = replace or {}
-    lines, chunks, off = [], [], 0
+    lines, chunks, ichunks, off, ioff = [], [], [], 0, 0
     for name, shape in net["inputs"].items():
         lines.append(f"input {name} {','.join(map(str, shape))}")
     for name, shape in net["outputs"].items():
@@ -140,8 +188,15 @@ def to_spec(net, replace=None, mark_binary=True):
     for name, shape in net.get("values", {}).items():
         lines.append(f"value {name} {','.join(map(str, shape))}")
     for name, arr in net["inits"].items():
-        a = np.asarray(replace.get(name, arr), dtype=np.float32)
-        lines.append(f"init {name} f32 {','.join(map(str, a.shape))} {off}")
+        a = np.asarray(replace.get(name, arr))
+        dims = ",".join(map(str, a.shape)) if a.ndim else "1"
+        if a.dtype == np.int64:  # shape operands of Reshape
+            lines.append(f"init {name} i64 {dims} {ioff}")
+            ichunks.append(a.reshape(-1))
+            ioff += a.size
+            continue
+        a = a.astype(np.float32)
+        lines.append(f"init {name} f32 {dims} {off}")
         chunks.append(a.reshape(-1))
         off += a.size
     for n in net["nodes"]:
@@ -159,4 +214,5 @@ def to_spec(net, replace=None, mark_binary=True):
     blob = np.concatenate(chunks) if chunks else np.zeros(1, dtype=np.float32)
     binary_line = "binary " + ",".join(sorted(net["binary"])) if net["binary"] and mark_binary else ""
     text = "\n".join(lines + ([binary_line] if binary_line else [])) + "\n"
-    return text, blob.astype(np.float32), np.zeros(1, dtype=np.int64)
+    iblob = np.concatenate(ichunks) if ichunks else np.zeros(1, dtype=np.int64)
+    return text, blob.astype(np.float32), iblob.astype(np.int64)

@@ -61,8 +61,9 @@ Tensor qlinear_matmul_binary_packed(const Tensor& a, const PackedWeights& w, flo
 //   C = (A * sign(W)) * alpha * scale + bias      (what the reference's float tbn::gemm gives on alpha*sign(W)).
 Tensor matmul_float_packed(const Tensor& a, const PackedWeights& w, const Tensor* bias = nullptr, float scale = 1.0f,
                            bool relu = false);
-// tbn::gemm (gemm.hpp:11-12): alpha * A B + beta * C with a 1-D C, transA = transB = 0.  A scaled-binary B
-// (+-alpha per column) runs on the packed-weight kernel, any other B on the float path.
+// tbn::gemm (gemm.hpp:11-12): alpha * op(A) op(B) + beta * C with a 1-D C.  A scaled-binary op(B)
+// (+-alpha per column) runs on the packed-weight kernel, any other B on the float path; transposed operands
+// are materialised on the device first.
 Tensor gemm(const Tensor& A, const Tensor& B, const Tensor* C = nullptr, float alpha = 1.0f, float beta = 0.0f,
             bool transA = false, bool transB = false);
 
@@ -107,8 +108,15 @@ struct Pool2DParams {
 Tensor maxpool2d(const Tensor& input, const Pool2DParams& params = Pool2DParams());
 Tensor avgpool2d(const Tensor& input, const Pool2DParams& params = Pool2DParams());
 Tensor global_avgpool2d(const Tensor& input);
+Tensor global_maxpool2d(const Tensor& input);
 Tensor relu(const Tensor& input);
 Tensor add(const Tensor& a, const Tensor& b);
+// The element-wise trio of the exported ternary-activation subgraph (Session::execute_greater / execute_less /
+// execute_sub, model.hpp:1176-1316): float 0/1 comparison results, rhs indexed modulo its length.
+Tensor greater(const Tensor& lhs, const Tensor& rhs);
+Tensor less(const Tensor& lhs, const Tensor& rhs);
+Tensor sub(const Tensor& lhs, const Tensor& rhs);
+Tensor transpose2d(const Tensor& x);  // [R,C] -> [C,R] on the device
 
 // Per-channel scale of scaled-binary weights (every row of [channels, per] is +-alpha up to rounding),
 // summed sequentially like Session::execute_conv (model.hpp:388-394).  Returns false when the weights are

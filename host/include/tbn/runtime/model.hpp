@@ -60,6 +60,12 @@ public:
     const Shape& get_input_shape(const std::string& name) const;
     const Shape& get_output_shape(const std::string& name) const;
     void validate() const;
+    void set_producer(const std::string& name, const std::string& version) {
+        producer_name_ = name;
+        producer_version_ = version;
+    }
+    const std::string& producer_name() const { return producer_name_; }
+    const std::string& producer_version() const { return producer_version_; }
 
     class Session {
     public:
@@ -97,6 +103,7 @@ public:
         std::shared_ptr<ModelGraph> graph_;
         std::unordered_map<std::string, Tensor> input_tensors_, output_tensors_, intermediate_tensors_;
         std::unordered_map<std::string, CachedWeights> weight_cache_;
+        std::unordered_map<std::string, Tensor> transposed_;  // op(B) of Gemm nodes with transB, once per weight
         std::unordered_set<std::string> declared_binary_;
         bool use_quantization_ = false;
         TilingParams tiling_;
@@ -106,14 +113,14 @@ public:
 
 private:
     std::shared_ptr<ModelGraph> graph_;
+    std::string producer_name_, producer_version_;
 };
 
-// Loader entry points of the reference (model.hpp:1328-1330, onnx_parser.hpp:46-47).  The ONNX protobuf
-// reader is not part of this build: they throw InvalidModelError; graphs are built programmatically or
-// with parse_graph_spec().
+// Loader entry points of the reference (model.hpp:1328-1330; implemented over the ONNX reader in
+// onnx_integration/onnx_parser.hpp).  Both throw InvalidModelError when the file cannot be opened or parsed.
 TBNModel load_model(const std::string& model_path);
-TBNModel load_onnx_model(const std::string& model_path);
-const char* get_version();
+TBNModel load_model_from_buffer(const void* data, size_t size);
+const char* get_version();  // "0.1.0", as the reference
 
 // Builds a graph from a line-oriented description (one declaration per line):
 //   input|output|value <name> <d0,d1,..>

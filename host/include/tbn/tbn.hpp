@@ -1,5 +1,6 @@
 // Umbrella header of the tbn:: API (reference: tbn-runtime/include/tbn/tbn.hpp).
 #pragma once
+#include "onnx_integration/onnx_parser.hpp"
 #include "operators/ops.hpp"
 #include "runtime/attribute.hpp"
 #include "runtime/model.hpp"

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <sstream>
 
+#include "tbn/onnx_integration/onnx_parser.hpp"
 #include "tbn/runtime/model.hpp"
 
 namespace tbn {
@@ -90,7 +91,9 @@ const TBNModel::Session::CachedWeights* TBNModel::Session::weights_for(const std
     if (it != weight_cache_.end()) return &it->second;
     if (w.dtype() != DataType::FLOAT32) return nullptr;
     CachedWeights cw;
-    const bool declared = declared_binary_.count(name) > 0;
+    // "^T" marks the materialised transpose of a Gemm weight: declarations are made under the graph's name.
+    const bool is_t = name.size() > 2 && name.compare(name.size() - 2, 2, "^T") == 0;
+    const bool declared = declared_binary_.count(is_t ? name.substr(0, name.size() - 2) : name) > 0;
     if (conv) {
         std::vector<float> scales;
         cw.scaled_binary = scaled_binary_channel_scales(w, &scales);
@@ -203,8 +206,34 @@ void TBNModel::Session::execute_gemm(const ModelNode& node) {
         auto it = intermediate_tensors_.find(node.inputs[2]);
         if (it != intermediate_tensors_.end()) C = &it->second;
     }
-    if (transA || transB) throw NotImplementedError("Gemm '" + node.name + "': transposed operands are not on the accelerated path");
     TBN_CHECK(Bw.shape().dims.size() == 2, InvalidShapeError, "Gemm B must be 2D");
+    if (transA || transB) {
+        // The reference sends every transposed Gemm to its float tbn::gemm, quantisation on or off
+        // (model.hpp:763: the binary path requires !transA && !transB).  Here: op(B) is materialised once per
+        // weight tensor, op(A) per call, and the product runs on the float x binary kernel when op(B) is
+        // scaled-binary, on the float path otherwise.
+        const std::string key = transB ? node.inputs[1] + "^T" : node.inputs[1];
+        if (transB && !transposed_.count(key)) transposed_[key] = transpose2d(Bw);
+        const Tensor& Bop = transB ? transposed_.at(key) : Bw;
+        const Tensor Aop = transA ? transpose2d(A) : A;
+        const CachedWeights* cwt = weights_for(key, Bop, false);
+        if (!cwt) throw NotImplementedError("Gemm '" + node.name + "': weights must be FLOAT32");
+        Tensor bias_t;
+        if (C && beta != 0.0f) {
+            TBN_CHECK(C->shape().dims.size() == 1, NotImplementedError, "Gemm: only a 1-D C (bias) is accelerated");
+            if (beta == 1.0f) {
+                bias_t = *C;
+            } else {
+                bias_t = C->to_device(DeviceType::CPU);
+                float* pb = bias_t.typed_data<float>();
+                for (int64_t i = 0; i < bias_t.num_elements(); ++i) pb[i] *= beta;
+            }
+        }
+        intermediate_tensors_[node.outputs[0]] =
+            cwt->dense ? matmul_float_dense(Aop, cwt->dense_w, bias_t.empty() ? nullptr : &bias_t, alpha)
+                       : matmul_float_packed(Aop, cwt->packed, bias_t.empty() ? nullptr : &bias_t, alpha);
+        return;
+    }
     const CachedWeights* cw = weights_for(node.inputs[1], Bw, false);
     if (!cw) throw NotImplementedError("Gemm '" + node.name + "': float weights that are neither scaled-binary nor declared with "
                                        "mark_binary() are not on the accelerated path");
@@ -275,6 +304,37 @@ void TBNModel::Session::execute_node(const ModelNode& node) {
         execute_pool(node, false);
     } else if (op == "GlobalAveragePool" || op == "GlobalAvgPool") {
         intermediate_tensors_[node.outputs.at(0)] = global_avgpool2d(value(node.inputs.at(0)));
+    } else if (op == "GlobalMaxPool") {
+        intermediate_tensors_[node.outputs.at(0)] = global_maxpool2d(value(node.inputs.at(0)));
+    } else if (op == "MatMul") {
+        // model.hpp:879-903: 2-D only, plain float product.
+        TBN_CHECK(node.inputs.size() == 2, InvalidArgumentError, "MatMul expects 2 inputs");
+        const Tensor& A = value(node.inputs[0]);
+        const Tensor& B = value(node.inputs[1]);
+        if (A.shape().dims.size() != 2 || B.shape().dims.size() != 2)
+            throw NotImplementedError("MatMul for non-2D tensors not implemented");
+        const CachedWeights* cw = graph_->initializers.count(node.inputs[1]) ? weights_for(node.inputs[1], B, false) : nullptr;
+        if (cw) intermediate_tensors_[node.outputs.at(0)] = cw->dense ? matmul_float_dense(A, cw->dense_w) : matmul_float_packed(A, cw->packed);
+        else intermediate_tensors_[node.outputs.at(0)] = gemm(A, B);
+    } else if (op == "Greater" || op == "Less") {
+        // model.hpp:1176-1270: the right-hand side is a tensor (usually a scalar initializer) or, when absent
+        // from the tensor map, the node's "value" attribute.
+        TBN_CHECK(node.inputs.size() == 2, InvalidArgumentError, op + " expects 2 inputs");
+        const Tensor& lhs = value(node.inputs[0]);
+        Tensor rhs;
+        auto it = intermediate_tensors_.find(node.inputs[1]);
+        if (it != intermediate_tensors_.end()) {
+            rhs = it->second;
+        } else {
+            float scalar = 0.0f;
+            auto a = node.attributes.find("value");
+            if (a != node.attributes.end()) scalar = a->second.as_float();
+            rhs = make_tensor(Shape{1}, std::vector<float>{scalar});
+        }
+        intermediate_tensors_[node.outputs.at(0)] = op == "Greater" ? greater(lhs, rhs) : less(lhs, rhs);
+    } else if (op == "Sub") {
+        TBN_CHECK(node.inputs.size() == 2, InvalidArgumentError, "Sub expects 2 inputs");
+        intermediate_tensors_[node.outputs.at(0)] = sub(value(node.inputs[0]), value(node.inputs[1]));
     } else if (op == "Add") {
         TBN_CHECK(node.inputs.size() == 2, InvalidArgumentError, "Add expects 2 inputs");
         intermediate_tensors_[node.outputs.at(0)] = add(value(node.inputs[0]), value(node.inputs[1]));
@@ -307,12 +367,9 @@ void TBNModel::Session::execute_node(const ModelNode& node) {
 
 // ------------------------------------------------------------------------- loaders
 
-TBNModel load_onnx_model(const std::string& model_path) {
-    throw InvalidModelError("load_onnx_model('" + model_path + "'): the ONNX protobuf reader is not part of this build; "
-                            "fill a ModelGraph by hand or use parse_graph_spec()");
-}
 TBNModel load_model(const std::string& model_path) { return load_onnx_model(model_path); }
-const char* get_version() { return "0.1.0-b200"; }
+TBNModel load_model_from_buffer(const void* data, size_t size) { return load_onnx_model_from_buffer(data, size); }
+const char* get_version() { return "0.1.0"; }
 
 namespace {
 std::vector<std::string> split(const std::string& s, char sep) {

@@ -269,9 +269,9 @@ bool scaled_binary_channel_scales(const Tensor& weights, std::vector<float>* sca
 Tensor gemm(const Tensor& A, const Tensor& B, const Tensor* C, float alpha, float beta, bool transA, bool transB) {
     TBN_CHECK(A.dtype() == DataType::FLOAT32, InvalidArgumentError, "gemm requires float32 input A");
     TBN_CHECK(B.dtype() == DataType::FLOAT32, InvalidArgumentError, "gemm requires float32 input B");
-    if (transA || transB) throw NotImplementedError("gemm: transposed operands are not on the accelerated path");
     require_f32_2d(A, "A");
     require_f32_2d(B, "B");
+    if (transA || transB) return gemm(transA ? transpose2d(A) : A, transB ? transpose2d(B) : B, C, alpha, beta, false, false);
     // Columns of a scaled-binary B are +-alpha: check on the transposed view (channels = columns).
     const int64_t K = B.shape().dims[0], N = B.shape().dims[1];
     const float* b = B.typed_data<float>();
@@ -442,6 +442,41 @@ Tensor global_avgpool2d(const Tensor& x) {
     const int64_t N = x.shape().dims[0], C = x.shape().dims[1], H = x.shape().dims[2], W = x.shape().dims[3];
     Tensor y = device_f32(Shape{N, C, 1, 1});
     check(tbn_global_avgpool2d(dptr(x), N, C, H, W, static_cast<float*>(y.device_data()), nullptr));
+    y.mark_device_written();
+    return y;
+}
+
+Tensor global_maxpool2d(const Tensor& x) {
+    TBN_CHECK(x.shape().dims.size() == 4, InvalidShapeError, "GlobalMaxPool2D input must be 4D (NCHW)");
+    const int64_t N = x.shape().dims[0], C = x.shape().dims[1], H = x.shape().dims[2], W = x.shape().dims[3];
+    Tensor y = device_f32(Shape{N, C, 1, 1});
+    check(tbn_global_maxpool2d(dptr(x), N, C, H, W, static_cast<float*>(y.device_data()), nullptr));
+    y.mark_device_written();
+    return y;
+}
+
+namespace {
+Tensor elementwise(int op, const Tensor& lhs, const Tensor& rhs, const char* what) {
+    TBN_CHECK(lhs.dtype() == DataType::FLOAT32 && rhs.dtype() == DataType::FLOAT32, InvalidArgumentError,
+              std::string(what) + " requires float32 inputs");
+    TBN_CHECK(rhs.num_elements() > 0, InvalidShapeError, std::string(what) + ": empty right-hand side");
+    Tensor y = device_f32(lhs.shape());
+    check(tbn_binary_elementwise(op, dptr(lhs), lhs.num_elements(), dptr(rhs), rhs.num_elements(),
+                                 static_cast<float*>(y.device_data()), nullptr));
+    y.mark_device_written();
+    return y;
+}
+}  // namespace
+
+Tensor greater(const Tensor& lhs, const Tensor& rhs) { return elementwise(TBN_ELT_GREATER, lhs, rhs, "Greater"); }
+Tensor less(const Tensor& lhs, const Tensor& rhs) { return elementwise(TBN_ELT_LESS, lhs, rhs, "Less"); }
+Tensor sub(const Tensor& lhs, const Tensor& rhs) { return elementwise(TBN_ELT_SUB, lhs, rhs, "Sub"); }
+
+Tensor transpose2d(const Tensor& x) {
+    require_f32_2d(x, "transpose input");
+    const int64_t R = x.shape().dims[0], C = x.shape().dims[1];
+    Tensor y = device_f32(Shape{C, R});
+    check(tbn_transpose2d(dptr(x), R, C, static_cast<float*>(y.device_data()), nullptr));
     y.mark_device_written();
     return y;
 }

@@ -1,7 +1,11 @@
 // Test driver for the C++ host API: reads a graph spec + weight blob + input from files, runs it through
 // tbn::TBNModel::Session and writes the output.  Usage:
 //   run_graph <spec.txt> <blob.f32> <input.f32> <input name> <output name> <quantization 0|1> <out.f32> [repeat]
+//   run_graph --onnx <model.onnx> <input.f32> <input name> <output name> <quantization 0|1> <out.f32> [binary names]
+//   run_graph --dump-onnx <model.onnx>     canonical text listing of the loaded graph (no GPU work)
 // Also exercises the error paths a reference user relies on (exception types), printing "errors ok".
+#include <algorithm>
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -15,6 +19,91 @@ static std::vector<char> read_file(const char* path) {
     std::ifstream f(path, std::ios::binary);
     if (!f) throw std::runtime_error(std::string("cannot open ") + path);
     return std::vector<char>((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+}
+
+static uint64_t fnv1a(const void* data, size_t n) {
+    const unsigned char* p = static_cast<const unsigned char*>(data);
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < n; ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return h;
+}
+
+static std::string join(const std::vector<std::string>& v) {
+    std::string out;
+    for (size_t i = 0; i < v.size(); ++i) out += (i ? "," : "") + v[i];
+    return out;
+}
+
+static std::string dims_of(const tbn::Shape& s) {
+    std::string out;
+    for (size_t i = 0; i < s.dims.size(); ++i) out += (i ? "," : "") + std::to_string(s.dims[i]);
+    return out.empty() ? "-" : out;
+}
+
+// One line per graph element, sorted where the container is unordered, so that two loaders can be compared.
+static int dump_onnx(const char* path) {
+    using namespace tbn;
+    TBNModel model = load_onnx_model(path);
+    const ModelGraph& g = model.graph();
+    std::printf("producer %s|%s\n", model.producer_name().c_str(), model.producer_version().c_str());
+    for (const auto& n : g.inputs) std::printf("input %s %s\n", n.c_str(), dims_of(g.value_info.at(n)).c_str());
+    for (const auto& n : g.outputs) std::printf("output %s %s\n", n.c_str(), dims_of(g.value_info.at(n)).c_str());
+    std::vector<std::string> names;
+    for (const auto& kv : g.value_info) names.push_back(kv.first);
+    std::sort(names.begin(), names.end());
+    for (const auto& n : names) std::printf("value %s %s\n", n.c_str(), dims_of(g.value_info.at(n)).c_str());
+    names.clear();
+    for (const auto& kv : g.initializers) names.push_back(kv.first);
+    std::sort(names.begin(), names.end());
+    for (const auto& n : names) {
+        const Tensor& t = g.initializers.at(n);
+        std::printf("init %s dtype=%d dims=%s bytes=%zu fnv=%016llx\n", n.c_str(), static_cast<int>(t.dtype()),
+                    dims_of(t.shape()).c_str(), t.data_size(), static_cast<unsigned long long>(fnv1a(t.data(), t.data_size())));
+    }
+    for (const auto& node : g.nodes) {
+        std::printf("node %s %s [%s] -> [%s]", node.op_type.c_str(), node.name.c_str(), join(node.inputs).c_str(),
+                    join(node.outputs).c_str());
+        std::vector<std::string> keys;
+        for (const auto& kv : node.attributes) keys.push_back(kv.first);
+        std::sort(keys.begin(), keys.end());
+        for (const auto& k : keys) {
+            const AttributeValue& a = node.attributes.at(k);
+            std::printf(" %s=", k.c_str());
+            if (a.is_int()) std::printf("i:%lld", static_cast<long long>(a.as_int()));
+            else if (a.is_float()) std::printf("f:%.9g", a.as_float());
+            else if (a.is_string()) std::printf("s:%s", a.as_string().c_str());
+            else if (a.is_ints()) { std::printf("I:"); for (size_t i = 0; i < a.as_ints().size(); ++i) std::printf(i ? ",%lld" : "%lld", static_cast<long long>(a.as_ints()[i])); }
+            else if (a.is_floats()) { std::printf("F:"); for (size_t i = 0; i < a.as_floats().size(); ++i) std::printf(i ? ",%.9g" : "%.9g", a.as_floats()[i]); }
+            else if (a.is_tensor()) std::printf("t:%s:%016llx", dims_of(a.as_tensor().shape()).c_str(),
+                                                static_cast<unsigned long long>(fnv1a(a.as_tensor().data(), a.as_tensor().data_size())));
+            else { std::printf("S:"); const auto& v = std::get<std::vector<std::string>>(a.value); for (size_t i = 0; i < v.size(); ++i) std::printf(i ? ",%s" : "%s", v[i].c_str()); }
+        }
+        std::printf("\n");
+    }
+    return 0;
+}
+
+static int run_onnx(int argc, char** argv) {
+    // argv: --onnx model input in_name out_name quant out [binary names]
+    tbn::TBNModel model = tbn::load_model(argv[2]);
+    model.validate();
+    const auto input = read_file(argv[3]);
+    auto session = model.create_session();
+    if (argc > 8) {
+        std::stringstream ss(argv[8]);
+        std::string name;
+        while (std::getline(ss, name, ',')) if (!name.empty()) session.mark_binary(name);
+    }
+    session.set_quantization(std::atoi(argv[6]) != 0);
+    tbn::Tensor x(model.get_input_shape(argv[4]), tbn::DataType::FLOAT32, input.data());
+    if (x.data_size() != input.size()) throw std::runtime_error("input file size does not match the model's input shape");
+    session.set_input(argv[4], x);
+    session.run();
+    tbn::Tensor y = session.get_output(argv[5]);
+    std::ofstream out(argv[7], std::ios::binary);
+    out.write(static_cast<const char*>(static_cast<const void*>(y.typed_data<float>())), static_cast<std::streamsize>(y.data_size()));
+    std::printf("ok %s\n", tbn::shape_to_string(y.shape()).c_str());
+    return 0;
 }
 
 static int error_paths() {
@@ -51,6 +140,8 @@ static int error_paths() {
 int main(int argc, char** argv) {
     try {
         if (argc == 2 && std::strcmp(argv[1], "--errors") == 0) return error_paths();
+        if (argc == 3 && std::strcmp(argv[1], "--dump-onnx") == 0) return dump_onnx(argv[2]);
+        if (argc >= 8 && std::strcmp(argv[1], "--onnx") == 0) return run_onnx(argc, argv);
         if (argc < 8) {
             std::fprintf(stderr, "usage: run_graph spec blob input in_name out_name quant out [repeat]\n");
             return 2;

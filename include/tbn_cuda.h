@@ -309,6 +309,21 @@ int32_t tbn_pool2d(int32_t kind, const float* d_x, int64_t N, int64_t C, int64_t
 int32_t tbn_global_avgpool2d(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float* d_y,
                              void* stream);
 
+/* tbn::global_maxpool2d (pooling.cpp:150-181): [N,C,H,W] -> [N,C,1,1]; a NaN never replaces the maximum. */
+int32_t tbn_global_maxpool2d(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float* d_y,
+                             void* stream);
+/* Session::execute_greater / execute_less / execute_sub (model.hpp:1176-1316): y[i] = x[i] > rhs[i % rhs_n] ? 1 : 0,
+ * y[i] = x[i] < rhs[...] ? 1 : 0, y[i] = x[i] - rhs[...]; float 0/1 results as in the reference, which treats
+ * the following Cast as a pass-through. */
+#define TBN_ELT_GREATER 0
+#define TBN_ELT_LESS 1
+#define TBN_ELT_SUB 2
+int32_t tbn_binary_elementwise(int32_t op, const float* d_x, int64_t n, const float* d_rhs, int64_t rhs_n,
+                               float* d_y, void* stream);
+/* y[cols][rows] = x[rows][cols]^T: the transA / transB forms of tbn::gemm (gemm.cpp:349-360) are materialised
+ * on the device (weights once per tensor, activations per call). */
+int32_t tbn_transpose2d(const float* d_x, int64_t rows, int64_t cols, float* d_y, void* stream);
+
 /* ---- multi-GPU helper -------------------------------------------------------------- */
 
 /* Column-sharded GEMM across G GPUs: rank g computes C[:, g*Nc:(g+1)*Nc] as a contiguous

@@ -26,7 +26,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from fast_arm_tbcnn_b200 import graphs as _recipes  # noqa: E402
-from fast_arm_tbcnn_b200.graphs import conv_layer, lenet, resnet18  # noqa: E402,F401
+from fast_arm_tbcnn_b200.graphs import conv_layer, exported_tbn_cnn, lenet, resnet18  # noqa: E402,F401
 
 
 def binary_alpha(w):
@@ -73,7 +73,10 @@ def run_float(net, x, oracle, keep=None):
     dequantised weights.  ``keep``: optional dict receiving every intermediate."""
     vals = {next(iter(net["inputs"])): np.asarray(x, dtype=np.float32)}
     for name, arr in net["inits"].items():
-        vals[name] = dequantise(arr) if name in net["binary"] else np.asarray(arr, dtype=np.float32)
+        if np.asarray(arr).dtype == np.int64:
+            vals[name] = np.asarray(arr)
+        else:
+            vals[name] = dequantise(arr) if name in net["binary"] else np.asarray(arr, dtype=np.float32)
     for n in net["nodes"]:
         ins = [vals[i] for i in n["inputs"]]
         a = n["attrs"]
@@ -102,6 +105,19 @@ def run_float(net, x, oracle, keep=None):
         elif op == "Gemm":
             out = oracle.gemm_f32(ins[0], ins[1], ins[2] if len(ins) > 2 else None, a.get("alpha", 1.0),
                                   a.get("beta", 1.0), bool(a.get("transA", 0)), bool(a.get("transB", 0)))
+        elif op in ("Greater", "Less"):  # model.hpp:1176-1270: float 0/1, rhs indexed modulo its length
+            rhs = np.resize(ins[1].reshape(-1), ins[0].size).reshape(ins[0].shape)
+            out = ((ins[0] > rhs) if op == "Greater" else (ins[0] < rhs)).astype(np.float32)
+        elif op == "Cast":               # model.hpp:1272-1287: pass-through
+            out = ins[0]
+        elif op == "Sub":                # model.hpp:1289-1316
+            out = (ins[0] - np.resize(ins[1].reshape(-1), ins[0].size).reshape(ins[0].shape)).astype(np.float32)
+        elif op == "Reshape":            # model.hpp:1039-1091
+            out = ins[0].reshape([int(d) for d in ins[1]]).copy()
+        elif op == "MatMul":             # model.hpp:879-903
+            out = oracle.gemm_f32(ins[0], ins[1])
+        elif op == "GlobalMaxPool":      # pooling.cpp:150-181
+            out = ins[0].max(axis=(2, 3), keepdims=True).astype(np.float32)
         else:
             raise NotImplementedError(op)
         vals[n["outputs"][0]] = out

@@ -112,6 +112,15 @@ def main():
     out["lenet_float_session"] = ref.session_run(spec, blob, iblob, "input", xin, "output", (1, 10), False)
     out["lenet_tbn_session"] = ref.session_run(spec, blob, iblob, "input", xin, "output", (1, 10), True)
     np.savez_compressed(os.path.join(HERE, "ref_outputs_small.npz"), **out)
+
+    # The exported MNIST TBN CNN (ternary-activation subgraph, Reshape, Gemm with transB = 1) through the
+    # reference Session, float and quantised, batch 2.
+    net = graphs.exported_tbn_cnn(batch=2, seed=3)
+    xin = np.random.default_rng(5).random((2, 1, 28, 28), dtype=np.float32)
+    spec, blob, iblob = graphs.to_spec(net)
+    np.savez_compressed(os.path.join(HERE, "ref_outputs_exported_cnn.npz"), x=xin,
+                        float_session=ref.session_run(spec, blob, iblob, "input", xin, "output", (2, 10), False),
+                        tbn_session=ref.session_run(spec, blob, iblob, "input", xin, "output", (2, 10), True))
     print("golden fixtures written to", HERE)
 
 

@@ -378,3 +378,34 @@ def test_resnet18_every_weight_layer_on_reference_inputs(tbn, oracle):
             assert err <= TOL_FP32, (node["name"], fast, err)
         checked += 1
     assert checked == 21
+
+
+@pytest.mark.gpu
+def test_elementwise_transpose_and_global_maxpool(tbn):
+    """Greater / Less / Sub with the reference Session's flat modulo broadcast (model.hpp:1176-1316), the 2-D
+    transpose behind transposed Gemm operands, GlobalMaxPool (pooling.cpp:150-181): exact against numpy."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn((3, 5, 7, 6), device="cuda", generator=g)
+    x[0, 0, 0, 0] = float("nan")
+    for rhs in (torch.tensor([0.25], device="cuda"), torch.randn(6, device="cuda", generator=g), torch.randn_like(x)):
+        xn, rn = x.cpu().numpy(), np.resize(rhs.cpu().numpy().reshape(-1), x.numel()).reshape(x.shape)
+        with np.errstate(invalid="ignore"):
+            assert np.array_equal(tbn.lib.binary_elementwise(tbn.ELT_GREATER, x, rhs).cpu().numpy(), (xn > rn).astype(np.float32))
+            assert np.array_equal(tbn.lib.binary_elementwise(tbn.ELT_LESS, x, rhs).cpu().numpy(), (xn < rn).astype(np.float32))
+            assert np.array_equal(tbn.lib.binary_elementwise(tbn.ELT_SUB, x, rhs).cpu().numpy(), xn - rn, equal_nan=True)
+    for shape in ((1, 1), (33, 65), (256, 10), (1000, 31)):
+        m = torch.randn(shape, device="cuda", generator=g)
+        assert torch.equal(tbn.lib.transpose2d(m), m.t().contiguous())
+    xm = x.clone()
+    got = tbn.lib.global_maxpool2d(xm).cpu().numpy()
+    ref = np.full((3, 5, 1, 1), -np.inf, dtype=np.float32)
+    xn = xm.cpu().numpy()
+    for n in range(3):
+        for c in range(5):
+            best = -np.inf
+            for v in xn[n, c].reshape(-1):
+                best = v if best < v else best      # std::max(best, v): a NaN never wins
+            ref[n, c, 0, 0] = best
+    assert np.array_equal(got, ref)
+    tbn.lib.sync()

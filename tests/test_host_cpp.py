@@ -22,7 +22,9 @@ def test_host_layer_builds_and_exports_reference_names(host):
     out = subprocess.run(["nm", "-DC", lib], capture_output=True, text=True, check=True).stdout
     for name in ["tbn::qlinear_matmul_binary(", "tbn::quantize_to_binary(", "tbn::quantize_to_ternary(",
                  "tbn::conv2d_binary(", "tbn::conv2d_binary_with_scales(", "tbn::conv2d(", "tbn::gemm(",
-                 "tbn::maxpool2d(", "tbn::avgpool2d(", "tbn::global_avgpool2d(", "tbn::load_onnx_model(",
+                 "tbn::maxpool2d(", "tbn::avgpool2d(", "tbn::global_avgpool2d(", "tbn::global_maxpool2d(", "tbn::load_onnx_model(",
+                 "tbn::load_onnx_model_from_buffer(", "tbn::load_model(", "tbn::load_model_from_buffer(", "tbn::get_version(",
+                 "tbn::OnnxParser::parse_from_file(", "tbn::OnnxParser::parse_from_buffer(", "tbn::OnnxParser::get_graph(",
                  "tbn::TBNModel::Session::set_input(", "tbn::TBNModel::Session::run(",
                  "tbn::TBNModel::Session::get_output(", "tbn::Tensor::to_device("]:
         assert name in out, name
@@ -89,3 +91,48 @@ def test_resnet18_through_cpp_session(host, oracle, tmp_path):
         got = _run(host[1], tmp_path, net, x, False, (1, 100), dequantised)
         assert rel_l2(got, expect) <= 1e-5
         assert got.argmax() == expect.argmax()
+
+
+def _run_onnx(driver, tmp_path, model_bytes, x, quant, out_shape, binary=""):
+    (tmp_path / "model.onnx").write_bytes(model_bytes)
+    np.ascontiguousarray(x, dtype=np.float32).tofile(tmp_path / "x.f32")
+    out = tmp_path / f"onnx_out_{quant}.f32"
+    cmd = [driver, "--onnx", str(tmp_path / "model.onnx"), str(tmp_path / "x.f32"), "input", "output", str(int(quant)), str(out)]
+    proc = subprocess.run(cmd + ([binary] if binary else []), capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stderr
+    return np.fromfile(out, dtype=np.float32).reshape(out_shape)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("storage", ["raw", "typed_fields"])
+def test_exported_tbn_cnn_from_onnx_file(host, golden, tmp_path, storage):
+    """load_model on an ONNX file of the exported MNIST TBN CNN (ternary-activation subgraph written as
+    Greater / Cast / Less / Cast / Sub, Reshape, Gemm with transB = 1), then Session::run: float mode within
+    1e-5 of the reference Session's stored output; quantised mode: the integer convolutions are bit-equal, the
+    final transposed Gemm is the reference's float gemm, so 1e-5 there too, and the classes agree."""
+    import onnx_schema
+    from fast_arm_tbcnn_b200 import graphs
+    net = graphs.exported_tbn_cnn(batch=2, seed=3)
+    extra = {"float_data": ("conv1_w", "conv2_b", "thr_hi", "flat_shape")} if storage == "typed_fields" else {}
+    model = onnx_schema.net_to_onnx(net, **extra)
+    ref = golden["ref_outputs_exported_cnn"]
+    got = _run_onnx(host[1], tmp_path, model, ref["x"], False, (2, 10))
+    assert rel_l2(got, ref["float_session"]) <= 1e-5
+    assert np.array_equal(got.argmax(axis=1), ref["float_session"].argmax(axis=1))
+    got_q = _run_onnx(host[1], tmp_path, model, ref["x"], True, (2, 10))
+    assert rel_l2(got_q, ref["tbn_session"]) <= 1e-5
+    assert np.array_equal(got_q.argmax(axis=1), ref["tbn_session"].argmax(axis=1))
+
+
+@pytest.mark.gpu
+def test_lenet_from_onnx_file_matches_the_spec_path(host, oracle, golden, tmp_path):
+    """The same LeNet through both loaders (ONNX file, text spec) gives identical bits; raw weights are declared
+    binary by name on the command line."""
+    import onnx_schema
+    from oracle import graphs
+    net = graphs.lenet(batch=1, seed=1)
+    x = golden["ref_outputs_small"]["lenet_x"]
+    via_spec = _run(host[1], tmp_path, net, x, False, (1, 10), False)
+    via_onnx = _run_onnx(host[1], tmp_path, onnx_schema.net_to_onnx(net), x, False, (1, 10), binary=",".join(sorted(net["binary"])))
+    assert np.array_equal(via_spec, via_onnx)
+    assert rel_l2(via_onnx, graphs.run_float(net, x, oracle)) <= 1e-5
