@@ -53,6 +53,8 @@ enum DeviceError : int {
     kErrWaitFullB = 3,      // MMA waited for the unpacked weight tile
     kErrWaitTmemFull = 4,   // epilogue waited for the accumulator
     kErrWaitTmemEmpty = 5,  // MMA waited for the epilogue to drain the accumulator
+    kErrPackWaitFull = 6,   // weight pack: consumers waited for a TMA tile
+    kErrPackWaitEmpty = 7,  // weight pack: the producer waited for a free stage
 };
 
 // ---- epilogue ----------------------------------------------------------------------

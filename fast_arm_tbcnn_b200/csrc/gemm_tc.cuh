@@ -767,24 +767,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 // Host-side helpers shared by the GEMM and convolution entry points
 // =====================================================================================
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess) {
-            cudaGetLastError();
-            sym = nullptr;
-        }
-        return reinterpret_cast<EncodeTiledFn>(sym);
-    }();
-    return fn;
-}
-
 inline int pick_bn(int64_t N) {
     // Largest tile whose padding waste stays within ~12 % of the best candidate.
     const int cand[3] = {256, 128, 64};

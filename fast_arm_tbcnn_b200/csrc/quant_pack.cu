@@ -9,9 +9,12 @@
 // Packed layout (all planes): uint32 word[n * (K_pad/32) + k/32], bit (k % 32);
 // K_pad = ceil128(K), N_pad = ceil8(N); padding bits are 0.
 // Comparisons are IEEE (no flush-to-zero on the compare, NaN compares false).
+#include <algorithm>
 #include <mutex>
+#include <string>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace tbn_cuda {
 namespace {
@@ -154,6 +157,143 @@ __global__ void __launch_bounds__(128) pack_kn_vec4_kernel(const float* __restri
     }
 }
 
+// Layout KN, streaming variant for large matrices: persistent CTAs (one per SM), a producer warp that keeps a
+// ring of TMA tiles in flight and eight consumer warps that classify from shared memory.
+//   job   = 128 (k) x 512 (n) block of W: four tiles of 32 rows x 512 columns, each row 2 KB contiguous in HBM;
+//   tile  = two TMA boxes of 32 x 256 fp32 (32 KB each); kPackStages tiles in flight per SM;
+//   thread t owns columns t and 256 + t of the job: conflict-free shared-memory reads (lane = bank), one word
+//   per tile and plane, one uint4 (128 k) per column and plane at the end of the job.
+// Jobs are numbered strip-fastest, so CTAs running at the same time read neighbouring 2 KB pieces of the same
+// rows.  The partial |w| sums per 128-row chunk are accumulated in the same order as in the other kernels.
+constexpr int kPackStages = 3;
+constexpr int kPackTileRows = 32, kPackBoxCols = 256, kPackJobCols = 512;
+constexpr int kPackBoxBytes = kPackTileRows * kPackBoxCols * 4;
+constexpr int kPackTileBytes = 2 * kPackBoxBytes;
+constexpr int kPackConsumers = 256;
+constexpr int kPackSmemBytes = kPackStages * kPackTileBytes + 1024 + 256;
+
+template <bool TERNARY>
+__global__ void __launch_bounds__(kPackConsumers + 32, 1)
+pack_kn_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, int64_t K, int64_t N, float lo, float hi, int ge,
+                   uint32_t* __restrict__ neg_words, uint32_t* __restrict__ pos_words, int64_t KW, int64_t N_pad,
+                   float* __restrict__ part_sum, float* __restrict__ part_cnt, int64_t strips, int64_t jobs,
+                   int* err_word) {
+    extern __shared__ uint8_t pack_smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(pack_smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const float* tiles = reinterpret_cast<const float*>(pack_smem_raw + (base - raw_addr));
+    const uint32_t bar_full = base + kPackStages * kPackTileBytes;
+    const uint32_t bar_empty = bar_full + 8 * kPackStages;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPackStages; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, kPackConsumers);
+        }
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    __syncthreads();
+
+    if (threadIdx.x >= kPackConsumers) {
+        // ---------------------------------------------------------------- producer warp (one lane)
+        if (threadIdx.x == kPackConsumers) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int64_t job = blockIdx.x; job < jobs; job += gridDim.x) {
+                const int64_t strip = job % strips, chunk = job / strips;
+                bool ok = true;
+                for (int sub = 0; sub < 4 && ok; ++sub) {
+                    if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, err_word, kErrPackWaitEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = bar_full + 8 * stage;
+                    const uint32_t dst = base + stage * kPackTileBytes;
+                    const int x = static_cast<int>(strip * kPackJobCols);
+                    const int y = static_cast<int>(chunk * kChunkK + sub * kPackTileRows);
+                    ptx::mbar_arrive_expect_tx(bar, kPackTileBytes);
+                    ptx::tma_load_2d(dst, &tmap_w, x, y, bar);                       // out-of-range parts arrive as zeros
+                    ptx::tma_load_2d(dst + kPackBoxBytes, &tmap_w, x + kPackBoxCols, y, bar);
+                    if (++stage == kPackStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    const int t = threadIdx.x;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int64_t job = blockIdx.x; job < jobs; job += gridDim.x) {
+        const int64_t strip = job % strips, chunk = job / strips;
+        const int64_t n0 = strip * kPackJobCols + t, n1 = n0 + kPackBoxCols;
+        uint32_t negw[2][4], posw[2][4];
+        float sum[2] = {0.f, 0.f}, cnt[2] = {0.f, 0.f};
+#pragma unroll
+        for (int sub = 0; sub < 4; ++sub) {
+            if (!ptx::mbar_wait(bar_full + 8 * stage, phase, err_word, kErrPackWaitFull)) return;
+            const float* tile = tiles + stage * (kPackTileBytes / 4) + t;
+            const int64_t k0 = chunk * kChunkK + sub * kPackTileRows;
+            const int rows = static_cast<int>(min(static_cast<int64_t>(kPackTileRows), K - k0));  // <= 0 past the end
+            uint32_t nb[2] = {0u, 0u}, pb[2] = {0u, 0u};
+#pragma unroll
+            for (int r = 0; r < kPackTileRows; ++r) {
+                const float e[2] = {tile[r * kPackBoxCols], tile[kPackBoxBytes / 4 + r * kPackBoxCols]};
+                if (r < rows) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const uint32_t c = classify<TERNARY>(e[j], lo, hi, ge);
+                        nb[j] |= (c & 1u) << r;
+                        if (TERNARY) {
+                            pb[j] |= (c >> 1) << r;
+                            if (c) {
+                                sum[j] += fabsf(e[j]);
+                                cnt[j] += 1.0f;
+                            }
+                        } else {
+                            sum[j] += fabsf(e[j]);
+                        }
+                    }
+                }
+            }
+            // The stage goes back to the producer only after every value read above has arrived in registers:
+            // the arrive is made to depend on them.
+            ptx::mbar_arrive_after(bar_empty + 8 * stage, nb[0] ^ nb[1] ^ pb[0] ^ pb[1] ^ __float_as_uint(sum[0]) ^ __float_as_uint(sum[1]));
+            if (++stage == kPackStages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                negw[j][sub] = nb[j];
+                posw[j][sub] = pb[j];
+            }
+        }
+        const int64_t ns[2] = {n0, n1};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int64_t n = ns[j];
+            if (n >= N_pad) continue;
+            const bool real = n < N;  // columns N .. N_pad-1 are padding: all bits 0
+            const int64_t widx = n * KW + chunk * 4;
+            *reinterpret_cast<uint4*>(neg_words + widx) =
+                real ? make_uint4(negw[j][0], negw[j][1], negw[j][2], negw[j][3]) : make_uint4(0u, 0u, 0u, 0u);
+            if (TERNARY)
+                *reinterpret_cast<uint4*>(pos_words + widx) =
+                    real ? make_uint4(posw[j][0], posw[j][1], posw[j][2], posw[j][3]) : make_uint4(0u, 0u, 0u, 0u);
+            if (part_sum && real) {
+                part_sum[chunk * N + n] = sum[j];
+                if (TERNARY) part_cnt[chunk * N + n] = cnt[j];
+            }
+        }
+    }
+}
+
 // Layout NK: W[n*ldw + k] (k contiguous).  One warp packs one 128-k chunk of one column:
 // four coalesced 128 B reads, four ballots.
 template <bool TERNARY>
@@ -293,7 +433,28 @@ int32_t quant_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t 
     const unsigned gy = static_cast<unsigned>((chunks + 3) / 4);
     const bool wide = layout == TBN_LAYOUT_KN && N % 4 == 0 && ldw % 4 == 0 && reinterpret_cast<uintptr_t>(d_w) % 16 == 0 &&
                       (!part_sum || reinterpret_cast<uintptr_t>(part_sum) % 16 == 0) && N >= 128;
-    if (wide) {
+    // Large matrices stream through TMA; the register kernels keep the small and the unaligned ones.
+    const bool stream = wide && K * N >= (1LL << 22) && N < (1LL << 31) && K < (1LL << 31) && device_error_word() != nullptr;
+    if (stream) {
+        EncodeTiledFn encode = encode_tiled_fn();
+        TBN_REQUIRE(encode != nullptr, TBN_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+        CUtensorMap tmap;
+        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K)};
+        const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ldw) * 4};
+        const cuuint32_t box[2] = {kPackBoxCols, kPackTileRows};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(d_w), gdim, gstride, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
+                    "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(cr)));
+        const int64_t strips = (N_pad + kPackJobCols - 1) / kPackJobCols, jobs = strips * chunks;
+        auto kernel = pack_kn_tma_kernel<TERNARY>;
+        TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPackSmemBytes));
+        const int grid = static_cast<int>(std::min<int64_t>(jobs, std::max(sm_count(), 1)));
+        kernel<<<grid, kPackConsumers + 32, kPackSmemBytes, st>>>(tmap, K, N, lo, hi, ge, d_neg, d_pos, KW, N_pad, part_sum,
+                                                                  part_cnt, strips, jobs, device_error_word());
+    } else if (wide) {
         dim3 grid(static_cast<unsigned>((N_pad + 127) / 128), gy);
         pack_kn_vec4_kernel<TERNARY><<<grid, 128, 0, st>>>(d_w, K, N, ldw, lo, hi, ge, d_neg, d_pos, KW, N_pad, part_sum,
                                                            part_cnt);

@@ -2,12 +2,14 @@
 
     python -m fast_arm_tbcnn_b200.host_build [--force]
 
-Produces host/lib/libtbn_host.so (links against lib/libtbn_cuda.so) and host/bin/run_graph.
+Produces host/lib/libtbn_host.so (links against lib/libtbn_cuda.so), host/bin/run_graph and the Python
+module host/lib/_tbn<ext suffix> (pybind11; `sys.path.insert(0, "host/lib"); import _tbn`).
 """
 import glob
 import os
 import subprocess
 import sys
+import sysconfig
 
 from . import build as _cuda_build
 
@@ -15,6 +17,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HOST = os.path.join(ROOT, "host")
 LIB = os.path.join(HOST, "lib", "libtbn_host.so")
 RUN_GRAPH = os.path.join(HOST, "bin", "run_graph")
+PY_MODULE = os.path.join(HOST, "lib", "_tbn" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 
 def _stale(target, deps):
@@ -46,7 +49,24 @@ def build(force=False):
         if proc.returncode != 0:
             sys.stderr.write(proc.stdout + proc.stderr)
             raise RuntimeError("g++ failed building " + RUN_GRAPH)
+    build_python_module(force, cxx, inc, cuda_dir, hdrs)
     return LIB, RUN_GRAPH
+
+
+def build_python_module(force=False, cxx="g++", inc=(), cuda_dir="", hdrs=()):
+    """The `_tbn` extension module (same Python API as the reference's pybind module)."""
+    import pybind11
+    src = os.path.join(HOST, "python", "bindings.cpp")
+    if force or _stale(PY_MODULE, [src, LIB] + list(hdrs)):
+        cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-o", PY_MODULE,
+               "-I", sysconfig.get_paths()["include"], "-I", pybind11.get_include()] + list(inc) + [
+               src, "-L", os.path.dirname(LIB), "-ltbn_host", "-L", cuda_dir, "-ltbn_cuda", "-Wl,-rpath,$ORIGIN",
+               "-Wl,-rpath,$ORIGIN/../../fast_arm_tbcnn_b200/lib"]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+            raise RuntimeError("g++ failed building " + PY_MODULE)
+    return PY_MODULE
 
 
 if __name__ == "__main__":

@@ -10,7 +10,10 @@ pytestmark = pytest.mark.gpu
 # error of about sqrt(K) * 2^-24; the kernel sums 128-row chunks, so the two agree to that level.
 ALPHA_RTOL = 1e-5
 
-SHAPES = [(64, 8), (128, 8), (200, 37), (576, 128), (1, 1), (129, 9), (1000, 300), (4608, 512)]
+# The last three are large enough (K*N >= 2^22) for the TMA-streamed kernel: ragged K, N off the 512-column
+# job width, and an exact multiple.
+SHAPES = [(64, 8), (128, 8), (200, 37), (576, 128), (1, 1), (129, 9), (1000, 300), (4608, 512),
+          (2500, 1700), (2049, 2052), (4096, 1024)]
 
 
 @pytest.fixture(scope="module")
