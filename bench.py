@@ -228,7 +228,7 @@ def cnn_block(args, L, capi, torch, dist, dev, rank, world):
     bias = torch.randn(128, generator=g, device=dev) * 0.05
     order = capi.CONV_WEIGHTS_TAP_MAJOR
     words, alpha = L.quant_pack_binary(L.permute_filters(w), capi.LAYOUT_NK)
-    ws, _ = L.conv_workspace(x.shape, 3, 3, dev, order)
+    ws, _ = L.conv_workspace(x.shape, 128, 3, 3, dev, order)
     y = torch.empty((b1 - b0, 128, 14, 14), device=dev)
     p = (1, 1, 1, 1, 1, 1)
     ms = timed(lambda: L.conv2d_fxb(x, words, w.shape, p, alpha=alpha, bias=bias, workspace=ws, out=y, order=order), 10)

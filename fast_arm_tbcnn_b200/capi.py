@@ -38,7 +38,7 @@ SIGNATURES = {
     "tbn_gemm_f32": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _f32, _vp, _vp, _i64, _u32, _vp, _sz, _vp]),
     "tbn_conv2d_f32": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp,
                               _vp, _u32, _i32, _vp, _sz, _vp]),
-    "tbn_conv2d_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64, _i32]),
+    "tbn_conv2d_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32]),
     "tbn_permute_filters": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp]),
     "tbn_conv2d_fxb": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
                               _vp, _f32, _vp, _vp, _vp, _i32, _u32, _i32, _vp, _sz, _vp]),
@@ -314,10 +314,10 @@ class _Lib:
             return 0, 0  # the library rejects the call; the output shape does not matter
         return (H + 2 * ph - dh * (kh - 1) - 1) // sh + 1, (W + 2 * pw - dw * (kw - 1) - 1) // sw + 1
 
-    def conv_workspace(self, xshape, kh, kw, device, order=CONV_WEIGHTS_REFERENCE):
+    def conv_workspace(self, xshape, m_out, kh, kw, device, order=CONV_WEIGHTS_REFERENCE):
         import torch
         N, Cc, H, W = xshape
-        nbytes = self.h.tbn_conv2d_workspace_bytes(N, Cc, H, W, kh, kw, order)
+        nbytes = self.h.tbn_conv2d_workspace_bytes(N, Cc, H, W, m_out, kh, kw, order)
         return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device), nbytes
 
     def permute_filters(self, w):
@@ -342,7 +342,7 @@ class _Lib:
         if out is None:
             out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
         if workspace is None:
-            workspace, nbytes = self.conv_workspace(x.shape, kh, kw, x.device, order)
+            workspace, nbytes = self.conv_workspace(x.shape, M_out, kh, kw, x.device, order)
         else:
             nbytes = workspace.numel()
         if residual is not None:
@@ -363,7 +363,7 @@ class _Lib:
         if out is None:
             out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
         if workspace is None:
-            workspace, nbytes = self.conv_workspace(x.shape, kh, kw, x.device, order)
+            workspace, nbytes = self.conv_workspace(x.shape, M_out, kh, kw, x.device, order)
         else:
             nbytes = workspace.numel()
         check(self.h.tbn_conv2d_tbn(_ptr(x), N, Cc, H, W, lo, hi, _ptr(neg), M_out, kh, kw, *[int(v) for v in p],
@@ -407,7 +407,7 @@ class _Lib:
         if out is None:
             out = torch.empty((N, M_out, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
         if workspace is None:
-            workspace, nbytes = self.conv_workspace(x.shape, kh, kw, x.device, order)
+            workspace, nbytes = self.conv_workspace(x.shape, M_out, kh, kw, x.device, order)
         else:
             nbytes = workspace.numel()
         if residual is not None:

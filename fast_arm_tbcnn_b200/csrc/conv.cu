@@ -77,6 +77,22 @@ __global__ void permute_filters_kernel(const float* __restrict__ w, int64_t M, i
     }
 }
 
+// Sign words [N_pad][KW] -> bf16 [N_pad][K_pad] (+1 = 0x3F80, -1 = 0xBF80, ternary zero = 0): the weight operand
+// of the convolutions, expanded once per call so that the GEMM kernel takes it by TMA.  One word (32 k, 64 output
+// bytes) per thread; a warp writes 2 KB contiguous.
+__global__ void expand_words_kernel(const uint32_t* __restrict__ neg, const uint32_t* __restrict__ pos, int64_t words,
+                                    uint4* __restrict__ out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += stride) {
+        const uint32_t nw = __ldg(neg + i), pw = pos ? __ldg(pos + i) : 0u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t nb = (nw >> (8 * q)) & 0xffu, pb = (pw >> (8 * q)) & 0xffu;
+            out[i * 4 + q] = pos ? unpack8<true>(nb, pb) : unpack8<false>(nb, pb);
+        }
+    }
+}
+
 struct ConvArgs {
     const void* dense_w = nullptr;  // split dense weights (float filters) instead of packed planes
     const float* x;
@@ -98,6 +114,9 @@ size_t xs_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int npass) {
 }
 
 size_t table_bytes(int64_t K_pad) { return static_cast<size_t>(round_up(K_pad * static_cast<int64_t>(sizeof(int2)), 256)); }
+
+// Expanded (bf16) copy of the packed filters, after the partial-sum tiles in the workspace.
+size_t expanded_bytes(int64_t K_pad, int64_t N_pad) { return static_cast<size_t>(round_up(K_pad * N_pad * 2, 256)); }
 
 int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float hi) {
     TBN_REQUIRE(a.N > 0 && a.C > 0 && a.H > 0 && a.W > 0 && a.M_out > 0 && a.kh > 0 && a.kw > 0, TBN_INVALID_SHAPE,
@@ -122,7 +141,8 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     TBN_REQUIRE(a.weight_order == TBN_CONV_WEIGHTS_REFERENCE || fast, TBN_INVALID_ARGUMENT, "conv2d: unknown weight order");
     TBN_REQUIRE(!fast || a.C % 64 == 0, TBN_INVALID_ARGUMENT,
                 "conv2d: tap-major weights need a channel count that is a multiple of 64");
-    const size_t need = (fast ? xs_bytes(a.N, a.C, a.H, a.W, npass) : table_bytes(K_pad)) + scratch_bytes();
+    const size_t front_bytes = fast ? xs_bytes(a.N, a.C, a.H, a.W, npass) : table_bytes(K_pad);
+    const size_t need = front_bytes + scratch_bytes() + (a.dense_w ? 0 : expanded_bytes(K_pad, N_pad));
     TBN_REQUIRE(a.ws && a.ws_bytes >= need, TBN_INVALID_ARGUMENT,
                 "conv2d: workspace too small (see tbn_conv2d_workspace_bytes)");
     TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.ws) % 128 == 0, TBN_INVALID_ARGUMENT,
@@ -167,10 +187,17 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
         if (rc) return rc;
         maps.pos = maps.neg;
     } else {
-        rc = make_word_map(encode, a.neg, K_pad / 32, N_pad, bn, &maps.neg);
+        // Packed filters are expanded to bf16 once per call (a few MB at most, L2 resident) and then arrive by TMA
+        // like float filters do, so that the build warps spend their instructions on the activation gather only.
+        uint4* expanded = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.ws) + front_bytes + scratch_bytes());
+        const int64_t words = N_pad * (K_pad / 32);
+        const int grid = static_cast<int>(std::max<int64_t>(1, std::min((words + 255) / 256, static_cast<int64_t>(std::max(sm_count(), 1)) * 8)));
+        expand_words_kernel<<<grid, 256, 0, a.st>>>(a.neg, a.pos, words, expanded);
+        rc = launched("expand_words_kernel");
         if (rc) return rc;
-        rc = make_word_map(encode, a.pos ? a.pos : a.neg, K_pad / 32, N_pad, bn, &maps.pos);
+        rc = make_split_map(encode, expanded, K_pad, N_pad, 1, bn, &maps.neg);
         if (rc) return rc;
+        maps.pos = maps.neg;
     }
     maps.a = maps.neg;  // unused in CONV mode
 
@@ -188,8 +215,7 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.err_word = device_error_word();
     p.c_vec_ok = 0;
     set_segments(p, npass);
-    p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.ws) +
-                                          (fast ? xs_bytes(a.N, a.C, a.H, a.W, npass) : table_bytes(K_pad)));
+    p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.ws) + front_bytes);
     p.conv.xs = xs;
     p.conv.xs_term_stride = term_stride;
     p.conv.kw = static_cast<int>(a.kw);
@@ -210,24 +236,22 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.conv.pw = a.pw;
     p.conv.act_lo = lo;
     p.conv.act_hi = hi;
-    const bool ternary_w = a.pos != nullptr;
+    // Weight source: 1 = two-term float filters, 2 = expanded sign filters (binary and ternary alike).
     if (fast) {
         if (a.dense_w) {
             set_segments(p, 3);
-            return dispatch_bn<2, false, 2, false, true>(bn, maps, p, a.st);
+            return dispatch_bn<2, false, 2, false, 1>(bn, maps, p, a.st);
         }
-        if (tern_act || npass == 1)
-            return ternary_w ? dispatch_bn<1, true, 2, false>(bn, maps, p, a.st) : dispatch_bn<1, false, 2, false>(bn, maps, p, a.st);
-        return ternary_w ? dispatch_bn<2, true, 2, false>(bn, maps, p, a.st) : dispatch_bn<2, false, 2, false>(bn, maps, p, a.st);
+        if (tern_act || npass == 1) return dispatch_bn<1, false, 2, false, 2>(bn, maps, p, a.st);
+        return dispatch_bn<2, false, 2, false, 2>(bn, maps, p, a.st);
     }
     if (a.dense_w) {
         set_segments(p, 3);
-        return dispatch_bn<2, false, 1, false, true>(bn, maps, p, a.st);
+        return dispatch_bn<2, false, 1, false, 1>(bn, maps, p, a.st);
     }
-    if (tern_act) return dispatch_bn<1, false, 1, true>(bn, maps, p, a.st);
-    if (npass == 1)
-        return ternary_w ? dispatch_bn<1, true, 1, false>(bn, maps, p, a.st) : dispatch_bn<1, false, 1, false>(bn, maps, p, a.st);
-    return ternary_w ? dispatch_bn<2, true, 1, false>(bn, maps, p, a.st) : dispatch_bn<2, false, 1, false>(bn, maps, p, a.st);
+    if (tern_act) return dispatch_bn<1, false, 1, true, 2>(bn, maps, p, a.st);
+    if (npass == 1) return dispatch_bn<1, false, 1, false, 2>(bn, maps, p, a.st);
+    return dispatch_bn<2, false, 1, false, 2>(bn, maps, p, a.st);
 }
 
 }  // namespace
@@ -237,10 +261,13 @@ using namespace tbn_cuda;
 
 extern "C" {
 
-size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t kh, int64_t kw, int32_t weight_order) {
-    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0) return 0;
-    const size_t front = weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR ? xs_bytes(N, C, H, W, 2) : table_bytes(round_up(C * kh * kw, 128));
-    return front + static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float);
+size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t M_out, int64_t kh, int64_t kw,
+                                  int32_t weight_order) {
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || M_out <= 0 || kh <= 0 || kw <= 0) return 0;
+    const int64_t K_pad = round_up(C * kh * kw, 128);
+    const size_t front = weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR ? xs_bytes(N, C, H, W, 2) : table_bytes(K_pad);
+    return front + static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float) +
+           expanded_bytes(K_pad, round_up(M_out, 8));
 }
 
 int32_t tbn_permute_filters(const float* d_w, int64_t M, int64_t C, int64_t taps, float* d_out, void* stream) {

@@ -289,7 +289,7 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     if (dense_w) {
         p.num_kb = static_cast<int>(K_pad / tc::BK);
         set_segments(p, 3);  // three MMA passes per k-block
-        return dispatch_bn<2, false, 0, false, true>(bn, maps, p, st);
+        return dispatch_bn<2, false, 0, false, 1>(bn, maps, p, st);
     }
     const bool ternary_w = d_pos != nullptr;
     if (npass == 1)

@@ -21,9 +21,11 @@
 // accumulator, and the epilogue adds the segments in fp32 (round to nearest) through a per-CTA scratch
 // tile that stays resident in L2.
 //
-// DENSE mode (float weights: the float x float Gemm / Conv of the CNN graphs): the weight operand is not
-// unpacked from bits but arrives by TMA as two pre-split bf16 terms, and the MMA issuer forms
-// hi*hi + hi*lo + lo*hi.
+// Weight source BSRC.  0: packed sign words, unpacked by the build warps (the GEMM).  1: float weights (the
+// float x float Gemm / Conv of the CNN graphs) arriving by TMA as two pre-split bf16 terms; the MMA issuer
+// forms hi*hi + hi*lo + lo*hi.  2: sign weights already expanded to +-1/0 bf16 (one term) arriving by TMA --
+// the convolutions, whose small weight matrices are expanded once per call and stay in L2, so that the
+// build warps only gather activations.
 //
 // Every wait is bounded and reports through the library's device error word.
 #pragma once
@@ -108,9 +110,10 @@ constexpr int kMaxAccumSteps = 4096;
 // Operand modes that lower a convolution (see AMODE at the kernel).
 __host__ __device__ constexpr bool is_conv_mode(int amode) { return amode == 1 || amode == 2; }
 
-template <int BN, int NPASS, bool TERNARY, bool DENSE = false, bool CONV = false>
+template <int BN, int NPASS, bool TERNARY, int BSRC = 0, bool CONV = false>
 struct Cfg {
-    static constexpr int kWordStages = DENSE ? 1 : (CONV ? kWordStagesConv : kWordStagesGemm);  // dense weights use no words
+    static constexpr bool DENSE = BSRC == 1;
+    static constexpr int kWordStages = BSRC != 0 ? 1 : (CONV ? kWordStagesConv : kWordStagesGemm);  // TMA-fed weights use no words
     static constexpr int B_TILE_BYTES = BN * BK * 2;
     static constexpr int B_TERMS = DENSE ? 2 : 1;  // dense weights: hi and lo bf16 terms
     static constexpr int B_BYTES = B_TERMS * B_TILE_BYTES;
@@ -181,13 +184,13 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gm;
 }
 
-// tmap_a: split activations (GEMM mode).  tmap_neg / tmap_pos: packed word planes; in DENSE mode tmap_neg is
+// tmap_a: split activations (GEMM mode).  tmap_neg / tmap_pos: packed word planes; with BSRC 1 or 2 tmap_neg is
 // the map of the split weights [2][N_pad][K_pad] instead.
 // AMODE: source of the activation operand.  0 = TMA from pre-split [terms][M][K] (plain GEMM);
 // 1 = element-wise gather from NCHW fp32 (any convolution geometry); 2 = cp.async from the channels-last
 // bf16 copy (convolutions with C % 64 == 0); 3 = the fp32 rows of A read by the build warps and split in
 // registers (plain GEMM without the separate split pass; loads run two k-blocks ahead of their use).
-template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE>
+template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_neg,
                                                               const __grid_constant__ CUtensorMap tmap_pos,
@@ -196,13 +199,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     constexpr bool FAST = AMODE == 2;
     constexpr bool ROWS = AMODE == 3;
     constexpr bool BUILT_A = CONV || ROWS;  // the build warps write the activation operand
-    static_assert(!(ROWS && DENSE), "float weights take their activations by TMA or by the convolution gathers");
-    using C = Cfg<BN, NPASS, TERNARY, DENSE, CONV>;
+    constexpr bool DENSE = BSRC == 1;      // two-term float weights
+    constexpr bool TMA_B = BSRC != 0;      // the weight tile arrives by TMA instead of being unpacked here
+    static_assert(!(ROWS && TMA_B), "TMA-fed weights take their activations by TMA or by the convolution gathers");
+    static_assert(BSRC != 2 || !TERNARY, "expanded weights carry their zeros themselves");
+    using C = Cfg<BN, NPASS, TERNARY, BSRC, CONV>;
     constexpr int kWordStages = C::kWordStages;
     static_assert(!DENSE || (NPASS == 2 && !TERNARY && !TERN_ACT), "dense weights use the two-term split on both sides");
     // Which operands arrive by TMA (signalled on full_a) and which are built by the build warps (full_b).
-    constexpr bool kTmaOperands = !BUILT_A || DENSE;
-    constexpr bool kBuiltOperands = BUILT_A || !DENSE;
+    constexpr bool kTmaOperands = !BUILT_A || TMA_B;
+    constexpr bool kBuiltOperands = BUILT_A || !TMA_B;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -266,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 int tm, tn;
                 tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!DENSE && (kb & 1) == 0) {
+                    if (!TMA_B && (kb & 1) == 0) {
                         // Packed words of k-blocks kb and kb+1 for the BN columns of this tile
                         // (rows past the end of the plane are zero-filled by TMA).
                         if (!ptx::mbar_wait(bar_empty_w + 8 * wstage, wphase ^ 1u, p.err_word, kErrWaitEmpty)) {
@@ -289,12 +295,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             break;
                         }
                         const uint32_t bar = bar_full_a + 8 * stage;
-                        ptx::mbar_arrive_expect_tx(bar, (BUILT_A ? 0 : NPASS * A_TILE_BYTES) + (DENSE ? C::B_BYTES : 0));
+                        ptx::mbar_arrive_expect_tx(bar, (BUILT_A ? 0 : NPASS * A_TILE_BYTES) + (TMA_B ? C::B_BYTES : 0));
                         const uint32_t b_dst = base + stage * C::STAGE_BYTES;
                         const uint32_t a_dst = b_dst + C::B_BYTES;
-                        if (DENSE) {
+                        if (TMA_B) {
 #pragma unroll
-                            for (int q = 0; q < 2; ++q)
+                            for (int q = 0; q < C::B_TERMS; ++q)
                                 ptx::tma_load_3d(b_dst + q * C::B_TILE_BYTES, &tmap_neg, kb * BK, tn * BN, q, bar);
                         }
                         if (!BUILT_A) {
@@ -424,8 +430,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             bool row_valid = false;
             const float* xwin = nullptr;
             int f_ih0[4], f_iw0[4];
-            int64_t f_img[4];
+            int64_t f_base[4];  // element offset of (image, window origin, this thread's 8 channels) in xs
             bool f_valid[4];
+            int f_cb = 0, f_ti = 0, f_tj = 0;  // channel block and filter tap of the current k-block
             if (CONV && !FAST) {
                 const int64_t m = static_cast<int64_t>(tm) * BM + a_row;
                 row_valid = m < p.M;
@@ -449,11 +456,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     const int oh = pix / p.conv.OW, ow = pix - oh * p.conv.OW;
                     f_ih0[j] = oh * p.conv.sh - p.conv.ph;
                     f_iw0[j] = ow * p.conv.sw - p.conv.pw;
-                    f_img[j] = img * p.conv.H * p.conv.W;
+                    f_base[j] = (img * p.conv.H * p.conv.W + static_cast<int64_t>(f_ih0[j]) * p.conv.W + f_iw0[j]) * p.conv.C +
+                                (r & 7) * 8;
                 }
             }
             for (int kb = 0; kb < p.num_kb; ++kb) {
-                if (!DENSE && (kb & 1) == 0) {
+                if (!TMA_B && (kb & 1) == 0) {
                     // Words of this and the next k-block: shared memory -> registers, then free the slot.
                     if (!ptx::mbar_wait(bar_full_w + 8 * wstage, wphase, p.err_word, kErrWaitFullB)) {
                         ok = false;
@@ -495,7 +503,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     break;
                 }
                 uint8_t* stage_ptr = base_ptr + stage * C::STAGE_BYTES;
-                if (!DENSE && r < BN) {
+                if (!TMA_B && r < BN) {
                     uint8_t* row = stage_ptr + r * 128;
                     const uint32_t nw[2] = {(kb & 1) ? wn.z : wn.x, (kb & 1) ? wn.w : wn.y};
                     const uint32_t pw[2] = {(kb & 1) ? wp.z : wp.x, (kb & 1) ? wp.w : wp.y};
@@ -510,11 +518,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 if (FAST) {
                     // One filter tap and 64 channels per k-block: this thread copies its 16-byte chunk (8 channels)
                     // of four pixels per term, or zeros where the tap falls outside the image.
-                    const int tap = kb / p.conv.cblocks;
-                    const int c0 = (kb - tap * p.conv.cblocks) * BK + (r & 7) * 8;
-                    const int ti = tap / p.conv.kw, tj = tap - ti * p.conv.kw;
-                    const int dy = ti * p.conv.dh, dx = tj * p.conv.dw;
-                    const bool tap_valid = tap < p.conv.taps;
+                    // (tap, channel block) advance with kb: no divisions in the loop.
+                    const int dy = f_ti * p.conv.dh, dx = f_tj * p.conv.dw;
+                    const bool tap_valid = f_ti * p.conv.kw + f_tj < p.conv.taps;
+                    const int64_t tap_off = (static_cast<int64_t>(dy) * p.conv.W + dx) * p.conv.C + f_cb * BK;
+                    if (++f_cb == p.conv.cblocks) {
+                        f_cb = 0;
+                        if (++f_tj == p.conv.kw) {
+                            f_tj = 0;
+                            ++f_ti;
+                        }
+                    }
                     const uint32_t a_base = base + stage * C::STAGE_BYTES + C::B_BYTES;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -523,9 +537,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         const bool inside = f_valid[j] && tap_valid &&
                                             static_cast<unsigned>(ih) < static_cast<unsigned>(p.conv.H) &&
                                             static_cast<unsigned>(iw) < static_cast<unsigned>(p.conv.W);
-                        const __nv_bfloat16* src =
-                            inside ? p.conv.xs + (f_img[j] + static_cast<int64_t>(ih) * p.conv.W + iw) * p.conv.C + c0
-                                   : p.conv.xs;
+                        const __nv_bfloat16* src = inside ? p.conv.xs + (f_base[j] + tap_off) : p.conv.xs;
                         const uint32_t dst = a_base + row * 128 + (((r & 7) ^ (row & 7)) << 4);
 #pragma unroll
                         for (int q = 0; q < NPASS; ++q)
@@ -806,10 +818,10 @@ inline void set_segments(tc::Params& p, int npass) {
     p.kb_per_seg = (p.num_kb + p.num_seg - 1) / p.num_seg;
 }
 
-template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE = false>
+template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC = 0>
 int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
-    using C = tc::Cfg<BN, NPASS, TERNARY, DENSE, tc::is_conv_mode(AMODE)>;
-    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>;
+    using C = tc::Cfg<BN, NPASS, TERNARY, BSRC, tc::is_conv_mode(AMODE)>;
+    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>;
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
@@ -819,12 +831,12 @@ int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) 
     return launched(tc::is_conv_mode(AMODE) ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
 }
 
-template <int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, bool DENSE = false>
+template <int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC = 0>
 int32_t dispatch_bn(int bn, const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
     switch (bn) {
-        case 256: return launch_tc<256, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>(maps, p, st);
-        case 128: return launch_tc<128, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>(maps, p, st);
-        default: return launch_tc<64, NPASS, TERNARY, AMODE, TERN_ACT, DENSE>(maps, p, st);
+        case 256: return launch_tc<256, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>(maps, p, st);
+        case 128: return launch_tc<128, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>(maps, p, st);
+        default: return launch_tc<64, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>(maps, p, st);
     }
 }
 

@@ -163,7 +163,7 @@ class Session:
         out_name = n["outputs"][0]
         order = w.get("order", capi.CONV_WEIGHTS_REFERENCE)
         ws = self._workspace("conv", L.h.tbn_conv2d_workspace_bytes(x.shape[0], x.shape[1], x.shape[2], x.shape[3],
-                                                                    w["shape"][2], w["shape"][3], order))
+                                                                    w["shape"][0], w["shape"][2], w["shape"][3], order))
         if self.quantization and "words" in w:
             y = L.conv2d_tbn(x, w["words"], w["shape"], p, alpha=w["alpha_tbn"], bias=bias,
                              epilogue=capi.EPI_BIAS_BEFORE_ALPHA, workspace=ws, order=order)

@@ -330,7 +330,7 @@ Tensor conv2d_float_packed(const Tensor& x, const PackedWeights& w, const Tensor
     Tensor y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
     if (residual) TBN_CHECK(residual->shape() == y.shape(), InvalidShapeError, "residual must have the output's shape");
     const int32_t order = w.tap_major ? TBN_CONV_WEIGHTS_TAP_MAJOR : TBN_CONV_WEIGHTS_REFERENCE;
-    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.kh, d.kw, order);
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.M, d.kh, d.kw, order);
     uint32_t epi = (relu_flag ? TBN_EPI_RELU : 0u) | (residual ? TBN_EPI_ADD_RESIDUAL : 0u);
     check(tbn_conv2d_fxb(dptr(x), d.N, d.C, d.H, d.W, static_cast<const uint32_t*>(w.neg.device_data()),
                          w.ternary ? static_cast<const uint32_t*>(w.pos.device_data()) : nullptr, d.M, d.kh, d.kw,
@@ -348,7 +348,7 @@ Tensor conv2d_tbn_packed(const Tensor& x, const PackedWeights& w, const Tensor* 
     check_bias(bias, d.M);
     Tensor y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
     const int32_t order = w.tap_major ? TBN_CONV_WEIGHTS_TAP_MAJOR : TBN_CONV_WEIGHTS_REFERENCE;
-    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.kh, d.kw, order);
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.M, d.kh, d.kw, order);
     check(tbn_conv2d_tbn(dptr(x), d.N, d.C, d.H, d.W, -0.1f, 0.1f, static_cast<const uint32_t*>(w.neg.device_data()), d.M, d.kh,
                          d.kw, static_cast<int32_t>(p.stride_h), static_cast<int32_t>(p.stride_w), static_cast<int32_t>(p.pad_h),
                          static_cast<int32_t>(p.pad_w), static_cast<int32_t>(p.dilation_h), static_cast<int32_t>(p.dilation_w),
@@ -401,7 +401,7 @@ Tensor conv2d_float_dense(const Tensor& x, const DenseWeights& w, const Tensor* 
     Tensor y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
     if (residual) TBN_CHECK(residual->shape() == y.shape(), InvalidShapeError, "residual must have the output's shape");
     const int32_t order = w.tap_major ? TBN_CONV_WEIGHTS_TAP_MAJOR : TBN_CONV_WEIGHTS_REFERENCE;
-    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.kh, d.kw, order);
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.M, d.kh, d.kw, order);
     const uint32_t epi = (relu_flag ? TBN_EPI_RELU : 0u) | (residual ? TBN_EPI_ADD_RESIDUAL : 0u);
     check(tbn_conv2d_f32(dptr(x), d.N, d.C, d.H, d.W, w.split.device_data(), d.M, d.kh, d.kw, static_cast<int32_t>(p.stride_h),
                          static_cast<int32_t>(p.stride_w), static_cast<int32_t>(p.pad_h), static_cast<int32_t>(p.pad_w),

@@ -253,8 +253,9 @@ int32_t tbn_gemm_f32(const float* d_a, int64_t M, int64_t K, int64_t lda, const 
 /* [M, C, taps] fp32 -> [M, taps, C] fp32 (taps = kh*kw). */
 int32_t tbn_permute_filters(const float* d_w, int64_t M, int64_t C, int64_t taps, float* d_out, void* stream);
 
-/* Bytes of scratch the convolution entry points need (tap table or channels-last copy + partial-sum tiles). */
-size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t kh, int64_t kw,
+/* Bytes of scratch the convolution entry points need (tap table or channels-last copy, partial-sum tiles,
+ * and the bf16 expansion of the packed filters: ceil128(C*kh*kw) * ceil8(M_out) * 2 bytes). */
+size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t M_out, int64_t kh, int64_t kw,
                                   int32_t weight_order);
 
 /* Float x binary / float x ternary Conv2D, NCHW fp32 in and out:
