@@ -236,6 +236,45 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.conv.pw = a.pw;
     p.conv.act_lo = lo;
     p.conv.act_hi = hi;
+    // Patch mode: when the channels-last copy exists and the geometry fits a TMA box, an m-tile is a rectangle of
+    // output pixels (whole output rows first, then several rows, then several images) of at most 128 pixels, and
+    // the activation operand of one tap and 64 channels is one tiled TMA load.
+    if (fast) {
+        const int64_t pbw = std::min<int64_t>(OW, tc::BM);
+        const int64_t pbh = std::min<int64_t>(OH, tc::BM / pbw);
+        const int64_t pbi = (pbw == OW && pbh == OH) ? std::max<int64_t>(1, std::min<int64_t>(tc::BM / (pbw * pbh), a.N)) : 1;
+        const bool patch_ok = pbw * a.sw <= 256 && pbh * a.sh <= 256 && a.sw <= 8 && a.sh <= 8 && pbi <= 256 &&
+                              a.N * a.H * a.W * a.C * 2 < (1LL << 40);
+        if (patch_ok) {
+            const cuuint64_t gdim[5] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W), static_cast<cuuint64_t>(a.H),
+                                        static_cast<cuuint64_t>(a.N), static_cast<cuuint64_t>(npass)};
+            const cuuint64_t gstride[4] = {static_cast<cuuint64_t>(a.C) * 2, static_cast<cuuint64_t>(a.W * a.C) * 2,
+                                           static_cast<cuuint64_t>(a.H * a.W * a.C) * 2, static_cast<cuuint64_t>(term_stride) * 2};
+            const cuuint32_t box[5] = {tc::BK, static_cast<cuuint32_t>(pbw * a.sw), static_cast<cuuint32_t>(pbh * a.sh),
+                                       static_cast<cuuint32_t>(pbi), 1};
+            const cuuint32_t estr[5] = {1, static_cast<cuuint32_t>(a.sw), static_cast<cuuint32_t>(a.sh), 1, 1};
+            const CUresult cr = encode(&maps.a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, xs, gdim, gstride, box, estr,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
+                        "cuTensorMapEncodeTiled (activation patches) failed with CUresult " + std::to_string(static_cast<int>(cr)));
+            p.conv.pbw = static_cast<int>(pbw);
+            p.conv.pbh = static_cast<int>(pbh);
+            p.conv.pbi = static_cast<int>(pbi);
+            p.conv.patches_w = static_cast<int>((OW + pbw - 1) / pbw);
+            p.conv.patches_h = static_cast<int>((OH + pbh - 1) / pbh);
+            p.conv.a_box_bytes = static_cast<int>(npass * pbw * pbh * pbi * 128);
+            const int64_t tiles_m = static_cast<int64_t>(p.conv.patches_w) * p.conv.patches_h * ((a.N + pbi - 1) / pbi);
+            TBN_REQUIRE(tiles_m * p.tiles_n < (1LL << 31), TBN_INVALID_SHAPE, "conv2d: too many tiles");
+            p.tiles_m = static_cast<int>(tiles_m);
+            if (a.dense_w) {
+                set_segments(p, 3);
+                return dispatch_bn<2, false, 4, false, 1>(bn, maps, p, a.st);
+            }
+            if (tern_act || npass == 1) return dispatch_bn<1, false, 4, false, 2>(bn, maps, p, a.st);
+            return dispatch_bn<2, false, 4, false, 2>(bn, maps, p, a.st);
+        }
+    }
     // Weight source: 1 = two-term float filters, 2 = expanded sign filters (binary and ternary alike).
     if (fast) {
         if (a.dense_w) {

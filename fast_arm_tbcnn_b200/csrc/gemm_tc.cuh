@@ -108,7 +108,7 @@ constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 constexpr int kMaxAccumSteps = 4096;
 
 // Operand modes that lower a convolution (see AMODE at the kernel).
-__host__ __device__ constexpr bool is_conv_mode(int amode) { return amode == 1 || amode == 2; }
+__host__ __device__ constexpr bool is_conv_mode(int amode) { return amode == 1 || amode == 2 || amode == 4; }
 
 template <int BN, int NPASS, bool TERNARY, int BSRC = 0, bool CONV = false>
 struct Cfg {
@@ -146,6 +146,10 @@ struct ConvGeom {
     const __nv_bfloat16* xs;
     int64_t xs_term_stride;  // elements between the bf16 terms
     int kw, taps, dh, dw, cblocks;
+    // Patch mode (AMODE 4): an m-tile is a box of pbi images x pbh output rows x pbw output columns
+    // (pbi*pbh*pbw <= 128 GEMM rows, row = (bi*pbh + bh)*pbw + bw); patches_w x patches_h boxes cover one image
+    // group.  a_box_bytes: bytes one TMA box delivers (all terms together).
+    int pbw, pbh, pbi, patches_w, patches_h, a_box_bytes;
 };
 
 struct Params {
@@ -189,7 +193,11 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 // AMODE: source of the activation operand.  0 = TMA from pre-split [terms][M][K] (plain GEMM);
 // 1 = element-wise gather from NCHW fp32 (any convolution geometry); 2 = cp.async from the channels-last
 // bf16 copy (convolutions with C % 64 == 0); 3 = the fp32 rows of A read by the build warps and split in
-// registers (plain GEMM without the separate split pass; loads run two k-blocks ahead of their use).
+// registers (plain GEMM without the separate split pass; loads run two k-blocks ahead of their use);
+// 4 = convolution whose m-tiles are rectangular patches of output pixels, so that the activation operand of one
+// filter tap and 64 channels is ONE tiled TMA box of the channels-last copy [term][img][h][w][c] (the hardware
+// zero-fills the halo, the tensor map's element strides implement the convolution stride): no thread touches
+// the operands.
 template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_neg,
@@ -198,7 +206,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     constexpr bool CONV = is_conv_mode(AMODE);
     constexpr bool FAST = AMODE == 2;
     constexpr bool ROWS = AMODE == 3;
-    constexpr bool BUILT_A = CONV || ROWS;  // the build warps write the activation operand
+    constexpr bool PATCH = AMODE == 4;
+    constexpr bool BUILT_A = AMODE == 1 || AMODE == 2 || ROWS;  // the build warps write the activation operand
+    static_assert(!PATCH || BSRC != 0, "patch-mode convolutions take both operands by TMA");
     constexpr bool DENSE = BSRC == 1;      // two-term float weights
     constexpr bool TMA_B = BSRC != 0;      // the weight tile arrives by TMA instead of being unpacked here
     static_assert(!(ROWS && TMA_B), "TMA-fed weights take their activations by TMA or by the convolution gathers");
@@ -271,6 +281,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int tm, tn;
                 tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+                // Patch mode: input coordinates of the patch's first pixel under tap (0, 0), and the tap state.
+                int pw0 = 0, ph0 = 0, pimg0 = 0, p_cb = 0, p_ti = 0, p_tj = 0;
+                if (PATCH) {
+                    const int px = tm % p.conv.patches_w;
+                    const int py = (tm / p.conv.patches_w) % p.conv.patches_h;
+                    pimg0 = (tm / (p.conv.patches_w * p.conv.patches_h)) * p.conv.pbi;
+                    pw0 = px * p.conv.pbw * p.conv.sw - p.conv.pw;
+                    ph0 = py * p.conv.pbh * p.conv.sh - p.conv.ph;
+                }
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!TMA_B && (kb & 1) == 0) {
                         // Packed words of k-blocks kb and kb+1 for the BN columns of this tile
@@ -295,7 +314,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             break;
                         }
                         const uint32_t bar = bar_full_a + 8 * stage;
-                        ptx::mbar_arrive_expect_tx(bar, (BUILT_A ? 0 : NPASS * A_TILE_BYTES) + (TMA_B ? C::B_BYTES : 0));
+                        ptx::mbar_arrive_expect_tx(bar, (BUILT_A ? 0 : (PATCH ? p.conv.a_box_bytes : NPASS * A_TILE_BYTES)) +
+                                                            (TMA_B ? C::B_BYTES : 0));
                         const uint32_t b_dst = base + stage * C::STAGE_BYTES;
                         const uint32_t a_dst = b_dst + C::B_BYTES;
                         if (TMA_B) {
@@ -303,7 +323,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             for (int q = 0; q < C::B_TERMS; ++q)
                                 ptx::tma_load_3d(b_dst + q * C::B_TILE_BYTES, &tmap_neg, kb * BK, tn * BN, q, bar);
                         }
-                        if (!BUILT_A) {
+                        if (PATCH) {
+                            // One box per term: channels [64*cb, +64) of the input pixels under filter tap (ti, tj)
+                            // for the whole patch; coordinates outside the image read zeros.
+                            const int x = pw0 + p_tj * p.conv.dw, y = ph0 + p_ti * p.conv.dh;
+                            const bool tap_valid = p_ti * p.conv.kw + p_tj < p.conv.taps;
+#pragma unroll
+                            for (int q = 0; q < NPASS; ++q)
+                                ptx::tma_load_5d(a_dst + q * A_TILE_BYTES, &tmap_a, p_cb * BK, tap_valid ? x : -(1 << 20), y, pimg0, q, bar);
+                            if (++p_cb == p.conv.cblocks) {
+                                p_cb = 0;
+                                if (++p_tj == p.conv.kw) {
+                                    p_tj = 0;
+                                    ++p_ti;
+                                }
+                            }
+                        } else if (!BUILT_A) {
 #pragma unroll
                             for (int q = 0; q < NPASS; ++q)
                                 ptx::tma_load_3d(a_dst + q * A_TILE_BYTES, &tmap_a, kb * BK, tm * BM, q, bar);
@@ -648,9 +683,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             }
             ptx::named_barrier_sync(1, kEpilogueThreads);
             const int64_t m = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
+            bool row_ok = m < p.M;
             // Output element (m, n) lives at out_base + n * out_cs.
             int64_t out_base, out_cs;
-            if (p.out_nchw) {
+            if (PATCH) {
+                // Row of the tile -> (image, output row, output column) inside this tile's patch.
+                const int row = quarter * 32 + lane;
+                const int bw = row % p.conv.pbw, bh = (row / p.conv.pbw) % p.conv.pbh, bi = row / (p.conv.pbw * p.conv.pbh);
+                const int px = tm % p.conv.patches_w, py = (tm / p.conv.patches_w) % p.conv.patches_h;
+                const int64_t img = static_cast<int64_t>(tm / (p.conv.patches_w * p.conv.patches_h)) * p.conv.pbi + bi;
+                const int oh = py * p.conv.pbh + bh, ow = px * p.conv.pbw + bw;
+                row_ok = bi < p.conv.pbi && oh < p.conv.OH && ow < p.conv.OW && img * p.out_hw < p.M;
+                out_base = img * p.N * p.out_hw + static_cast<int64_t>(oh) * p.conv.OW + ow;
+                out_cs = p.out_hw;
+            } else if (p.out_nchw) {
                 const int64_t img = m / p.out_hw;
                 out_base = img * p.N * p.out_hw + (m - img * p.out_hw);
                 out_cs = p.out_hw;
@@ -728,7 +774,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             }
                         }
                         __syncwarp();
-                    } else if (m < p.M) {
+                    } else if (row_ok) {
                         const int64_t nc = n0 + c * 32;
                         const float* as = alpha_s + sbuf * BN + c * 32;
                         const float* bs = bias_s + sbuf * BN + c * 32;

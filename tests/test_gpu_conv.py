@@ -86,6 +86,12 @@ FAST_CASES = [
     (2, 64, 12, 10, 70, 3, 2, (1, 1, 2, 1, 2, 1)),
     (2, 512, 4, 4, 300, 3, 3, (1, 1, 1, 1, 1, 1)),
     (70, 64, 7, 7, 64, 3, 3, (1, 1, 1, 1, 1, 1)),
+    (5, 64, 7, 7, 64, 3, 3, (1, 1, 1, 1, 1, 1)),        # several whole images per tile, last tile partly empty
+    (2, 64, 56, 56, 64, 3, 3, (1, 1, 1, 1, 1, 1)),      # two output rows per tile
+    (1, 64, 150, 9, 16, 3, 3, (1, 1, 1, 1, 1, 1)),      # rows shorter than a tile, several rows per tile
+    (1, 64, 5, 300, 16, 1, 3, (1, 2, 0, 1, 1, 1)),      # output rows longer than one tile
+    (2, 128, 28, 28, 64, 1, 1, (2, 2, 0, 0, 1, 1)),     # strided 1x1 (the shortcut convolutions)
+    (2, 64, 40, 40, 8, 3, 3, (9, 9, 1, 1, 1, 1)),       # stride beyond the TMA element-stride range: cp.async path
 ]
 
 
