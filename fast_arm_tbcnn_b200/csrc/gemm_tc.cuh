@@ -219,6 +219,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     // Which operands arrive by TMA (signalled on full_a) and which are built by the build warps (full_b).
     constexpr bool kTmaOperands = !BUILT_A || TMA_B;
     constexpr bool kBuiltOperands = BUILT_A || !TMA_B;
+    // When no operand is built by threads, the eight build warps join the epilogue: three warps per TMEM lane
+    // quarter, each taking every third 32-column chunk.
+    constexpr bool kWideEpilogue = !kBuiltOperands;
+    constexpr int kEpiGroups = kWideEpilogue ? 3 : 1;
+    constexpr int kEpiThreads = kEpilogueThreads * kEpiGroups;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -252,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(bar_tmem_full + 8 * b, 1);
-            ptx::mbar_init(bar_tmem_empty + 8 * b, kEpilogueThreads);
+            ptx::mbar_init(bar_tmem_empty + 8 * b, kEpiThreads);
         }
         for (int w = 0; w < kWordStages; ++w) {
             ptx::mbar_init(bar_full_w + 8 * w, 1);
@@ -407,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 }
             }
         }
-    } else if (warp < 2 + kBuildThreads / 32) {
+    } else if (!kWideEpilogue && warp < 2 + kBuildThreads / 32) {
         // ------------------------------------------------------------ operand build
         static_assert(BN <= kBuildThreads, "one build thread per weight column of the tile");
         const int r = threadIdx.x - 64;  // weight column (row of the K-major weight tile) of this thread
@@ -665,9 +670,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        const int e = threadIdx.x - (64 + kBuildThreads);
+        const int e = kWideEpilogue ? threadIdx.x - 64 : threadIdx.x - (64 + kBuildThreads);  // index among the epilogue threads
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
-        float4* scratch = p.scratch + static_cast<int64_t>(blockIdx.x) * (BN / 4) * kEpilogueThreads + e;
+        const int group = kWideEpilogue ? (warp - 2) >> 2 : 0;  // which of the warps sharing this quarter
+        // Partial-sum slot of this thread's tile row (the warps of one quarter own the same rows, different chunks).
+        float4* scratch = p.scratch + static_cast<int64_t>(blockIdx.x) * (BN / 4) * kEpilogueThreads + quarter * 32 + lane;
         int iter = 0;
         int tile_iter = 0;
         bool ok = true;
@@ -676,12 +683,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
             const int sbuf = tile_iter & 1;
             const int64_t n0 = static_cast<int64_t>(tn) * BN;
-            for (int j = e; j < BN; j += kEpilogueThreads) {
+            for (int j = e; j < BN; j += kEpiThreads) {
                 const int64_t n = n0 + j;
                 alpha_s[sbuf * BN + j] = (p.ep.alpha && n < p.N) ? __ldg(p.ep.alpha + n) : 1.0f;
                 bias_s[sbuf * BN + j] = (p.ep.bias && n < p.N) ? __ldg(p.ep.bias + n) : 0.0f;
             }
-            ptx::named_barrier_sync(1, kEpilogueThreads);
+            ptx::named_barrier_sync(1, kEpiThreads);
             const int64_t m = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
             bool row_ok = m < p.M;
             // Output element (m, n) lives at out_base + n * out_cs.
@@ -716,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 ptx::tc_fence_after_sync();
                 const bool first = seg == 0, last = seg == p.num_seg - 1;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = group; c < BN / 32; c += kEpiGroups) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                            static_cast<uint32_t>(buf * BN + c * 32), r);
@@ -793,11 +800,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             // Ragged edge, residual add or NCHW: element stores.  In NCHW consecutive lanes
                             // hold consecutive pixels of one channel, so each store is coalesced.
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (nc + j < p.N) {
-                                    const int64_t idx = out_base + (nc + j) * out_cs;
-                                    const float rv = add_res ? __ldg(res + idx) : 0.0f;
-                                    p.c[idx] = apply_epilogue(v[j], as[j], bs[j], p.ep.scale, p.ep.flags, rv);
+                            for (int j4 = 0; j4 < 8; ++j4) {
+                                const float4 a4 = *reinterpret_cast<const float4*>(as + 4 * j4);
+                                const float4 b4 = *reinterpret_cast<const float4*>(bs + 4 * j4);
+                                const float aj[4] = {a4.x, a4.y, a4.z, a4.w}, bj[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int j = 4 * j4 + i;
+                                    if (nc + j < p.N) {
+                                        const int64_t idx = out_base + (nc + j) * out_cs;
+                                        const float rv = add_res ? __ldg(res + idx) : 0.0f;
+                                        p.c[idx] = apply_epilogue(v[j], aj[i], bj[i], p.ep.scale, p.ep.flags, rv);
+                                    }
                                 }
                             }
                         }
