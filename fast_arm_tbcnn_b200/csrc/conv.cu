@@ -28,38 +28,38 @@ __global__ void conv_tap_table_kernel(int2* __restrict__ table, int K, int K_pad
 }
 
 // NCHW fp32 -> channels-last bf16 terms xs[q][n][h][w][c] (or the ternarised activation as one exact term).
-// One block transposes a 64-channel x 32-pixel tile of one image row through shared memory: reads are
-// coalesced along w, writes along c (128 bytes per pixel).  HBM bound: 4 B read + 2 NPASS B written per element.
+// One block transposes a 64-channel x 32-pixel tile of one image through shared memory; pixels are taken along the
+// flattened h*W + w index, so that reads are 128 contiguous bytes per channel whatever the image width, and writes
+// are 128 bytes per pixel.  HBM bound: 4 B read + 2 NPASS B written per element.
 template <int NPASS, bool TERNARISE>
-__global__ void __launch_bounds__(256) nhwc_split_kernel(const float* __restrict__ x, int C, int H, int W,
+__global__ void __launch_bounds__(256) nhwc_split_kernel(const float* __restrict__ x, int C, int HW, int tiles_per_image,
                                                          __nv_bfloat16* __restrict__ xs, int64_t term_stride, float lo,
                                                          float hi) {
     __shared__ float tile[64][33];
-    const int w0 = blockIdx.z * 32, c0 = blockIdx.y * 64;
-    const int64_t nh = blockIdx.x;  // n * H + h (grid.x: the only dimension that may exceed 65535)
-    const int64_t n = nh / H;
-    const int h = static_cast<int>(nh - n * H);
+    const int64_t n = blockIdx.x / tiles_per_image;  // grid.x: the only dimension that may exceed 65535
+    const int p0 = static_cast<int>(blockIdx.x - n * tiles_per_image) * 32;
+    const int c0 = blockIdx.y * 64;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int c = ty + 8 * i, w = w0 + tx;
-        tile[c][tx] = (w < W) ? __ldg(x + ((n * C + c0 + c) * H + h) * static_cast<int64_t>(W) + w) : 0.0f;
+        const int c = ty + 8 * i;
+        tile[c][tx] = (p0 + tx < HW) ? __ldg(x + (n * C + c0 + c) * HW + p0 + tx) : 0.0f;
     }
     __syncthreads();
-    const int chunk = threadIdx.x & 7, pw = threadIdx.x >> 3;  // 8 channels of pixel (w0 + pw)
-    if (w0 + pw >= W) return;
+    const int chunk = threadIdx.x & 7, pp = threadIdx.x >> 3;  // 8 channels of pixel (p0 + pp)
+    if (p0 + pp >= HW) return;
     uint32_t packed[NPASS][4];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         uint16_t term[NPASS];
-        split_terms<NPASS, TERNARISE>(tile[chunk * 8 + e][pw], lo, hi, term);
+        split_terms<NPASS, TERNARISE>(tile[chunk * 8 + e][pp], lo, hi, term);
 #pragma unroll
         for (int q = 0; q < NPASS; ++q) {
             if (e & 1) packed[q][e >> 1] |= static_cast<uint32_t>(term[q]) << 16;
             else packed[q][e >> 1] = term[q];
         }
     }
-    const int64_t off = ((n * H + h) * static_cast<int64_t>(W) + w0 + pw) * C + c0 + chunk * 8;
+    const int64_t off = (n * HW + p0 + pp) * C + c0 + chunk * 8;
 #pragma unroll
     for (int q = 0; q < NPASS; ++q)
         *reinterpret_cast<uint4*>(xs + q * term_stride + off) = make_uint4(packed[q][0], packed[q][1], packed[q][2], packed[q][3]);
@@ -160,16 +160,20 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     const int64_t term_stride = a.N * a.H * a.W * a.C;
     int32_t rc;
     if (fast) {
-        TBN_REQUIRE(a.H * a.N < (1LL << 31) && a.W <= 65535LL * 32 && a.C / 64 <= 65535, TBN_INVALID_SHAPE,
+        const int64_t HW = a.H * a.W, tiles_per_image = (HW + 31) / 32;
+        TBN_REQUIRE(HW < (1LL << 31) && a.N * tiles_per_image < (1LL << 31) && a.C / 64 <= 65535, TBN_INVALID_SHAPE,
                     "conv2d: input too large for the pre-pass grid");
-        dim3 grid(static_cast<unsigned>(a.N * a.H), static_cast<unsigned>(a.C / 64), static_cast<unsigned>((a.W + 31) / 32));
+        dim3 grid(static_cast<unsigned>(a.N * tiles_per_image), static_cast<unsigned>(a.C / 64));
         profile_begin(kProfSplit, a.st);
-        if (tern_act) nhwc_split_kernel<1, true><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(a.H),
-                                                                        static_cast<int>(a.W), xs, term_stride, lo, hi);
-        else if (npass == 1) nhwc_split_kernel<1, false><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(a.H),
-                                                                               static_cast<int>(a.W), xs, term_stride, 0.f, 0.f);
-        else nhwc_split_kernel<2, false><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(a.H),
-                                                               static_cast<int>(a.W), xs, term_stride, 0.f, 0.f);
+        if (tern_act)
+            nhwc_split_kernel<1, true><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(HW),
+                                                               static_cast<int>(tiles_per_image), xs, term_stride, lo, hi);
+        else if (npass == 1)
+            nhwc_split_kernel<1, false><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(HW),
+                                                                static_cast<int>(tiles_per_image), xs, term_stride, 0.f, 0.f);
+        else
+            nhwc_split_kernel<2, false><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(HW),
+                                                                static_cast<int>(tiles_per_image), xs, term_stride, 0.f, 0.f);
         profile_end(kProfSplit, a.st);
         rc = launched("nhwc_split_kernel");
     } else {

@@ -798,7 +798,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             }
                         } else {
                             // Ragged edge, residual add or NCHW: element stores.  In NCHW consecutive lanes
-                            // hold consecutive pixels of one channel, so each store is coalesced.
+                            // hold consecutive pixels of one channel, so each store is coalesced.  The flags are
+                            // uniform: each is tested once per chunk, outside the unrolled element loops, and
+                            // the residual loads are all issued before the first one is used.
+                            float o[32];
+                            const bool bias_first = (p.ep.flags & TBN_EPI_BIAS_BEFORE_ALPHA) != 0;
 #pragma unroll
                             for (int j4 = 0; j4 < 8; ++j4) {
                                 const float4 a4 = *reinterpret_cast<const float4*>(as + 4 * j4);
@@ -807,12 +811,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     const int j = 4 * j4 + i;
-                                    if (nc + j < p.N) {
-                                        const int64_t idx = out_base + (nc + j) * out_cs;
-                                        const float rv = add_res ? __ldg(res + idx) : 0.0f;
-                                        p.c[idx] = apply_epilogue(v[j], aj[i], bj[i], p.ep.scale, p.ep.flags, rv);
-                                    }
+                                    o[j] = bias_first ? __fmul_rn(__fadd_rn(__fmul_rn(v[j], p.ep.scale), bj[i]), aj[i])
+                                                      : __fadd_rn(__fmul_rn(__fmul_rn(v[j], aj[i]), p.ep.scale), bj[i]);
                                 }
+                            }
+                            const int ncols = static_cast<int>(min(static_cast<int64_t>(32), p.N - nc));
+                            const int64_t first = out_base + nc * out_cs;
+                            if (add_res) {
+                                const float* rp = res + first;
+                                float rv[32];
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) rv[j] = j < ncols ? __ldg(rp + j * out_cs) : 0.0f;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) o[j] = __fadd_rn(o[j], rv[j]);
+                            }
+                            if (p.ep.flags & TBN_EPI_RELU) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) o[j] = fmaxf(o[j], 0.0f);
+                            }
+                            float* dst = p.c + first;
+                            if (ncols == 32) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) dst[j * out_cs] = o[j];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (j < ncols) dst[j * out_cs] = o[j];
                             }
                         }
                     }
