@@ -208,7 +208,7 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     tc::Params p = {};
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
-    p.num_kb = static_cast<int>(K_pad / tc::BK);
+    p.num_kb = static_cast<int>((K + tc::BK - 1) / tc::BK);  // k-blocks that hold real k; the operands are zero beyond K
     p.tiles_m = static_cast<int>(M_pad / tc::BM);
     p.tiles_n = static_cast<int>((N + bn - 1) / bn);
     p.c = a.y;

@@ -269,7 +269,7 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     tc::Params p = {};
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
-    p.num_kb = static_cast<int>(K_pad / tc::BK);
+    p.num_kb = static_cast<int>((K + tc::BK - 1) / tc::BK);  // k-blocks that hold real k; the operands are zero beyond K
     p.tiles_m = static_cast<int>(M_pad / tc::BM);
     p.tiles_n = static_cast<int>((N + bn - 1) / bn);
     p.c = d_c;
@@ -287,7 +287,6 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     if (fused_split)
         return d_pos ? dispatch_bn<2, true, 3, false>(bn, maps, p, st) : dispatch_bn<2, false, 3, false>(bn, maps, p, st);
     if (dense_w) {
-        p.num_kb = static_cast<int>(K_pad / tc::BK);
         set_segments(p, 3);  // three MMA passes per k-block
         return dispatch_bn<2, false, 0, false, 1>(bn, maps, p, st);
     }
