@@ -377,12 +377,25 @@ def run_ours(args):
             gathered = torch.empty((world, n, nc), dtype=torch.float32, device=dev)
             C_full = torch.empty((n, n), dtype=torch.float32, device=dev)
 
+    span_events = None  # N > 1: [after GEMM, after barrier] per timed step, to report what the barrier costs
+
     def step():
         if world == 1:
             L.gemm_fxb(A_d, words, nc, alpha=alpha, mode=mode, out=C_slab, workspace=ws)
         elif fused:
             L.gemm_fxb_multi(A_d, words, nc, dests, n, alpha=alpha, mode=mode, workspace=ws)
-            dist.all_reduce(flag)
+            if span_events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                span_events.append(ev)
+            if args.barrier == "symm":
+                hdl.barrier(channel=0)
+            else:
+                dist.all_reduce(flag)
+            if span_events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                span_events.append(ev)
         else:
             L.gemm_fxb(A_d, words, nc, alpha=alpha, mode=mode, out=C_slab, workspace=ws)
             dist.all_gather_into_tensor(gathered.view(world * n, nc), C_slab)
@@ -398,7 +411,6 @@ def run_ours(args):
     L.sync()
     L.profile_enable(True)
     L.profile_read()
-    barrier()
     props = torch.cuda.get_device_properties(dev)
     try:
         pci = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
@@ -406,13 +418,29 @@ def run_ours(args):
         pci = None
     sampler = ClockSampler(local, pci)
     if rank == 0:
-        sampler.start()
+        sampler.start()   # before the barrier: its start-up (NVML initialisation) must not delay rank 0 into the timed loop
+    barrier()
     launches0 = L.launch_count()
+    if world > 1 and fused:
+        span_events = []
     ev0.record()
     for _ in range(args.steps):
         step()
     ev1.record()
     torch.cuda.synchronize()
+    barrier_ms = None
+    if span_events:
+        pairs = list(zip(span_events[0::2], span_events[1::2]))
+        mine = [sum(a.elapsed_time(b) for a, b in pairs) / len(pairs)]
+        # barrier end of step i -> GEMM end of step i+1: split + GEMM + whatever separates them on the stream
+        nxt = list(zip(span_events[1::2][:-1], span_events[2::2]))
+        mine.append(sum(a.elapsed_time(b) for a, b in nxt) / max(len(nxt), 1))
+        both = torch.tensor(mine, device=dev)
+        every = torch.empty(world * 2, device=dev)
+        dist.all_gather_into_tensor(every, both)
+        vals = [round(float(v), 4) for v in every.tolist()]
+        barrier_ms = {"barrier_ms_ranks": vals[0::2], "split_plus_gemm_span_ms_ranks": vals[1::2]}
+    span_events = None
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     launches = L.launch_count() - launches0
@@ -525,7 +553,8 @@ def run_ours(args):
                 "peak_source": f"{peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} "
                                f"{pipe_peak} TFLOP/s / {npass} passes",
                 "executed_tflops": achieved * npass, "frac_of_pipe_raw": achieved / pipe_peak,
-                "kernel_ms": gemm_ms, "kernel_ms_ranks": kernel_ms_ranks, "activation_split": (
+                "kernel_ms": gemm_ms, "kernel_ms_ranks": kernel_ms_ranks, "barrier_ms": barrier_ms, "barrier": (
+                    None if world == 1 else args.barrier), "activation_split": (
                     "separate kernel" if prof["split_launches"] else "inside the GEMM kernel (fp32 rows split in registers)"),
                 "split_kernel_ms": prof["split_ms"] / max(prof["split_launches"], 1),
                 "hbm_algorithmic_gbs": (4.0 * n * n + n * nc / 8.0 + 4.0 * n * nc) / (gemm_ms * 1e-3) / 1e9,
@@ -564,6 +593,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cnn", action="store_true", help="skip the binary-CNN images/s block")
     ap.add_argument("--only-cnn", action="store_true", help="run only the binary-CNN images/s block")
+    ap.add_argument("--barrier", choices=["nccl", "symm"], default="nccl",
+                    help="N > 1, fused path: step-closing barrier = tiny NCCL all-reduce or the symmetric-memory signal barrier")
     ap.add_argument("--no-fused-gather", action="store_true", help="N > 1: use NCCL all-gather instead of peer stores")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -777,7 +777,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             if (mm < p.M && col + 4 <= p.N) {
                                 const int64_t idx = mm * p.ldc + col;
 #pragma unroll 1
-                                for (int d = 0; d < p.num_out; ++d) *reinterpret_cast<float4*>(p.out_list[d] + idx) = o;
+                                // Write-through stores: lines bound for a peer GPU leave for NVLink at once instead of
+                                // collecting in this GPU's L2 until the flush at the end of the kernel.
+                                for (int d = 0; d < p.num_out; ++d) __stwt(reinterpret_cast<float4*>(p.out_list[d] + idx), o);
                             }
                         }
                         __syncwarp();
