@@ -280,7 +280,11 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     set_segments(p, npass);
     p.scratch = reinterpret_cast<float4*>(static_cast<uint8_t*>(d_ws) + split_bytes);
     p.num_out = num_out;
-    for (int i = 0; i < num_out; ++i) p.out_list[i] = outs[i];
+    for (int i = 0; i < num_out; ++i) {
+        p.out_list[i] = outs[i];
+        rc = make_out_map(encode, outs[i], M, N, ldc, &maps.out.m[i]);
+        if (rc) return rc;
+    }
     p.a_rows = d_a;
     p.lda = lda;
     p.K = static_cast<int>(K);

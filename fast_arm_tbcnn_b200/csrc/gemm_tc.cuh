@@ -152,6 +152,12 @@ struct ConvGeom {
     int pbw, pbh, pbi, patches_w, patches_h, a_box_bytes;
 };
 
+// Tensor maps of the destinations of the multi-destination epilogue: [N columns][M rows] fp32 with row stride
+// ldc, box 32 x 32, 128-byte swizzle.  Rows and columns past the matrix are clipped by the hardware.
+struct OutMaps {
+    CUtensorMap m[kMaxOutputs];
+};
+
 struct Params {
     int M, N;
     int num_kb;            // K_pad / 64
@@ -167,8 +173,10 @@ struct Params {
     int kb_per_seg;        // k-blocks per segment (the last one may be shorter)
     float4* scratch;       // [gridDim.x][BN/4][128] partial sums, used when num_seg > 1
     // Multi-destination epilogue (column-sharded multi-GPU GEMM): when num_out > 0 the finished tile is
-    // written, with full-line stores, to every out_list[i] (same row stride ldc) -- the local result
-    // buffer and the peers' buffers mapped into this GPU's address space -- instead of p.c.
+    // written to every destination (same row stride ldc) -- the local result buffer and the peers' buffers
+    // mapped into this GPU's address space -- instead of p.c: each epilogue warp stages its 32 x 32 block in
+    // shared memory and one lane issues a tiled TMA store per destination (OutMaps), so that the transfer over
+    // NVLink runs asynchronously beside the next block.  out_list keeps the raw pointers (argument checks).
     int num_out;
     float* out_list[kMaxOutputs];
     // AMODE 3: the fp32 activation rows themselves (16-byte aligned, lda % 4 == 0, K % 4 == 0).
@@ -202,7 +210,7 @@ template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_neg,
                                                               const __grid_constant__ CUtensorMap tmap_pos,
-                                                              const Params p) {
+                                                              const __grid_constant__ OutMaps out_maps, const Params p) {
     constexpr bool CONV = is_conv_mode(AMODE);
     constexpr bool FAST = AMODE == 2;
     constexpr bool ROWS = AMODE == 3;
@@ -754,6 +762,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         const float* bs = bias_s + sbuf * BN + c * 32;
                         float* tbuf = stage_out + (warp & 3) * (kStageOutBytes / 16);  // 32 x 32 floats per warp
                         const int64_t m_warp = static_cast<int64_t>(tm) * BM + quarter * 32;
+                        // The previous block's stores must have read the staging buffer before it is rewritten.
+                        if (lane == 0) ptx::bulk_wait_group_read<0>();
+                        __syncwarp();
                         // lane = row: write this row's 32 columns as 8 float4 at swizzled positions.
 #pragma unroll
                         for (int j4 = 0; j4 < 8; ++j4) {
@@ -765,24 +776,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags, 0.0f);
                             *reinterpret_cast<float4*>(tbuf + lane * 32 + ((j4 ^ (lane & 7)) << 2)) = o;
                         }
+                        // Shared memory written by these lanes -> readable by the TMA engine; then one lane sends the
+                        // block to every destination.
+                        ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        // 8 lanes per row (32 floats = 128 bytes), 4 rows per instruction.
-#pragma unroll
-                        for (int rr = 0; rr < 8; ++rr) {
-                            const int row = rr * 4 + (lane >> 3);
-                            const int q8 = lane & 7;
-                            const float4 o = *reinterpret_cast<const float4*>(tbuf + row * 32 + ((q8 ^ (row & 7)) << 2));
-                            const int64_t mm = m_warp + row;
-                            const int64_t col = nc + q8 * 4;
-                            if (mm < p.M && col + 4 <= p.N) {
-                                const int64_t idx = mm * p.ldc + col;
+                        if (lane == 0) {
+                            const uint32_t src = ptx::smem_u32(tbuf);
 #pragma unroll 1
-                                // Write-through stores: lines bound for a peer GPU leave for NVLink at once instead of
-                                // collecting in this GPU's L2 until the flush at the end of the kernel.
-                                for (int d = 0; d < p.num_out; ++d) __stwt(reinterpret_cast<float4*>(p.out_list[d] + idx), o);
-                            }
+                            for (int d = 0; d < p.num_out; ++d)
+                                ptx::tma_store_2d(&out_maps.m[d], src, static_cast<int>(nc), static_cast<int>(m_warp));
+                            ptx::bulk_commit_group();
                         }
-                        __syncwarp();
                     } else if (row_ok) {
                         const int64_t nc = n0 + c * 32;
                         const float* as = alpha_s + sbuf * BN + c * 32;
@@ -850,6 +854,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     }
 
     // ------------------------------------------------------------ teardown
+    ptx::bulk_wait_group<0>();  // stores issued by this thread (multi-destination epilogue) have completed
     __syncwarp();
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -880,7 +885,22 @@ inline size_t scratch_bytes() { return static_cast<size_t>(std::max(sm_count(), 
 
 struct TensorMaps {
     CUtensorMap a, neg, pos;
+    tc::OutMaps out = {};
 };
+
+// Destination map of the multi-destination epilogue (see tc::OutMaps).
+inline int32_t make_out_map(EncodeTiledFn encode, float* base, int64_t M, int64_t N, int64_t ldc, CUtensorMap* out) {
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ldc) * 4};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, gdim, gstride, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
+                "cuTensorMapEncodeTiled (destination) failed with CUresult " + std::to_string(static_cast<int>(cr)));
+    return TBN_SUCCESS;
+}
 
 // Packed-word plane [N_pad][KW] uint32 -> box of 4 words (128 k) x BN columns, no swizzle.
 inline int32_t make_word_map(EncodeTiledFn encode, const uint32_t* words, int64_t KW, int64_t N_pad, int bn,
@@ -912,7 +932,7 @@ int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) 
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
     profile_begin(kProfGemm, st);
-    kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, p);
+    kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, maps.out, p);
     profile_end(kProfGemm, st);
     return launched(tc::is_conv_mode(AMODE) ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
 }

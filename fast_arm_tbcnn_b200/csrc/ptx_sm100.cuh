@@ -145,6 +145,24 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// Tiled 2-D store shared -> global (local or peer memory); completion is tracked by the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src_smem, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(src_smem)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the shared-memory sources of all but the newest N groups have been read (the buffer may be reused).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until all but the newest N groups have completed.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Tiled 2-D load (no multicast).
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* m, int x, int y, uint32_t bar) {
     asm volatile(
