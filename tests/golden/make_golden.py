@@ -1,6 +1,6 @@
 """Generates the committed golden fixtures under tests/golden/.
 
-Run once in a container that has the reference tree (default /root/reference) and
+Run once in a container that has the reference tree (its location: environment variable TBN_REFERENCE) and
 the compiled reference (oracle/_ref/libtbn_ref.so, `make -C oracle ref`):
 
     python tests/golden/make_golden.py

@@ -13,7 +13,7 @@ from fast_arm_tbcnn_b200 import graphs, host_build
 
 import onnx_schema
 
-REFERENCE_TREE = "/root/reference"
+REFERENCE_TREE = os.environ.get("TBN_REFERENCE", "/root/reference")
 
 
 @pytest.fixture(scope="module")
