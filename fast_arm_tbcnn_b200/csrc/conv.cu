@@ -93,6 +93,69 @@ __global__ void expand_words_kernel(const uint32_t* __restrict__ neg, const uint
     }
 }
 
+// ---- stride-2 convolutions over very few channels (image stems) ------------------------------------------
+// A 2 x 2 space-to-depth of the input turns a stride-2 convolution over C <= 4 channels into a stride-1 one over
+// 4C <= 16 channels.  Stored channels-last with 16 bf16 per position, four neighbouring positions are 128
+// contiguous bytes: one 64-deep k-block = one row of the folded filter, and its operand for output column ow is
+// the window of positions ow .. ow+3.  A tensor map whose position stride (32 bytes) is smaller than its window
+// (128 bytes) hands those overlapping windows to the patch-mode kernel as ordinary boxes.
+//   T[term][n][Rs][Qs][(pr*2 + pc)*C + c] = x[n][c][2*Rs + pr][2*(Qs - left) + pc]   (0 outside the image / channels)
+template <int NPASS, bool TERNARISE>
+__global__ void s2d_split_kernel(const float* __restrict__ x, int64_t N, int C, int H, int W, int rows, int Qp, int left,
+                                 __nv_bfloat16* __restrict__ t, int64_t term_stride, float lo, float hi) {
+    const int64_t total = N * rows * Qp;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int qs = static_cast<int>(idx % Qp);
+        const int rs = static_cast<int>((idx / Qp) % rows);
+        const int64_t n = idx / (static_cast<int64_t>(Qp) * rows);
+        uint32_t packed[NPASS][8];
+#pragma unroll
+        for (int q = 0; q < NPASS; ++q)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) packed[q][e] = 0u;
+#pragma unroll
+        for (int sidx = 0; sidx < 16; ++sidx) {
+            float v = 0.0f;
+            if (sidx < 4 * C) {
+                const int pr = sidx / (2 * C), pc = (sidx / C) & 1, c = sidx % C;
+                const int h = 2 * rs + pr, w = 2 * (qs - left) + pc;
+                if (h < H && w >= 0 && w < W) v = __ldg(x + ((n * C + c) * H + h) * static_cast<int64_t>(W) + w);
+            }
+            uint16_t term[NPASS];
+            split_terms<NPASS, TERNARISE>(v, lo, hi, term);
+#pragma unroll
+            for (int q = 0; q < NPASS; ++q) packed[q][sidx >> 1] |= static_cast<uint32_t>(term[q]) << (16 * (sidx & 1));
+        }
+#pragma unroll
+        for (int q = 0; q < NPASS; ++q) {
+            uint4* dst = reinterpret_cast<uint4*>(t + q * term_stride + idx * 16);
+            dst[0] = make_uint4(packed[q][0], packed[q][1], packed[q][2], packed[q][3]);
+            dst[1] = make_uint4(packed[q][4], packed[q][5], packed[q][6], packed[q][7]);
+        }
+    }
+}
+
+// Filters [terms][N_pad][K_pad] bf16 in the reference order k = (c*kh + i)*kw + j  ->  folded order
+// k' = t*64 + q*16 + (pr*2 + pc)*C + c with i = 2t + pr - eh, j = 2q + pc - ew (zero where no such tap exists).
+__global__ void fold_filters_kernel(const __nv_bfloat16* __restrict__ src, int terms, int64_t N_pad, int64_t K_pad, int C,
+                                    int kh, int kw, int eh, int ew, int kh2, int64_t K2_pad,
+                                    __nv_bfloat16* __restrict__ dst) {
+    const int64_t total = static_cast<int64_t>(terms) * N_pad * K2_pad;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int64_t k2 = idx % K2_pad, row = idx / K2_pad;  // row = term * N_pad + n
+        const int t = static_cast<int>(k2 / 64), q = static_cast<int>((k2 % 64) / 16), sidx = static_cast<int>(k2 % 16);
+        __nv_bfloat16 v = __float2bfloat16_rn(0.0f);
+        if (t < kh2 && sidx < 4 * C) {
+            const int pr = sidx / (2 * C), pc = (sidx / C) & 1, c = sidx % C;
+            const int i = 2 * t + pr - eh, j = 2 * q + pc - ew;
+            if (i >= 0 && i < kh && j >= 0 && j < kw) v = src[row * K_pad + (static_cast<int64_t>(c) * kh + i) * kw + j];
+        }
+        dst[idx] = v;
+    }
+}
+
 struct ConvArgs {
     const void* dense_w = nullptr;  // split dense weights (float filters) instead of packed planes
     const float* x;
@@ -118,7 +181,34 @@ size_t table_bytes(int64_t K_pad) { return static_cast<size_t>(round_up(K_pad * 
 // Expanded (bf16) copy of the packed filters, after the partial-sum tiles in the workspace.
 size_t expanded_bytes(int64_t K_pad, int64_t N_pad) { return static_cast<size_t>(round_up(K_pad * N_pad * 2, 256)); }
 
-int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float hi) {
+// Geometry of the folded (space-to-depth) form of a stride-2 convolution; `ok` says whether it applies.
+struct FoldGeom {
+    bool ok = false;
+    int eh = 0, ew = 0, kh2 = 0, kw2 = 0, rows = 0, Qp = 0, left = 0, top = 0;
+    int64_t t_bytes = 0, K2_pad = 0;
+};
+
+FoldGeom fold_geometry(int64_t N, int64_t C, int64_t H, int64_t W, int64_t kh, int64_t kw, int sh, int sw, int ph, int pw,
+                       int dh, int dw, int64_t OW, int npass) {
+    FoldGeom g;
+    if (C < 1 || C > 4 || sh != 2 || sw != 2 || dh != 1 || dw != 1 || kh > 64 || kw > 8) return g;
+    const int Sh = (ph + 1) / 2 * 2, Sw = (pw + 1) / 2 * 2;  // even shifts >= the pads
+    g.eh = Sh - ph;
+    g.ew = Sw - pw;
+    g.kh2 = (g.eh + static_cast<int>(kh) - 1) / 2 + 1;
+    g.kw2 = (g.ew + static_cast<int>(kw) - 1) / 2 + 1;
+    if (g.kw2 > 4) return g;
+    g.top = Sh / 2;
+    g.left = Sw / 2;
+    g.rows = static_cast<int>((H + 1) / 2);
+    g.Qp = static_cast<int>(std::max<int64_t>(OW + 3, g.left + (W + 1) / 2));  // every window of 4 positions is in storage
+    g.t_bytes = round_up(static_cast<int64_t>(npass) * N * g.rows * g.Qp * 16 * 2, 256);
+    g.K2_pad = round_up(static_cast<int64_t>(g.kh2) * 64, 128);
+    g.ok = N * g.rows * g.Qp * 32 < (1LL << 40);
+    return g;
+}
+
+int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float hi, bool allow_fold = true) {
     TBN_REQUIRE(a.N > 0 && a.C > 0 && a.H > 0 && a.W > 0 && a.M_out > 0 && a.kh > 0 && a.kw > 0, TBN_INVALID_SHAPE,
                 "conv2d: dimensions must be positive");
     TBN_REQUIRE(a.sh > 0 && a.sw > 0 && a.dh > 0 && a.dw > 0 && a.ph >= 0 && a.pw >= 0, TBN_INVALID_ARGUMENT,
@@ -141,8 +231,13 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     TBN_REQUIRE(a.weight_order == TBN_CONV_WEIGHTS_REFERENCE || fast, TBN_INVALID_ARGUMENT, "conv2d: unknown weight order");
     TBN_REQUIRE(!fast || a.C % 64 == 0, TBN_INVALID_ARGUMENT,
                 "conv2d: tap-major weights need a channel count that is a multiple of 64");
-    const size_t front_bytes = fast ? xs_bytes(a.N, a.C, a.H, a.W, npass) : table_bytes(K_pad);
-    const size_t need = front_bytes + scratch_bytes() + (a.dense_w ? 0 : expanded_bytes(K_pad, N_pad));
+    FoldGeom fold;
+    if (!fast && allow_fold) fold = fold_geometry(a.N, a.C, a.H, a.W, a.kh, a.kw, a.sh, a.sw, a.ph, a.pw, a.dh, a.dw, OW, npass);
+    const int terms_w = a.dense_w ? 2 : 1;
+    const size_t folded_w_bytes = fold.ok ? static_cast<size_t>(round_up(terms_w * N_pad * fold.K2_pad * 2, 256)) : 0;
+    const size_t front_bytes = fast ? xs_bytes(a.N, a.C, a.H, a.W, npass)
+                                    : (fold.ok ? static_cast<size_t>(fold.t_bytes) : table_bytes(K_pad));
+    const size_t need = front_bytes + scratch_bytes() + (a.dense_w ? 0 : expanded_bytes(K_pad, N_pad)) + folded_w_bytes;
     TBN_REQUIRE(a.ws && a.ws_bytes >= need, TBN_INVALID_ARGUMENT,
                 "conv2d: workspace too small (see tbn_conv2d_workspace_bytes)");
     TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.ws) % 128 == 0, TBN_INVALID_ARGUMENT,
@@ -154,6 +249,28 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                 "conv2d: TBN_EPI_ADD_RESIDUAL needs a residual tensor");
     EncodeTiledFn encode = encode_tiled_fn();
     TBN_REQUIRE(encode != nullptr, TBN_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+
+    // Folded form: its activation tensor map (overlapping windows) is encoded before anything is launched; if the
+    // driver refuses it, or the workspace only covers the gather path, the element-gather path runs instead.
+    CUtensorMap fold_map;
+    const int64_t fold_pbw = std::min<int64_t>(OW, tc::BM), fold_pbh = std::min<int64_t>(OH, tc::BM / fold_pbw);
+    const int64_t fold_pbi =
+        (fold_pbw == OW && fold_pbh == OH) ? std::max<int64_t>(1, std::min<int64_t>(tc::BM / (fold_pbw * fold_pbh), a.N)) : 1;
+    if (fold.ok) {
+        const int64_t t_stride = a.N * fold.rows * fold.Qp * 16;
+        // Positions (overlapping 64-element windows, 16 elements apart) x folded rows x images x terms.
+        const cuuint64_t gdim[5] = {64, static_cast<cuuint64_t>(fold.Qp - 3), static_cast<cuuint64_t>(fold.rows),
+                                    static_cast<cuuint64_t>(a.N), static_cast<cuuint64_t>(npass)};
+        const cuuint64_t gstride[4] = {32, static_cast<cuuint64_t>(fold.Qp) * 32, static_cast<cuuint64_t>(fold.rows) * fold.Qp * 32,
+                                       static_cast<cuuint64_t>(t_stride) * 2};
+        const cuuint32_t box[5] = {tc::BK, static_cast<cuuint32_t>(fold_pbw), static_cast<cuuint32_t>(fold_pbh),
+                                   static_cast<cuuint32_t>(fold_pbi), 1};
+        const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        const CUresult cr = encode(&fold_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, a.ws, gdim, gstride, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return conv_common(a, npass, tern_act, lo, hi, /*allow_fold=*/false);
+    }
 
     int2* table = static_cast<int2*>(a.ws);
     __nv_bfloat16* xs = static_cast<__nv_bfloat16*>(a.ws);
@@ -176,6 +293,22 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                                                                 static_cast<int>(tiles_per_image), xs, term_stride, 0.f, 0.f);
         profile_end(kProfSplit, a.st);
         rc = launched("nhwc_split_kernel");
+    } else if (fold.ok) {
+        const int64_t total = a.N * fold.rows * fold.Qp;
+        const int grid = static_cast<int>(std::max<int64_t>(1, std::min((total + 255) / 256, static_cast<int64_t>(std::max(sm_count(), 1)) * 32)));
+        const int64_t t_stride = total * 16;
+        profile_begin(kProfSplit, a.st);
+        if (tern_act)
+            s2d_split_kernel<1, true><<<grid, 256, 0, a.st>>>(a.x, a.N, static_cast<int>(a.C), static_cast<int>(a.H), static_cast<int>(a.W),
+                                                              fold.rows, fold.Qp, fold.left, xs, t_stride, lo, hi);
+        else if (npass == 1)
+            s2d_split_kernel<1, false><<<grid, 256, 0, a.st>>>(a.x, a.N, static_cast<int>(a.C), static_cast<int>(a.H), static_cast<int>(a.W),
+                                                               fold.rows, fold.Qp, fold.left, xs, t_stride, 0.f, 0.f);
+        else
+            s2d_split_kernel<2, false><<<grid, 256, 0, a.st>>>(a.x, a.N, static_cast<int>(a.C), static_cast<int>(a.H), static_cast<int>(a.W),
+                                                               fold.rows, fold.Qp, fold.left, xs, t_stride, 0.f, 0.f);
+        profile_end(kProfSplit, a.st);
+        rc = launched("s2d_split_kernel");
     } else {
         conv_tap_table_kernel<<<static_cast<unsigned>((K_pad + 127) / 128), 128, 0, a.st>>>(
             table, static_cast<int>(K), static_cast<int>(K_pad), static_cast<int>(a.H), static_cast<int>(a.W),
@@ -204,6 +337,22 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
         maps.pos = maps.neg;
     }
     maps.a = maps.neg;  // unused in CONV mode
+    if (fold.ok) {
+        // Fold the filters (float terms or the bf16 expansion just made) into the space-to-depth order.
+        const __nv_bfloat16* w_src = a.dense_w ? static_cast<const __nv_bfloat16*>(a.dense_w)
+                                               : reinterpret_cast<const __nv_bfloat16*>(static_cast<uint8_t*>(a.ws) + front_bytes + scratch_bytes());
+        __nv_bfloat16* w_fold = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(a.ws) + front_bytes + scratch_bytes() +
+                                                                 (a.dense_w ? 0 : expanded_bytes(K_pad, N_pad)));
+        const int64_t total = static_cast<int64_t>(terms_w) * N_pad * fold.K2_pad;
+        const int grid = static_cast<int>(std::max<int64_t>(1, std::min((total + 255) / 256, static_cast<int64_t>(std::max(sm_count(), 1)) * 8)));
+        fold_filters_kernel<<<grid, 256, 0, a.st>>>(w_src, terms_w, N_pad, K_pad, static_cast<int>(a.C), static_cast<int>(a.kh),
+                                                    static_cast<int>(a.kw), fold.eh, fold.ew, fold.kh2, fold.K2_pad, w_fold);
+        rc = launched("fold_filters_kernel");
+        if (rc) return rc;
+        rc = make_split_map(encode, w_fold, fold.K2_pad, N_pad, terms_w, bn, &maps.neg);
+        if (rc) return rc;
+        maps.pos = maps.neg;
+    }
 
     tc::Params p = {};
     p.M = static_cast<int>(M);
@@ -243,6 +392,34 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     // Patch mode: when the channels-last copy exists and the geometry fits a TMA box, an m-tile is a rectangle of
     // output pixels (whole output rows first, then several rows, then several images) of at most 128 pixels, and
     // the activation operand of one tap and 64 channels is one tiled TMA load.
+    if (fold.ok) {
+        const int64_t pbw = fold_pbw, pbh = fold_pbh, pbi = fold_pbi;
+        maps.a = fold_map;
+        // The kernel sees a stride-1 convolution with kh2 taps of 64 "channels": one k-block per folded filter row.
+        p.num_kb = fold.kh2;
+        set_segments(p, a.dense_w ? 3 : npass);
+        p.conv.kw = 1;
+        p.conv.taps = fold.kh2;
+        p.conv.dh = 1;
+        p.conv.dw = 1;
+        p.conv.cblocks = 1;
+        p.conv.sh = 1;
+        p.conv.sw = 1;
+        p.conv.ph = fold.top;
+        p.conv.pw = 0;
+        p.conv.pbw = static_cast<int>(pbw);
+        p.conv.pbh = static_cast<int>(pbh);
+        p.conv.pbi = static_cast<int>(pbi);
+        p.conv.patches_w = static_cast<int>((OW + pbw - 1) / pbw);
+        p.conv.patches_h = static_cast<int>((OH + pbh - 1) / pbh);
+        p.conv.a_box_bytes = static_cast<int>(npass * pbw * pbh * pbi * 128);
+        const int64_t tiles_m = static_cast<int64_t>(p.conv.patches_w) * p.conv.patches_h * ((a.N + pbi - 1) / pbi);
+        TBN_REQUIRE(tiles_m * p.tiles_n < (1LL << 31), TBN_INVALID_SHAPE, "conv2d: too many tiles");
+        p.tiles_m = static_cast<int>(tiles_m);
+        if (a.dense_w) return dispatch_bn<2, false, 4, false, 1>(bn, maps, p, a.st);
+        if (tern_act || npass == 1) return dispatch_bn<1, false, 4, false, 2>(bn, maps, p, a.st);
+        return dispatch_bn<2, false, 4, false, 2>(bn, maps, p, a.st);
+    }
     if (fast) {
         const int64_t pbw = std::min<int64_t>(OW, tc::BM);
         const int64_t pbh = std::min<int64_t>(OH, tc::BM / pbw);
@@ -308,9 +485,15 @@ size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, in
                                   int32_t weight_order) {
     if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || M_out <= 0 || kh <= 0 || kw <= 0) return 0;
     const int64_t K_pad = round_up(C * kh * kw, 128);
-    const size_t front = weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR ? xs_bytes(N, C, H, W, 2) : table_bytes(K_pad);
+    size_t front = weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR ? xs_bytes(N, C, H, W, 2) : table_bytes(K_pad);
+    size_t folded = 0;
+    if (weight_order != TBN_CONV_WEIGHTS_TAP_MAJOR && C <= 4) {
+        // Upper bounds of the space-to-depth form (the strides and pads are not known here).
+        front = std::max(front, static_cast<size_t>(round_up(2 * N * ((H + 1) / 2) * ((W + 1) / 2 + 16) * 32, 256)));
+        folded = static_cast<size_t>(round_up(2 * round_up(M_out, 8) * round_up((kh / 2 + 2) * 64, 128) * 2, 256));
+    }
     return front + static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float) +
-           expanded_bytes(K_pad, round_up(M_out, 8));
+           expanded_bytes(K_pad, round_up(M_out, 8)) + folded;
 }
 
 int32_t tbn_permute_filters(const float* d_w, int64_t M, int64_t C, int64_t taps, float* d_out, void* stream) {

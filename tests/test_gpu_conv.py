@@ -30,6 +30,14 @@ CONV_CASES = [
     (2, 3, 32, 32, 64, 7, 7, (2, 2, 3, 3, 1, 1)),
     (33, 8, 7, 5, 24, 3, 3, (1, 1, 1, 1, 1, 1)),
     (2, 512, 4, 4, 300, 3, 3, (1, 1, 1, 1, 1, 1)),     # K = 4608: three accumulation segments
+    # stride 2 over <= 4 channels: the space-to-depth (folded) path of the image stems
+    (2, 3, 20, 20, 8, 7, 7, (2, 2, 3, 3, 1, 1)),
+    (1, 1, 13, 17, 4, 5, 5, (2, 2, 2, 2, 1, 1)),
+    (3, 4, 9, 8, 3, 3, 3, (2, 2, 1, 1, 1, 1)),
+    (2, 2, 12, 12, 3, 2, 2, (2, 2, 0, 0, 1, 1)),
+    (1, 3, 31, 40, 4, 7, 5, (2, 2, 0, 1, 1, 1)),
+    (130, 3, 6, 6, 2, 3, 3, (2, 2, 1, 1, 1, 1)),
+    (4, 3, 64, 64, 64, 7, 7, (2, 2, 3, 3, 1, 1)),
 ]
 
 
