@@ -38,6 +38,10 @@ SIGNATURES = {
     "tbn_gemm_f32": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _f32, _vp, _vp, _i64, _u32, _vp, _sz, _vp]),
     "tbn_conv2d_f32": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp,
                               _vp, _u32, _i32, _vp, _sz, _vp]),
+    "tbn_conv2d_fxb_chain": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
+                                    _i32, _vp, _f32, _vp, _vp, _vp, _vp, _i32, _u32, _i32, _vp, _sz, _vp]),
+    "tbn_conv2d_f32_chain": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
+                                    _i32, _vp, _vp, _vp, _vp, _u32, _i32, _vp, _sz, _vp]),
     "tbn_conv2d_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32]),
     "tbn_permute_filters": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp]),
     "tbn_conv2d_fxb": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
@@ -415,6 +419,38 @@ class _Lib:
         check(self.h.tbn_conv2d_f32(_ptr(x), N, Cc, H, W, _ptr(packed_w), M_out, kh, kw, *[int(v) for v in p], _ptr(bias),
                                     _ptr(residual), _ptr(out), epilogue, order, _ptr(workspace), nbytes, _stream()))
         return out
+
+    def conv2d_chain(self, xshape, w, wshape, p, x=None, x_cl=None, want_y=True, want_y_cl=False, alpha=None, scale=1.0,
+                     bias=None, residual=None, epilogue=0, workspace=None, mode=MODE_TC_BF16X2, device=None):
+        """Convolution inside a layer sequence (tap-major filters).  `w` is {"words": ...} (packed sign filters) or
+        {"split": ...} (float filters).  Input: the NCHW fp32 tensor `x` or its channels-last bf16 terms `x_cl`
+        [2, N, H, W, C] as written by a previous call.  Returns (y or None, y_cl or None)."""
+        import torch
+        self.init()
+        N, Cc, H, W = xshape
+        M_out, _, kh, kw = wshape
+        device = device or (x.device if x is not None else x_cl.device)
+        oh, ow = self.conv_out_hw(H, W, kh, kw, p)
+        y = torch.empty((N, M_out, oh, ow), dtype=torch.float32, device=device) if want_y else None
+        y_cl = torch.empty((2, N, oh, ow, M_out), dtype=torch.bfloat16, device=device) if want_y_cl else None
+        if workspace is None:
+            workspace, nbytes = self.conv_workspace(xshape, M_out, kh, kw, device, CONV_WEIGHTS_TAP_MAJOR)
+        else:
+            nbytes = workspace.numel()
+        if residual is not None:
+            epilogue |= EPI_ADD_RESIDUAL
+        if x is not None:
+            x = x.contiguous()
+        if "words" in w:
+            check(self.h.tbn_conv2d_fxb_chain(_ptr(x), _ptr(x_cl), N, Cc, H, W, _ptr(w["words"]), None, M_out, kh, kw,
+                                              *[int(v) for v in p], _ptr(alpha), scale, _ptr(bias), _ptr(residual), _ptr(y),
+                                              _ptr(y_cl), mode, epilogue, CONV_WEIGHTS_TAP_MAJOR, _ptr(workspace), nbytes,
+                                              _stream()))
+        else:
+            check(self.h.tbn_conv2d_f32_chain(_ptr(x), _ptr(x_cl), N, Cc, H, W, _ptr(w["split"]), M_out, kh, kw,
+                                              *[int(v) for v in p], _ptr(bias), _ptr(residual), _ptr(y), _ptr(y_cl), epilogue,
+                                              CONV_WEIGHTS_TAP_MAJOR, _ptr(workspace), nbytes, _stream()))
+        return y, y_cl
 
     def relu(self, x):
         import torch

@@ -170,6 +170,8 @@ struct ConvArgs {
     size_t ws_bytes;
     cudaStream_t st;
     int32_t weight_order = 0;  // TBN_CONV_WEIGHTS_*
+    const void* x_cl = nullptr;  // input already as channels-last bf16 terms [2][N][H][W][C] (skips the pre-pass)
+    void* y_cl = nullptr;        // also / instead write the output as channels-last bf16 terms [2][N][OH][OW][M_out]
 };
 
 size_t xs_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int npass) {
@@ -220,7 +222,11 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     TBN_REQUIRE(a.H + 2 * a.ph - a.dh * (a.kh - 1) - 1 >= 0 && a.W + 2 * a.pw - a.dw * (a.kw - 1) - 1 >= 0 && OH > 0 &&
                     OW > 0,
                 TBN_INVALID_SHAPE, "conv2d: invalid output dimensions");
-    TBN_REQUIRE(a.x && (a.neg || a.dense_w) && a.y, TBN_INVALID_ARGUMENT, "conv2d: null pointer");
+    TBN_REQUIRE((a.x || a.x_cl) && (a.neg || a.dense_w) && (a.y || a.y_cl), TBN_INVALID_ARGUMENT, "conv2d: null pointer");
+    TBN_REQUIRE(!a.x_cl || (a.weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR && !tern_act), TBN_INVALID_ARGUMENT,
+                "conv2d: a channels-last input needs tap-major filters and the float x binary / float modes");
+    TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.x_cl) % 16 == 0 && reinterpret_cast<uintptr_t>(a.y_cl) % 16 == 0,
+                TBN_INVALID_ARGUMENT, "conv2d: channels-last tensors must be 16-byte aligned");
     TBN_REQUIRE(a.H < 32000 && a.W < 32000 && a.dh * (a.kh - 1) < 32000 && a.dw * (a.kw - 1) < 32000, TBN_INVALID_SHAPE,
                 "conv2d: image or dilated kernel too large");
     const int64_t K = a.C * a.kh * a.kw, M = a.N * OH * OW, N = a.M_out;
@@ -273,10 +279,12 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     }
 
     int2* table = static_cast<int2*>(a.ws);
-    __nv_bfloat16* xs = static_cast<__nv_bfloat16*>(a.ws);
+    __nv_bfloat16* xs = a.x_cl ? static_cast<__nv_bfloat16*>(const_cast<void*>(a.x_cl)) : static_cast<__nv_bfloat16*>(a.ws);
     const int64_t term_stride = a.N * a.H * a.W * a.C;
-    int32_t rc;
-    if (fast) {
+    int32_t rc = TBN_SUCCESS;
+    if (a.x_cl) {
+        // the producing layer's epilogue wrote this form already
+    } else if (fast) {
         const int64_t HW = a.H * a.W, tiles_per_image = (HW + 31) / 32;
         TBN_REQUIRE(HW < (1LL << 31) && a.N * tiles_per_image < (1LL << 31) && a.C / 64 <= 65535, TBN_INVALID_SHAPE,
                     "conv2d: input too large for the pre-pass grid");
@@ -361,6 +369,8 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.tiles_m = static_cast<int>(M_pad / tc::BM);
     p.tiles_n = static_cast<int>((N + bn - 1) / bn);
     p.c = a.y;
+    p.out_cl = static_cast<__nv_bfloat16*>(a.y_cl);
+    p.out_cl_term_stride = M * N;
     p.ldc = N;
     p.out_nchw = 1;
     p.out_hw = static_cast<int>(OH * OW);
@@ -517,6 +527,35 @@ int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                      Epilogue{d_alpha, d_bias, d_residual, scale, epilogue}, d_y, d_workspace, workspace_bytes,
                      as_stream(stream), weight_order};
     return conv_common(a, mode == TBN_MODE_TC_BF16X1 ? 1 : 2, false, 0.f, 0.f);
+}
+
+int32_t tbn_conv2d_fxb_chain(const float* d_x, const void* d_x_cl, int64_t N, int64_t C, int64_t H, int64_t W,
+                             const uint32_t* d_neg, const uint32_t* d_pos, int64_t M_out, int64_t kh, int64_t kw, int32_t sh,
+                             int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale,
+                             const float* d_bias, const float* d_residual, float* d_y, void* d_y_cl, int32_t mode,
+                             uint32_t epilogue, int32_t weight_order, void* d_workspace, size_t workspace_bytes, void* stream) {
+    TBN_REQUIRE(mode == TBN_MODE_AUTO || mode == TBN_MODE_TC_BF16X1 || mode == TBN_MODE_TC_BF16X2, TBN_NOT_IMPLEMENTED,
+                "tbn_conv2d_fxb_chain: modes are AUTO (= two bf16 terms), TC_BF16X1 and TC_BF16X2");
+    ConvArgs a{nullptr, d_x, N, C, H, W, d_neg, d_pos, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+               Epilogue{d_alpha, d_bias, d_residual, scale, epilogue}, d_y, d_workspace, workspace_bytes,
+               as_stream(stream), weight_order};
+    a.x_cl = d_x_cl;
+    a.y_cl = d_y_cl;
+    return conv_common(a, mode == TBN_MODE_TC_BF16X1 ? 1 : 2, false, 0.f, 0.f);
+}
+
+int32_t tbn_conv2d_f32_chain(const float* d_x, const void* d_x_cl, int64_t N, int64_t C, int64_t H, int64_t W,
+                             const void* d_packed_w, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw, int32_t ph,
+                             int32_t pw, int32_t dh, int32_t dw, const float* d_bias, const float* d_residual, float* d_y,
+                             void* d_y_cl, uint32_t epilogue, int32_t weight_order, void* d_workspace, size_t workspace_bytes,
+                             void* stream) {
+    TBN_REQUIRE(d_packed_w != nullptr, TBN_INVALID_ARGUMENT, "tbn_conv2d_f32_chain: null weights");
+    ConvArgs a{d_packed_w, d_x, N, C, H, W, nullptr, nullptr, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+               Epilogue{nullptr, d_bias, d_residual, 1.0f, epilogue}, d_y, d_workspace, workspace_bytes,
+               as_stream(stream), weight_order};
+    a.x_cl = d_x_cl;
+    a.y_cl = d_y_cl;
+    return conv_common(a, 2, false, 0.f, 0.f);
 }
 
 int32_t tbn_conv2d_tbn(const float* d_x, int64_t N, int64_t C, int64_t H, int64_t W, float lo, float hi,

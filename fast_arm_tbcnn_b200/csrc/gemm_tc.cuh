@@ -179,6 +179,11 @@ struct Params {
     // NVLink runs asynchronously beside the next block.  out_list keeps the raw pointers (argument checks).
     int num_out;
     float* out_list[kMaxOutputs];
+    // Optional second result of a convolution: the output as channels-last bf16 terms [2][pixel][N] (what the
+    // next convolution's patch mode reads), written by the epilogue so that no pre-pass is needed in between.
+    // p.c may be null when only this form is wanted.
+    __nv_bfloat16* out_cl;
+    int64_t out_cl_term_stride;
     // AMODE 3: the fp32 activation rows themselves (16-byte aligned, lda % 4 == 0, K % 4 == 0).
     const float* a_rows;
     int64_t lda;
@@ -699,8 +704,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             ptx::named_barrier_sync(1, kEpiThreads);
             const int64_t m = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
             bool row_ok = m < p.M;
-            // Output element (m, n) lives at out_base + n * out_cs.
-            int64_t out_base, out_cs;
+            // Output element (m, n) lives at out_base + n * out_cs; cl_row is the pixel index of the row.
+            int64_t out_base, out_cs, cl_row = m;
             if (PATCH) {
                 // Row of the tile -> (image, output row, output column) inside this tile's patch.
                 const int row = quarter * 32 + lane;
@@ -711,6 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 row_ok = bi < p.conv.pbi && oh < p.conv.OH && ow < p.conv.OW && img * p.out_hw < p.M;
                 out_base = img * p.N * p.out_hw + static_cast<int64_t>(oh) * p.conv.OW + ow;
                 out_cs = p.out_hw;
+                cl_row = img * p.out_hw + static_cast<int64_t>(oh) * p.conv.OW + ow;
             } else if (p.out_nchw) {
                 const int64_t img = m / p.out_hw;
                 out_base = img * p.N * p.out_hw + (m - img * p.out_hw);
@@ -835,14 +841,51 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) o[j] = fmaxf(o[j], 0.0f);
                             }
-                            float* dst = p.c + first;
-                            if (ncols == 32) {
+                            if (p.out_cl != nullptr) {
+                                // Channels-last bf16 terms of the same values (hi = rn(o), lo = rn(o - hi)): what the
+                                // pre-pass of the next convolution would have computed from the fp32 result.
+                                __nv_bfloat16* cl = p.out_cl + cl_row * p.N + nc;
+                                if (ncols == 32 && (p.N & 7) == 0) {
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) dst[j * out_cs] = o[j];
-                            } else {
+                                    for (int g8 = 0; g8 < 4; ++g8) {
+                                        uint32_t hi[4], lo[4];
 #pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (j < ncols) dst[j * out_cs] = o[j];
+                                        for (int e = 0; e < 8; ++e) {
+                                            uint16_t term[2];
+                                            split_terms<2, false>(o[g8 * 8 + e], 0.f, 0.f, term);
+                                            if (e & 1) {
+                                                hi[e >> 1] |= static_cast<uint32_t>(term[0]) << 16;
+                                                lo[e >> 1] |= static_cast<uint32_t>(term[1]) << 16;
+                                            } else {
+                                                hi[e >> 1] = term[0];
+                                                lo[e >> 1] = term[1];
+                                            }
+                                        }
+                                        *reinterpret_cast<uint4*>(cl + g8 * 8) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                                        *reinterpret_cast<uint4*>(cl + p.out_cl_term_stride + g8 * 8) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) {
+                                        if (j < ncols) {
+                                            uint16_t term[2];
+                                            split_terms<2, false>(o[j], 0.f, 0.f, term);
+                                            cl[j] = __ushort_as_bfloat16(term[0]);
+                                            cl[p.out_cl_term_stride + j] = __ushort_as_bfloat16(term[1]);
+                                        }
+                                    }
+                                }
+                            }
+                            if (p.c != nullptr) {
+                                float* dst = p.c + first;
+                                if (ncols == 32) {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) dst[j * out_cs] = o[j];
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j)
+                                        if (j < ncols) dst[j * out_cs] = o[j];
+                                }
                             }
                         }
                     }

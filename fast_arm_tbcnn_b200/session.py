@@ -24,7 +24,7 @@ from . import capi
 
 
 class Session:
-    def __init__(self, graph, device=None, fuse=True, fast=True):
+    def __init__(self, graph, device=None, fuse=True, fast=True, chain=True):
         import torch
         self.torch = torch
         self.graph = graph
@@ -33,6 +33,10 @@ class Session:
         self.quantization = False
         self.fuse = fuse
         self.fast = fast  # channels-last convolution path where the channel count allows it
+        # Layer chaining (float x binary mode): a convolution whose result feeds channels-last convolutions writes the
+        # bf16 channels-last form from its epilogue (and skips the fp32 NCHW tensor when nothing else reads it), and
+        # those convolutions skip their pre-pass.  Same bits as the unchained execution.
+        self.chain = chain and fast
         self.inputs = {}
         self.values = {}
         self.weights = {}
@@ -113,12 +117,20 @@ class Session:
                 last_use[i] = idx
         keep_all = getattr(self, "keep_intermediates", True)
         skip = set()
+        self._cl = {}       # value name -> channels-last bf16 terms of that value (written by a chained convolution)
+        self._shapes = {}   # value name -> NCHW shape, for values that exist only in the channels-last form
+        self._chain_now = self.chain and not self.quantization
+        self._readers = {}
+        for n in nodes:
+            for i in n["inputs"]:
+                self._readers.setdefault(i, []).append(n)
         for idx, n in enumerate(nodes):
             if not keep_all:
                 for name in [k for k, last in last_use.items() if last < idx and k in vals and k not in self.graph["outputs"]
                              and k not in self.inputs]:
                     del vals[name]
                     del last_use[name]
+                    self._cl.pop(name, None)
             if idx in skip:
                 continue
             op = n["op"]
@@ -157,12 +169,14 @@ class Session:
         pd = a.get("pads", [0, 0, 0, 0])
         dl = a.get("dilations", [1, 1])
         p = (st[0], st[1], pd[0], pd[1], dl[0], dl[1])  # only pads[0], pads[1] are honoured (model.hpp:313-321)
-        x = vals[n["inputs"][0]]
+        in_name = n["inputs"][0]
+        x = vals.get(in_name)          # None when the producer only wrote the channels-last form
+        xshape = tuple(x.shape) if x is not None else self._shapes[in_name]
         w = self.weights[n["inputs"][1]]
         bias = self.weights[n["inputs"][2]]["dense"] if len(n["inputs"]) > 2 else None
         out_name = n["outputs"][0]
         order = w.get("order", capi.CONV_WEIGHTS_REFERENCE)
-        ws = self._workspace("conv", L.h.tbn_conv2d_workspace_bytes(x.shape[0], x.shape[1], x.shape[2], x.shape[3],
+        ws = self._workspace("conv", L.h.tbn_conv2d_workspace_bytes(xshape[0], xshape[1], xshape[2], xshape[3],
                                                                     w["shape"][0], w["shape"][2], w["shape"][3], order))
         if self.quantization and "words" in w:
             y = L.conv2d_tbn(x, w["words"], w["shape"], p, alpha=w["alpha_tbn"], bias=bias,
@@ -180,11 +194,29 @@ class Session:
                   and nodes[idx + 2]["op"] == "Relu" and nodes[idx + 2]["inputs"] == nxt["outputs"]
                   and consumers.get(nxt["outputs"][0], 0) == 1):
                 other = [i for i in nxt["inputs"] if i != out_name]
-                if len(other) == 1 and other[0] in vals:
+                if len(other) == 1 and vals.get(other[0]) is not None:
                     residual = vals[other[0]]
                     epilogue |= capi.EPI_RELU
                     skip.update((idx + 1, idx + 2))
                     out_name = nodes[idx + 2]["outputs"][0]
+        if self._chain_now and order == capi.CONV_WEIGHTS_TAP_MAJOR:
+            # Who reads the (possibly fused) result?  Channels-last convolutions take the bf16 form written by this
+            # epilogue; anything else (a residual add, a pool, a graph output) needs the fp32 NCHW tensor.
+            readers = self._readers.get(out_name, [])
+            cl_readers = [r for r in readers if r["op"] == "Conv" and r["inputs"][0] == out_name
+                          and self.weights[r["inputs"][1]].get("order") == capi.CONV_WEIGHTS_TAP_MAJOR]
+            want_cl = len(cl_readers) > 0
+            want_y = (len(cl_readers) != len(readers) or not readers or out_name in self.graph["outputs"]
+                      or getattr(self, "keep_intermediates", True))
+            x_cl = self._cl.get(in_name)
+            y, y_cl = L.conv2d_chain(xshape, w, w["shape"], p, x=None if x_cl is not None else x, x_cl=x_cl, want_y=want_y,
+                                     want_y_cl=want_cl, alpha=w.get("alpha"), bias=bias, residual=residual,
+                                     epilogue=epilogue, workspace=ws, device=self.device)
+            if y_cl is not None:
+                self._cl[out_name] = y_cl
+            self._shapes[out_name] = (xshape[0], w["shape"][0]) + tuple(
+                L.conv_out_hw(xshape[2], xshape[3], w["shape"][2], w["shape"][3], p))
+            return out_name, y
         if "words" in w:
             y = L.conv2d_fxb(x, w["words"], w["shape"], p, alpha=w["alpha"], bias=bias, residual=residual,
                              epilogue=epilogue, workspace=ws, order=order)

@@ -275,6 +275,24 @@ int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                        uint32_t epilogue, int32_t weight_order, void* d_workspace, size_t workspace_bytes,
                        void* stream);
 
+/* Chained forms of tbn_conv2d_fxb / tbn_conv2d_f32 for layer sequences (no reference counterpart: the reference
+ * keeps every activation as NCHW fp32).  d_x_cl, when not null, is the input already in the channels-last form
+ * bf16 [2 terms][N][H][W][C] (hi = rn(x), lo = rn(x - hi)) that the patch-mode kernel reads: the pre-pass is skipped
+ * and d_x may be null (needs C % 64 == 0 and tap-major filters).  d_y_cl, when not null, receives the output in that
+ * same form [2][N][OH][OW][M_out] from the epilogue, in addition to d_y or — with d_y null — instead of it.  Feeding
+ * d_y_cl of one call as d_x_cl of the next gives bit-identical results to passing the fp32 tensors. */
+int32_t tbn_conv2d_fxb_chain(const float* d_x, const void* d_x_cl, int64_t N, int64_t C, int64_t H, int64_t W,
+                             const uint32_t* d_neg, const uint32_t* d_pos, int64_t M_out, int64_t kh, int64_t kw,
+                             int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw,
+                             const float* d_alpha, float scale, const float* d_bias, const float* d_residual,
+                             float* d_y, void* d_y_cl, int32_t mode, uint32_t epilogue, int32_t weight_order,
+                             void* d_workspace, size_t workspace_bytes, void* stream);
+int32_t tbn_conv2d_f32_chain(const float* d_x, const void* d_x_cl, int64_t N, int64_t C, int64_t H, int64_t W,
+                             const void* d_packed_w, int64_t M_out, int64_t kh, int64_t kw, int32_t sh, int32_t sw,
+                             int32_t ph, int32_t pw, int32_t dh, int32_t dw, const float* d_bias,
+                             const float* d_residual, float* d_y, void* d_y_cl, uint32_t epilogue,
+                             int32_t weight_order, void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* "TBN mode" Conv2D: activations ternarised at (lo, hi) while they are gathered, exact integer
  * accumulation.  With alpha, bias and TBN_EPI_BIAS_BEFORE_ALPHA it is bit-equal to the cached fast
  * path of Session::execute_conv (tbn/runtime/model.hpp:375-559: im2col_ternary_packed,

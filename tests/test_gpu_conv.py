@@ -423,3 +423,62 @@ def test_elementwise_transpose_and_global_maxpool(tbn):
             ref[n, c, 0, 0] = best
     assert np.array_equal(got, ref)
     tbn.lib.sync()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("weights", ["binary", "float"])
+def test_chained_convolutions_are_bit_identical(tbn, weights):
+    """tbn_conv2d_*_chain: the channels-last bf16 result written by one convolution's epilogue, fed to the next
+    convolution instead of the fp32 tensor, gives the same bits as the unchained sequence; it equals the split of
+    the fp32 result; and the fp32 tensor can be left out altogether."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = torch.randn((3, 64, 14, 14), device="cuda", generator=g)
+    w1 = torch.randn((128, 64, 3, 3), device="cuda", generator=g) * 0.05
+    w2 = torch.randn((64, 128, 3, 3), device="cuda", generator=g) * 0.05
+    b1 = torch.randn(128, device="cuda", generator=g) * 0.1
+    res = torch.randn((3, 64, 7, 7), device="cuda", generator=g)
+    p1, p2 = (1, 1, 1, 1, 1, 1), (2, 2, 1, 1, 1, 1)
+
+    def prep(w):
+        flat = tbn.lib.permute_filters(w)
+        if weights == "binary":
+            words, alpha = tbn.lib.quant_pack_binary(flat, tbn.LAYOUT_NK)
+            return {"words": words}, alpha
+        return {"split": tbn.lib.dense_pack(flat, tbn.LAYOUT_NK)}, None
+
+    k1, a1 = prep(w1)
+    k2, a2 = prep(w2)
+    y1, y1_cl = tbn.lib.conv2d_chain(tuple(x.shape), k1, tuple(w1.shape), p1, x=x, want_y=True, want_y_cl=True, alpha=a1,
+                                     bias=b1, epilogue=tbn.EPI_RELU)
+    none_y, y1_cl_only = tbn.lib.conv2d_chain(tuple(x.shape), k1, tuple(w1.shape), p1, x=x, want_y=False, want_y_cl=True,
+                                              alpha=a1, bias=b1, epilogue=tbn.EPI_RELU)
+    tbn.lib.sync()
+    assert none_y is None and torch.equal(y1_cl, y1_cl_only)
+    hi = y1.permute(0, 2, 3, 1).bfloat16()
+    assert torch.equal(y1_cl[0], hi)
+    assert torch.equal(y1_cl[1], (y1.permute(0, 2, 3, 1) - hi.float()).bfloat16())
+    plain, _ = tbn.lib.conv2d_chain(tuple(y1.shape), k2, tuple(w2.shape), p2, x=y1, alpha=a2, residual=res)
+    chained, _ = tbn.lib.conv2d_chain(tuple(y1.shape), k2, tuple(w2.shape), p2, x_cl=y1_cl, alpha=a2, residual=res)
+    tbn.lib.sync()
+    assert torch.equal(plain, chained) and float(plain.abs().sum()) > 0
+
+
+@pytest.mark.gpu
+def test_session_layer_chaining_changes_no_bit(tbn, oracle):
+    """ResNet-18 through the Session with and without layer chaining (epilogues writing the channels-last form,
+    pre-passes skipped, fp32 tensors left out where only convolutions read them): identical outputs."""
+    import torch
+    from fast_arm_tbcnn_b200 import graphs
+    from fast_arm_tbcnn_b200.session import Session
+    net = graphs.resnet18(batch=3, seed=2, image=64, classes=10)
+    x = torch.randn((3, 3, 64, 64), device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
+    outs = []
+    for chain, keep in ((False, True), (True, True), (True, False)):
+        s = Session(net, chain=chain)
+        s.keep_intermediates = keep
+        s.set_input("input", x)
+        s.run()
+        outs.append(s.get_output("output").clone())
+    tbn.lib.sync()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
