@@ -106,9 +106,19 @@ __global__ void s2d_split_kernel(const float* __restrict__ x, int64_t N, int C, 
     const int64_t total = N * rows * Qp;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        const int qs = static_cast<int>(idx % Qp);
-        const int rs = static_cast<int>((idx / Qp) % rows);
-        const int64_t n = idx / (static_cast<int64_t>(Qp) * rows);
+        int qs, rs;
+        int64_t n;
+        if (total < (1LL << 31)) {  // 32-bit index arithmetic where it fits
+            const unsigned u = static_cast<unsigned>(idx), r = u / static_cast<unsigned>(Qp);
+            qs = static_cast<int>(u - r * static_cast<unsigned>(Qp));
+            const unsigned img = r / static_cast<unsigned>(rows);
+            rs = static_cast<int>(r - img * static_cast<unsigned>(rows));
+            n = img;
+        } else {
+            qs = static_cast<int>(idx % Qp);
+            rs = static_cast<int>((idx / Qp) % rows);
+            n = idx / (static_cast<int64_t>(Qp) * rows);
+        }
         uint32_t packed[NPASS][8];
 #pragma unroll
         for (int q = 0; q < NPASS; ++q)
