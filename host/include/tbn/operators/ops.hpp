@@ -92,6 +92,15 @@ Tensor conv2d_tbn_packed(const Tensor& input, const PackedWeights& w, const Tens
                          const Conv2DParams& params, bool bias_before_alpha);
 Tensor conv2d_float_dense(const Tensor& input, const DenseWeights& w, const Tensor* bias, const Conv2DParams& params,
                           const Tensor* residual = nullptr, bool relu = false);
+// Convolution inside a layer sequence (tap-major filters only: C % 64 == 0).  The input is the NCHW fp32 tensor `x`
+// and / or its channels-last bf16 form `x_cl` written by the previous call; the result comes back as the NCHW
+// fp32 tensor (want_y), as the channels-last bf16 form (want_y_cl), or both.  Bit-identical to the plain calls.
+struct ConvChainResult {
+    Tensor y, y_cl;
+};
+ConvChainResult conv2d_chain(const Shape& x_shape, const Tensor* x, const Tensor* x_cl, const PackedWeights* packed,
+                             const DenseWeights* dense, const Tensor* bias, const Conv2DParams& params,
+                             const Tensor* residual, bool relu, bool want_y, bool want_y_cl);
 // tbn::conv2d (conv2d.hpp:40-41): scaled-binary filters run on the packed-weight kernel, others on the float path.
 Tensor conv2d(const Tensor& input, const Tensor& weights, const Tensor* bias = nullptr,
               const Conv2DParams& params = Conv2DParams());

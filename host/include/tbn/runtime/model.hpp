@@ -79,6 +79,13 @@ public:
         // Declares a weight initializer as raw fp32 weights to be binarised by sign with the per-output-channel
         // scale mean|w| (extension; the reference only recognises weights that are already +-alpha).
         void mark_binary(const std::string& weight_name) { declared_binary_.insert(weight_name); }
+        // Graph-level optimisations of the float mode, on by default; results are bit-identical either way.
+        //   fusion   a Relu, or an Add with the block input followed by a Relu, that only consumes a Conv's result
+        //            runs in that convolution's epilogue;
+        //   chaining a Conv whose result feeds channels-last convolutions writes the bf16 channels-last form from its
+        //            epilogue (and no fp32 tensor when nothing else reads it); those convolutions skip their pre-pass;
+        //   release  intermediates are freed after their last reader (outputs and inputs are kept).
+        void set_graph_optimizations(bool enable) { optimize_ = enable; }
 
         void set_input(const std::string& name, const Tensor& tensor);
         Tensor get_input(const std::string& name) const;
@@ -95,7 +102,7 @@ public:
         };
         const CachedWeights* weights_for(const std::string& name, const Tensor& w, bool conv);
         void execute_node(const ModelNode& node);
-        void execute_conv(const ModelNode& node);
+        void execute_conv(const ModelNode& node, size_t idx);
         void execute_gemm(const ModelNode& node);
         void execute_pool(const ModelNode& node, bool is_max);
         const Tensor& value(const std::string& name) const;
@@ -104,6 +111,12 @@ public:
         std::unordered_map<std::string, Tensor> input_tensors_, output_tensors_, intermediate_tensors_;
         std::unordered_map<std::string, CachedWeights> weight_cache_;
         std::unordered_map<std::string, Tensor> transposed_;  // op(B) of Gemm nodes with transB, once per weight
+        // State of one run(): channels-last forms and shapes of values, readers of every value, fused-away nodes.
+        std::unordered_map<std::string, Tensor> cl_tensors_;
+        std::unordered_map<std::string, Shape> value_shapes_;
+        std::unordered_map<std::string, std::vector<size_t>> readers_;
+        std::unordered_set<size_t> skip_;
+        bool optimize_ = true;
         std::unordered_set<std::string> declared_binary_;
         bool use_quantization_ = false;
         TilingParams tiling_;

@@ -7,6 +7,9 @@
 // typed_data() / data() hand out the host mirror (downloading first if the device copy is newer);
 // device_data() hands out the device buffer (uploading first if the host copy is newer).
 // A mutable host pointer marks the device copy stale.  Not thread-safe, like the reference.
+// Device buffers come from a caching pool (the Session's tensor allocator, now in HBM): a freed block is kept and
+// handed to the next request of a similar size, so that a Session run allocates from the driver only while its
+// working set still grows.  All kernels of this layer run on one stream, which orders reuse after the last use.
 #pragma once
 
 #include <memory>
@@ -20,6 +23,7 @@ namespace tbn {
 namespace detail {
 struct Storage {
     size_t bytes = 0;
+    size_t capacity = 0;  // bytes of the device block (a pooled block may be larger than `bytes`)
     std::unique_ptr<uint8_t[]> host;
     void* device = nullptr;
     bool host_valid = false;
@@ -33,6 +37,8 @@ public:
     Tensor() = default;
     Tensor(const Shape& shape, DataType dtype, DeviceType device = DeviceType::CPU);
     Tensor(const Shape& shape, DataType dtype, const void* data, DeviceType device = DeviceType::CPU);
+    // Device tensor whose contents are NOT zero-filled: for results that a kernel overwrites completely.
+    static Tensor device_uninitialized(const Shape& shape, DataType dtype);
 
     const Shape& shape() const { return shape_; }
     DataType dtype() const { return dtype_; }

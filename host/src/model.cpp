@@ -75,14 +75,42 @@ void TBNModel::Session::run() {
                   std::to_string(input_tensors_.size()) + ")");
     output_tensors_.clear();
     intermediate_tensors_.clear();
+    cl_tensors_.clear();
+    value_shapes_.clear();
+    readers_.clear();
+    skip_.clear();
     for (const auto& kv : input_tensors_) intermediate_tensors_[kv.first] = kv.second;
     for (const auto& kv : graph_->initializers) intermediate_tensors_[kv.first] = kv.second;
-    for (const auto& node : graph_->nodes) execute_node(node);
+    const auto& nodes = graph_->nodes;
+    std::unordered_map<std::string, size_t> last_use;
+    for (size_t i = 0; i < nodes.size(); ++i)
+        for (const auto& in : nodes[i].inputs) {
+            readers_[in].push_back(i);
+            last_use[in] = i;
+        }
+    const std::unordered_set<std::string> outputs(graph_->outputs.begin(), graph_->outputs.end());
+    for (size_t i = 0; i < nodes.size(); ++i) {
+        if (!skip_.count(i)) {
+            if (nodes[i].op_type == "Conv") execute_conv(nodes[i], i);
+            else execute_node(nodes[i]);
+        }
+        if (optimize_) {
+            // Values whose last reader has run are freed (graph inputs, outputs and weights stay).
+            for (const auto& in : nodes[i].inputs) {
+                auto lu = last_use.find(in);
+                if (lu == last_use.end() || lu->second != i) continue;
+                if (outputs.count(in) || input_tensors_.count(in) || graph_->initializers.count(in)) continue;
+                intermediate_tensors_.erase(in);
+                cl_tensors_.erase(in);
+            }
+        }
+    }
     for (const auto& out : graph_->outputs) {
         auto it = intermediate_tensors_.find(out);
         TBN_CHECK(it != intermediate_tensors_.end(), RuntimeError, "Output '" + out + "' was not produced");
         output_tensors_[out] = it->second;
     }
+    cl_tensors_.clear();
     synchronize();
 }
 
@@ -124,10 +152,17 @@ const TBNModel::Session::CachedWeights* TBNModel::Session::weights_for(const std
     return &weight_cache_.emplace(name, std::move(cw)).first->second;
 }
 
-void TBNModel::Session::execute_conv(const ModelNode& node) {
+void TBNModel::Session::execute_conv(const ModelNode& node, size_t idx) {
     TBN_CHECK(node.inputs.size() >= 2, InvalidArgumentError, "Conv expects at least 2 inputs");
     TBN_CHECK(node.outputs.size() == 1, InvalidArgumentError, "Conv expects 1 output");
-    const Tensor& X = value(node.inputs[0]);
+    // The input may exist only in its channels-last form (written by the previous convolution's epilogue).
+    auto x_it = intermediate_tensors_.find(node.inputs[0]);
+    auto xcl_it = cl_tensors_.find(node.inputs[0]);
+    TBN_CHECK(x_it != intermediate_tensors_.end() || xcl_it != cl_tensors_.end(), RuntimeError,
+              "Input tensor '" + node.inputs[0] + "' not found");
+    const Tensor* Xp = x_it != intermediate_tensors_.end() ? &x_it->second : nullptr;
+    const Tensor* Xcl = xcl_it != cl_tensors_.end() ? &xcl_it->second : nullptr;
+    const Shape x_shape = Xp ? Xp->shape() : value_shapes_.at(node.inputs[0]);
     const Tensor& W = value(node.inputs[1]);
     TBN_CHECK(W.shape().dims.size() == 4, InvalidShapeError, "Conv2D weights must be 4D (MCHW)");
     Conv2DParams p;
@@ -161,29 +196,82 @@ void TBNModel::Session::execute_conv(const ModelNode& node) {
         auto it = intermediate_tensors_.find(node.inputs[2]);
         if (it != intermediate_tensors_.end()) B = &it->second;
     }
+    const auto& nodes = graph_->nodes;
+    std::string out_name = node.outputs[0];
     Tensor result;
-    if (W.dtype() == DataType::BINARY) {
-        result = conv2d_binary(X, W, B, p);
-    } else if (W.dtype() == DataType::TERNARY) {
-        result = conv2d_ternary(X, W, B, p);
-    } else {
-        const CachedWeights* cw = weights_for(node.inputs[1], W, true);
-        if (cw && cw->dense && !use_quantization_) {
-            result = conv2d_float_dense(X, cw->dense_w, B, p);
-        } else if (use_quantization_) {
-            if (cw && cw->scaled_binary) {
-                result = conv2d_tbn_packed(X, cw->packed, &cw->alpha_tbn, B, p, true);  // (acc + bias) * alpha
-            } else {
-                // model.hpp:560-563: quantize_to_binary + conv2d_binary (no per-channel scale).
-                result = conv2d_binary(X, quantize_to_binary(W), B, p);
-            }
+    if (W.dtype() == DataType::BINARY || W.dtype() == DataType::TERNARY) {
+        TBN_CHECK(Xp != nullptr, RuntimeError, "Input tensor '" + node.inputs[0] + "' not found");
+        result = W.dtype() == DataType::BINARY ? conv2d_binary(*Xp, W, B, p) : conv2d_ternary(*Xp, W, B, p);
+        intermediate_tensors_[out_name] = result;
+        return;
+    }
+    const CachedWeights* cw = weights_for(node.inputs[1], W, true);
+    if (use_quantization_) {
+        TBN_CHECK(Xp != nullptr, RuntimeError, "Input tensor '" + node.inputs[0] + "' not found");
+        if (cw && cw->scaled_binary) {
+            result = conv2d_tbn_packed(*Xp, cw->packed, &cw->alpha_tbn, B, p, true);  // (acc + bias) * alpha
         } else {
-            if (!cw) throw NotImplementedError("Conv '" + node.name + "': float filters that are neither scaled-binary nor "
-                                               "declared with mark_binary() are not on the accelerated path");
-            result = conv2d_float_packed(X, cw->packed, B, p);
+            // model.hpp:560-563: quantize_to_binary + conv2d_binary (no per-channel scale).
+            result = conv2d_binary(*Xp, quantize_to_binary(W), B, p);
+        }
+        intermediate_tensors_[out_name] = result;
+        return;
+    }
+    if (!cw) throw NotImplementedError("Conv '" + node.name + "': weights must be FLOAT32");
+    // Float mode.  Fold a following Relu, or Add (with an existing fp32 tensor) + Relu, into the epilogue.
+    bool relu_fused = false;
+    const Tensor* residual = nullptr;
+    if (optimize_ && readers_[out_name].size() == 1 && idx + 1 < nodes.size()) {
+        const ModelNode& nxt = nodes[idx + 1];
+        if (nxt.op_type == "Relu" && nxt.inputs.size() == 1 && nxt.inputs[0] == out_name) {
+            relu_fused = true;
+            skip_.insert(idx + 1);
+            out_name = nxt.outputs.at(0);
+        } else if (nxt.op_type == "Add" && nxt.inputs.size() == 2 && (nxt.inputs[0] == out_name || nxt.inputs[1] == out_name) &&
+                   idx + 2 < nodes.size() && nodes[idx + 2].op_type == "Relu" && nodes[idx + 2].inputs.size() == 1 &&
+                   nodes[idx + 2].inputs[0] == nxt.outputs.at(0) && readers_[nxt.outputs[0]].size() == 1) {
+            const std::string& other = nxt.inputs[0] == out_name ? nxt.inputs[1] : nxt.inputs[0];
+            auto rit = intermediate_tensors_.find(other);
+            if (other != out_name && rit != intermediate_tensors_.end() && rit->second.dtype() == DataType::FLOAT32) {
+                residual = &rit->second;
+                relu_fused = true;
+                skip_.insert(idx + 1);
+                skip_.insert(idx + 2);
+                out_name = nodes[idx + 2].outputs.at(0);
+            }
         }
     }
-    intermediate_tensors_[node.outputs[0]] = result;
+    const bool tap_major = cw->dense ? cw->dense_w.tap_major : cw->packed.tap_major;
+    if (optimize_ && tap_major) {
+        // Chaining: channels-last convolutions among the readers take the bf16 form from this epilogue; any other
+        // reader (a residual add, a pool, a graph output) needs the fp32 NCHW tensor.
+        size_t cl_readers = 0;
+        const auto& rd = readers_[out_name];
+        for (size_t r : rd) {
+            const ModelNode& rn = nodes[r];
+            if (rn.op_type != "Conv" || rn.inputs.at(0) != out_name || rn.inputs.size() < 2) continue;
+            auto wi = graph_->initializers.find(rn.inputs[1]);
+            if (wi == graph_->initializers.end() || wi->second.dtype() != DataType::FLOAT32 || wi->second.shape().dims.size() != 4)
+                continue;
+            if (wi->second.shape().dims[1] % 64 == 0) ++cl_readers;  // what pack_*_weights lay out tap-major
+        }
+        const bool is_output = std::find(graph_->outputs.begin(), graph_->outputs.end(), out_name) != graph_->outputs.end();
+        const bool want_cl = cl_readers > 0;
+        const bool want_y = cl_readers != rd.size() || rd.empty() || is_output;
+        ConvChainResult r = conv2d_chain(x_shape, Xcl ? nullptr : Xp, Xcl, cw->dense ? nullptr : &cw->packed,
+                                         cw->dense ? &cw->dense_w : nullptr, B, p, residual, relu_fused, want_y, want_cl);
+        if (want_cl) cl_tensors_[out_name] = r.y_cl;
+        if (want_y) intermediate_tensors_[out_name] = r.y;
+        const Shape& ws = W.shape();
+        const int64_t OH = (x_shape.dims[2] + 2 * p.pad_h - p.dilation_h * (ws.dims[2] - 1) - 1) / p.stride_h + 1;
+        const int64_t OW = (x_shape.dims[3] + 2 * p.pad_w - p.dilation_w * (ws.dims[3] - 1) - 1) / p.stride_w + 1;
+        value_shapes_[out_name] = Shape{x_shape.dims[0], ws.dims[0], OH, OW};
+        return;
+    }
+    TBN_CHECK(Xp != nullptr, RuntimeError, "Input tensor '" + node.inputs[0] + "' not found");
+    result = cw->dense ? conv2d_float_dense(*Xp, cw->dense_w, B, p, residual, relu_fused)
+                       : conv2d_float_packed(*Xp, cw->packed, B, p, residual, relu_fused);
+    intermediate_tensors_[out_name] = result;
 }
 
 void TBNModel::Session::execute_gemm(const ModelNode& node) {
@@ -291,9 +379,7 @@ void TBNModel::Session::execute_pool(const ModelNode& node, bool is_max) {
 
 void TBNModel::Session::execute_node(const ModelNode& node) {
     const std::string& op = node.op_type;
-    if (op == "Conv") {
-        execute_conv(node);
-    } else if (op == "Gemm") {
+    if (op == "Gemm") {
         execute_gemm(node);
     } else if (op == "Relu") {
         TBN_CHECK(node.inputs.size() == 1, InvalidArgumentError, "ReLU expects 1 input");

@@ -15,7 +15,8 @@ namespace {
 
 using detail::check;
 
-Tensor device_f32(const Shape& shape) { return Tensor(shape, DataType::FLOAT32, DeviceType::CUDA); }
+// Results that a kernel overwrites completely: no zero fill.
+Tensor device_f32(const Shape& shape) { return Tensor::device_uninitialized(shape, DataType::FLOAT32); }
 
 const float* dptr(const Tensor& t) { return static_cast<const float*>(t.device_data()); }
 const float* dptr_or_null(const Tensor* t) { return t ? dptr(*t) : nullptr; }
@@ -410,6 +411,48 @@ Tensor conv2d_float_dense(const Tensor& x, const DenseWeights& w, const Tensor* 
                          ws_bytes, nullptr));
     y.mark_device_written();
     return y;
+}
+
+ConvChainResult conv2d_chain(const Shape& x_shape, const Tensor* x, const Tensor* x_cl, const PackedWeights* packed,
+                             const DenseWeights* dense, const Tensor* bias, const Conv2DParams& p, const Tensor* residual,
+                             bool relu_flag, bool want_y, bool want_y_cl) {
+    TBN_CHECK((x || x_cl) && (packed || dense) && (want_y || want_y_cl), InvalidArgumentError, "conv2d_chain: missing operand");
+    const Shape& wshape = packed ? packed->weight_shape : dense->weight_shape;
+    TBN_CHECK(x_shape.dims.size() == 4 && wshape.dims.size() == 4, InvalidShapeError, "Conv2D input and weights must be 4D");
+    TBN_CHECK((packed ? packed->tap_major : dense->tap_major), InvalidArgumentError, "conv2d_chain needs tap-major filters");
+    ConvDims d{x_shape.dims[0], x_shape.dims[1], x_shape.dims[2], x_shape.dims[3], wshape.dims[0], wshape.dims[2], wshape.dims[3], 0, 0};
+    TBN_CHECK(d.C == wshape.dims[1], InvalidShapeError, "Input channels must match weight channels");
+    if (p.groups != 1) throw NotImplementedError("Grouped convolution not yet implemented");
+    d.OH = (d.H + 2 * p.pad_h - p.dilation_h * (d.kh - 1) - 1) / p.stride_h + 1;
+    d.OW = (d.W + 2 * p.pad_w - p.dilation_w * (d.kw - 1) - 1) / p.stride_w + 1;
+    TBN_CHECK(d.OH > 0 && d.OW > 0, InvalidShapeError, "Invalid output dimensions");
+    check_bias(bias, d.M);
+    ConvChainResult out;
+    if (want_y) out.y = device_f32(Shape{d.N, d.M, d.OH, d.OW});
+    if (want_y_cl) out.y_cl = Tensor::device_uninitialized(Shape{2, d.N, d.OH, d.OW, d.M}, DataType::BFLOAT16);
+    if (residual) TBN_CHECK(residual->shape() == (Shape{d.N, d.M, d.OH, d.OW}), InvalidShapeError, "residual must have the output's shape");
+    const size_t ws_bytes = tbn_conv2d_workspace_bytes(d.N, d.C, d.H, d.W, d.M, d.kh, d.kw, TBN_CONV_WEIGHTS_TAP_MAJOR);
+    const uint32_t epi = (relu_flag ? TBN_EPI_RELU : 0u) | (residual ? TBN_EPI_ADD_RESIDUAL : 0u);
+    const float* xp = x_cl ? nullptr : dptr(*x);
+    const void* xclp = x_cl ? x_cl->device_data() : nullptr;
+    float* yp = want_y ? static_cast<float*>(out.y.device_data()) : nullptr;
+    void* yclp = want_y_cl ? out.y_cl.device_data() : nullptr;
+    const int32_t sh = static_cast<int32_t>(p.stride_h), sw = static_cast<int32_t>(p.stride_w), ph = static_cast<int32_t>(p.pad_h),
+                  pw = static_cast<int32_t>(p.pad_w), dh = static_cast<int32_t>(p.dilation_h), dw = static_cast<int32_t>(p.dilation_w);
+    if (packed) {
+        check(tbn_conv2d_fxb_chain(xp, xclp, d.N, d.C, d.H, d.W, static_cast<const uint32_t*>(packed->neg.device_data()),
+                                   packed->ternary ? static_cast<const uint32_t*>(packed->pos.device_data()) : nullptr, d.M, d.kh,
+                                   d.kw, sh, sw, ph, pw, dh, dw, dptr(packed->alpha), 1.0f, dptr_or_null(bias),
+                                   dptr_or_null(residual), yp, yclp, TBN_MODE_AUTO, epi, TBN_CONV_WEIGHTS_TAP_MAJOR,
+                                   workspace().get(ws_bytes), ws_bytes, nullptr));
+    } else {
+        check(tbn_conv2d_f32_chain(xp, xclp, d.N, d.C, d.H, d.W, dense->split.device_data(), d.M, d.kh, d.kw, sh, sw, ph, pw, dh,
+                                   dw, dptr_or_null(bias), dptr_or_null(residual), yp, yclp, epi, TBN_CONV_WEIGHTS_TAP_MAJOR,
+                                   workspace().get(ws_bytes), ws_bytes, nullptr));
+    }
+    if (want_y) out.y.mark_device_written();
+    if (want_y_cl) out.y_cl.mark_device_written();
+    return out;
 }
 
 // ---------------------------------------------------------------- pooling / elementwise

@@ -1,5 +1,7 @@
 // tbn::Tensor storage on top of the C ABI (tbn_cuda_malloc / h2d / d2h), error mapping, helpers.
+#include <algorithm>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <sstream>
 
@@ -29,8 +31,71 @@ void ensure_runtime() {
     check(status);
 }
 
+// Caching pool of device blocks.  Requests are rounded up to 512 bytes; a cached block is reused when it is at
+// most twice the request (or within 1 MiB of it); at most kPoolLimit bytes stay cached.
+class DevicePool {
+public:
+    void* acquire(size_t bytes, bool zero, size_t* capacity) {
+        const size_t want = (bytes + 511) / 512 * 512;
+        {
+            std::lock_guard<std::mutex> lock(mutex_);
+            auto it = free_.lower_bound(want);
+            if (it != free_.end() && it->first <= std::max(want * 2, want + (size_t(1) << 20))) {
+                void* p = it->second;
+                *capacity = it->first;
+                cached_ -= it->first;
+                free_.erase(it);
+                if (zero) check(tbn_cuda_memset(p, 0, bytes, nullptr));
+                return p;
+            }
+        }
+        void* p = nullptr;
+        const int status = tbn_cuda_malloc(&p, want);  // zero-filled by the library
+        if (status == TBN_OUT_OF_MEMORY) {           // give the cached blocks back and try once more
+            trim(0);
+            check(tbn_cuda_malloc(&p, want));
+        } else {
+            check(status);
+        }
+        *capacity = want;
+        return p;
+    }
+    void release(void* p, size_t capacity) {
+        if (!p) return;
+        {
+            std::lock_guard<std::mutex> lock(mutex_);
+            if (cached_ + capacity <= kPoolLimit) {
+                free_.emplace(capacity, p);
+                cached_ += capacity;
+                return;
+            }
+        }
+        tbn_cuda_free(p);
+    }
+    void trim(size_t keep) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        while (cached_ > keep && !free_.empty()) {
+            auto it = std::prev(free_.end());
+            tbn_cuda_free(it->second);
+            cached_ -= it->first;
+            free_.erase(it);
+        }
+    }
+
+private:
+    static constexpr size_t kPoolLimit = size_t(32) << 30;
+    std::mutex mutex_;
+    std::multimap<size_t, void*> free_;
+    size_t cached_ = 0;
+};
+
+DevicePool& pool() {
+    static DevicePool* p = new DevicePool();  // never destroyed: the CUDA context may be gone at exit
+    return *p;
+}
+
 Storage::~Storage() {
-    if (device) tbn_cuda_free(device);
+    if (device) pool().release(device, capacity);
 }
 
 }  // namespace detail
@@ -49,7 +114,7 @@ Tensor::Tensor(const Shape& shape, DataType dtype, DeviceType device)
     storage_->bytes = static_cast<size_t>(shape.size()) * element_size(dtype);
     if (device == DeviceType::CUDA) {
         detail::ensure_runtime();
-        detail::check(tbn_cuda_malloc(&storage_->device, storage_->bytes));  // zero-filled
+        if (storage_->bytes) storage_->device = detail::pool().acquire(storage_->bytes, /*zero=*/true, &storage_->capacity);
         storage_->device_valid = true;
     } else {
         storage_->host.reset(new uint8_t[storage_->bytes ? storage_->bytes : 1]);
@@ -63,6 +128,20 @@ Tensor::Tensor(const Shape& shape, DataType dtype, const void* data, DeviceType 
     if (storage_->bytes) std::memcpy(storage_->host.get(), data, storage_->bytes);
     device_ = device;
     if (device == DeviceType::CUDA) ensure_device();
+}
+
+Tensor Tensor::device_uninitialized(const Shape& shape, DataType dtype) {
+    Tensor t;
+    for (int64_t d : shape.dims) TBN_CHECK(d >= 0, InvalidShapeError, "negative dimension in " + shape_to_string(shape));
+    t.shape_ = shape;
+    t.dtype_ = dtype;
+    t.device_ = DeviceType::CUDA;
+    t.storage_ = std::make_shared<detail::Storage>();
+    t.storage_->bytes = static_cast<size_t>(shape.size()) * element_size(dtype);
+    detail::ensure_runtime();
+    if (t.storage_->bytes) t.storage_->device = detail::pool().acquire(t.storage_->bytes, /*zero=*/false, &t.storage_->capacity);
+    t.storage_->device_valid = true;
+    return t;
 }
 
 void Tensor::ensure_host() const {
@@ -82,7 +161,7 @@ void Tensor::ensure_device() const {
     detail::Storage& s = *storage_;
     if (s.device_valid) return;
     detail::ensure_runtime();
-    if (!s.device && s.bytes) detail::check(tbn_cuda_malloc(&s.device, s.bytes));
+    if (!s.device && s.bytes) s.device = detail::pool().acquire(s.bytes, /*zero=*/!s.host_valid, &s.capacity);
     if (s.host_valid && s.bytes) {
         detail::check(tbn_cuda_h2d(s.device, s.host.get(), s.bytes, nullptr));
         detail::check(tbn_cuda_sync(nullptr));  // the host mirror may be freed or rewritten right after

@@ -1,11 +1,13 @@
 // Test driver for the C++ host API: reads a graph spec + weight blob + input from files, runs it through
 // tbn::TBNModel::Session and writes the output.  Usage:
-//   run_graph <spec.txt> <blob.f32> <input.f32> <input name> <output name> <quantization 0|1> <out.f32> [repeat]
+//   run_graph <spec.txt> <blob.f32> <input.f32> <input name> <output name> <quantization 0|1> <out.f32> [repeat [noopt]]
+//     (repeat > 1 prints the wall time per Session::run after the first; noopt switches the graph optimisations off)
 //   run_graph --onnx <model.onnx> <input.f32> <input name> <output name> <quantization 0|1> <out.f32> [binary names]
 //   run_graph --dump-onnx <model.onnx>     canonical text listing of the loaded graph (no GPU work)
 // Also exercises the error paths a reference user relies on (exception types), printing "errors ok".
 #include <algorithm>
 #include <cstdint>
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -160,7 +162,13 @@ int main(int argc, char** argv) {
         tbn::Tensor x(model.get_input_shape(argv[4]), tbn::DataType::FLOAT32, input.data());
         session.set_input(argv[4], x);
         const int repeat = argc > 8 ? std::atoi(argv[8]) : 1;
-        for (int i = 0; i < repeat; ++i) session.run();
+        if (argc > 9 && std::strcmp(argv[9], "noopt") == 0) session.set_graph_optimizations(false);
+        session.run();  // first run: packs and caches the weights
+        const auto t0 = std::chrono::steady_clock::now();
+        for (int i = 1; i < repeat; ++i) session.run();
+        if (repeat > 1)
+            std::printf("ms_per_run %.4f\n",
+                        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() / (repeat - 1));
         tbn::Tensor y = session.get_output(argv[5]);
         std::ofstream out(argv[7], std::ios::binary);
         out.write(static_cast<const char*>(static_cast<const void*>(y.typed_data<float>())), static_cast<std::streamsize>(y.data_size()));

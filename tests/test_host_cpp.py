@@ -31,7 +31,7 @@ def test_host_layer_builds_and_exports_reference_names(host):
     assert os.access(driver, os.X_OK)
 
 
-def _run(driver, tmp_path, net, x, quant, out_shape, dequantised, repeat=1):
+def _run(driver, tmp_path, net, x, quant, out_shape, dequantised, repeat=1, extra=()):
     from oracle import graphs
     spec, blob, _ = graphs.to_spec(net, dequantised=dequantised)
     (tmp_path / "spec.txt").write_text(spec)
@@ -39,7 +39,7 @@ def _run(driver, tmp_path, net, x, quant, out_shape, dequantised, repeat=1):
     np.ascontiguousarray(x, dtype=np.float32).tofile(tmp_path / "x.f32")
     out = tmp_path / f"out_{quant}.f32"
     proc = subprocess.run([driver, str(tmp_path / "spec.txt"), str(tmp_path / "blob.f32"), str(tmp_path / "x.f32"), "input",
-                           "output", str(int(quant)), str(out), str(repeat)], capture_output=True, text=True)
+                           "output", str(int(quant)), str(out), str(repeat)] + list(extra), capture_output=True, text=True)
     assert proc.returncode == 0, proc.stderr
     return np.fromfile(out, dtype=np.float32).reshape(out_shape)
 
@@ -136,3 +136,15 @@ def test_lenet_from_onnx_file_matches_the_spec_path(host, oracle, golden, tmp_pa
     via_onnx = _run_onnx(host[1], tmp_path, onnx_schema.net_to_onnx(net), x, False, (1, 10), binary=",".join(sorted(net["binary"])))
     assert np.array_equal(via_spec, via_onnx)
     assert rel_l2(via_onnx, graphs.run_float(net, x, oracle)) <= 1e-5
+
+
+@pytest.mark.gpu
+def test_cpp_session_graph_optimisations_change_no_bit(host, tmp_path):
+    """Epilogue fusion, layer chaining and early release in tbn::TBNModel::Session (on by default) against the
+    node-by-node execution: identical output bits on a ResNet-18 whose stages have 64..512 channels."""
+    from oracle import graphs
+    net = graphs.resnet18(batch=2, seed=2, image=64, classes=10)
+    x = np.random.default_rng(3).standard_normal((2, 3, 64, 64), dtype=np.float32)
+    fast = _run(host[1], tmp_path, net, x, False, (2, 10), False, repeat=2)
+    plain = _run(host[1], tmp_path, net, x, False, (2, 10), False, repeat=2, extra=["noopt"])
+    assert np.array_equal(fast, plain) and np.abs(fast).sum() > 0
