@@ -197,7 +197,7 @@ def cpu_reference_arm(n, steps, warmup, threads, rows_per_thread):
 
 def cnn_block(args, L, capi, torch, dist, dev, rank, world):
     """Binary-CNN throughput, batch-sharded over the ranks with no collective: the 64x14x14 -> 128 3x3 conv
-    layer at batch 4096 and the binary ResNet-18-style network at 224x224 (micro-batches of 128 images per
+    layer at batch 4096 and the binary ResNet-18-style network at 224x224 (micro-batches of 512 images per
     GPU).  Whole-job images/s = images of all ranks / max-over-ranks device time."""
     from fast_arm_tbcnn_b200 import sharding
     from fast_arm_tbcnn_b200.session import Session
@@ -239,7 +239,7 @@ def cnn_block(args, L, capi, torch, dist, dev, rank, world):
     del x, y
 
     # ---- binary ResNet-18-style CNN, 3x224x224
-    micro = 128
+    micro = args.resnet_microbatch
     net = graphs.resnet18(batch=micro, seed=2, image=224, classes=1000)
     sess = Session(net)
     sess.keep_intermediates = False
@@ -593,6 +593,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cnn", action="store_true", help="skip the binary-CNN images/s block")
     ap.add_argument("--only-cnn", action="store_true", help="run only the binary-CNN images/s block")
+    ap.add_argument("--resnet-microbatch", type=int, default=512, help="images per GPU and Session.run in the ResNet-18 block")
     ap.add_argument("--barrier", choices=["nccl", "symm"], default="nccl",
                     help="N > 1, fused path: step-closing barrier = tiny NCCL all-reduce or the symmetric-memory signal barrier")
     ap.add_argument("--no-fused-gather", action="store_true", help="N > 1: use NCCL all-gather instead of peer stores")
