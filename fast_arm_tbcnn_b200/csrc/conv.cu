@@ -250,6 +250,11 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     FoldGeom fold;
     if (!fast && allow_fold) fold = fold_geometry(a.N, a.C, a.H, a.W, a.kh, a.kw, a.sh, a.sw, a.ph, a.pw, a.dh, a.dw, OW, npass);
     const int terms_w = a.dense_w ? 2 : 1;
+    // The workspace query sizes the folded form from upper bounds that unusual pads can exceed: when the caller's
+    // buffer only covers the gather path, that path runs.
+    if (fold.ok && a.ws_bytes < static_cast<size_t>(fold.t_bytes) + scratch_bytes() + (a.dense_w ? 0 : expanded_bytes(K_pad, N_pad)) +
+                                    static_cast<size_t>(round_up(terms_w * N_pad * fold.K2_pad * 2, 256)))
+        fold = FoldGeom{};
     const size_t folded_w_bytes = fold.ok ? static_cast<size_t>(round_up(terms_w * N_pad * fold.K2_pad * 2, 256)) : 0;
     const size_t front_bytes = fast ? xs_bytes(a.N, a.C, a.H, a.W, npass)
                                     : (fold.ok ? static_cast<size_t>(fold.t_bytes) : table_bytes(K_pad));

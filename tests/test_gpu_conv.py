@@ -38,6 +38,7 @@ CONV_CASES = [
     (1, 3, 31, 40, 4, 7, 5, (2, 2, 0, 1, 1, 1)),
     (130, 3, 6, 6, 2, 3, 3, (2, 2, 1, 1, 1, 1)),
     (4, 3, 64, 64, 64, 7, 7, (2, 2, 3, 3, 1, 1)),
+    (1, 3, 8, 8, 4, 3, 3, (2, 2, 40, 40, 1, 1)),        # pads far beyond the image
 ]
 
 
