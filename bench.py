@@ -268,6 +268,40 @@ def cnn_block(args, L, capi, torch, dist, dev, rank, world):
     return out
 
 
+def ternary_block(L, capi, torch, dev):
+    """Float x ternary GEMM of the MLP-projection shape: A 4096 x 4096, W 4096 x 11008 ternarised at 0.7 * mean|W|,
+    per-column scale = mean |W| over the non-zero entries; two bf16 terms.  One GPU, inputs resident."""
+    M, K, N = 4096, 4096, 11008
+    g = torch.Generator(device=dev).manual_seed(0)
+    A = torch.randn((M, K), generator=g, device=dev)
+    W = torch.randn((K, N), generator=g, device=dev)
+    delta = 0.7 * float(W.abs().mean())
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(2):
+        codes, pos, neg, alpha = L.quant_pack_ternary(W, -delta, delta)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(5):
+        codes, pos, neg, alpha = L.quant_pack_ternary(W, -delta, delta)
+    ev1.record()
+    torch.cuda.synchronize()
+    pack_ms = ev0.elapsed_time(ev1) / 5
+    ws, _ = L.gemm_workspace(M, K, capi.MODE_TC_BF16X2, dev)
+    out = torch.empty((M, N), device=dev)
+    for _ in range(3):
+        L.gemm_fxb(A, neg, N, pos=pos, alpha=alpha, mode=capi.MODE_TC_BF16X2, out=out, workspace=ws)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(10):
+        L.gemm_fxb(A, neg, N, pos=pos, alpha=alpha, mode=capi.MODE_TC_BF16X2, out=out, workspace=ws)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / 10
+    return {"shape": [M, K, N], "ms": ms, "tflops": 2.0 * M * K * N / (ms * 1e-3) / 1e12, "mode": "x2",
+            "zeros_fraction": float((W.abs() <= delta).float().mean()), "pack_ms": pack_ms,
+            "pack_note": "sign planes + 2-bit reference codes + per-column scale"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -517,6 +551,12 @@ def run_ours(args):
             cnn = cnn_block(args, L, capi, torch, dist, dev, rank, world)
         except Exception as exc:  # noqa: BLE001  -- the GEMM line must still be printed
             cnn = {"error": repr(exc)}
+    ternary = None
+    if not args.no_cnn and world == 1:
+        try:
+            ternary = ternary_block(L, capi, torch, dev)
+        except Exception as exc:  # noqa: BLE001
+            ternary = {"error": repr(exc)}
     if rank == 0:
         peaks = load_peaks()
         flops_step = 2.0 * n * n * n
@@ -564,6 +604,7 @@ def run_ours(args):
                             "peak_source": f"{peaks['source']} copy {peaks['hbm_gbs']} GB/s"},
         }
         line["cnn"] = cnn
+        line["ternary_mlp_projection"] = ternary
         if world == 1 and not args.no_cpu_baseline:
             from oracle import cpu_oracle
             if cpu_oracle.reference_available():
