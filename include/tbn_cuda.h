@@ -192,8 +192,9 @@ int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const 
  * stride: d_c_list[0..num_out) is a HOST array of device pointers (1..8), e.g. this GPU's result buffer
  * and the peers' buffers mapped into this GPU's address space, each already offset to the column slab
  * this call produces.  This is the compute + all-gather step of the column-sharded multi-GPU GEMM done
- * in one kernel: the tile is transposed through shared memory and leaves as full 64-byte row segments
- * (plain st.global; no TMA multicast).  The caller synchronises the GPUs before anyone reads the result.
+ * in one kernel: every 32 x 32 block of the tile is staged in shared memory and leaves as one tiled TMA store
+ * per destination (ordinary stores into local or peer memory; nothing is broadcast by the hardware), rows and
+ * columns past the matrix being clipped.  The caller synchronises the GPUs before anyone reads the result.
  * Tensor-core modes only; N and ldc multiples of 4.  (New: the reference is single-device.) */
 int32_t tbn_gemm_fxb_multi(const float* d_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,
                            const uint32_t* d_pos, int64_t N, const float* d_alpha, float scale,
