@@ -383,6 +383,7 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.num_kb = static_cast<int>((K + tc::BK - 1) / tc::BK);  // k-blocks that hold real k; the operands are zero beyond K
     p.tiles_m = static_cast<int>(M_pad / tc::BM);
     p.tiles_n = static_cast<int>((N + bn - 1) / bn);
+    p.K = static_cast<int>(K);
     p.c = a.y;
     p.out_cl = static_cast<__nv_bfloat16*>(a.y_cl);
     p.out_cl_term_stride = M * N;

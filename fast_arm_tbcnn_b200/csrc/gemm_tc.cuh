@@ -539,6 +539,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     // overlaps the wait.  Lanes hold consecutive output pixels: coalesced for stride 1.
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
+                        // An 8-element chunk that lies entirely beyond the real K is zero: no table reads, no tests.
+                        if (kb * BK + (a_chunk0 + 2 * j) * 8 >= p.K) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) av[j * 8 + i] = 0.0f;
+                            continue;
+                        }
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int k = kb * BK + (a_chunk0 + 2 * j) * 8 + i;
@@ -738,6 +744,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 const bool first = seg == 0, last = seg == p.num_seg - 1;
 #pragma unroll 1
                 for (int c = group; c < BN / 32; c += kEpiGroups) {
+                    if (n0 + c * 32 >= p.N) break;  // columns past the matrix: nothing to read, add or store
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                            static_cast<uint32_t>(buf * BN + c * 32), r);
