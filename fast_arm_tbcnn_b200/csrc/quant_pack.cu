@@ -158,18 +158,18 @@ __global__ void __launch_bounds__(128) pack_kn_vec4_kernel(const float* __restri
 }
 
 // Layout KN, streaming variant for large matrices: persistent CTAs (one per SM), a producer warp that keeps a
-// ring of TMA tiles in flight and eight consumer warps that classify from shared memory.
+// ring of TMA tiles in flight and sixteen consumer warps that classify from shared memory.
 //   job   = 128 (k) x 512 (n) block of W: four tiles of 32 rows x 512 columns, each row 2 KB contiguous in HBM;
 //   tile  = two TMA boxes of 32 x 256 fp32 (32 KB each); kPackStages tiles in flight per SM;
-//   thread t owns columns t and 256 + t of the job: conflict-free shared-memory reads (lane = bank), one word
-//   per tile and plane, one uint4 (128 k) per column and plane at the end of the job.
+//   thread t owns column t of the job: conflict-free shared-memory reads (lane = bank), one word per tile and
+//   plane, one uint4 (128 k) per column and plane at the end of the job.
 // Jobs are numbered strip-fastest, so CTAs running at the same time read neighbouring 2 KB pieces of the same
 // rows.  The partial |w| sums per 128-row chunk are accumulated in the same order as in the other kernels.
 constexpr int kPackStages = 3;
 constexpr int kPackTileRows = 32, kPackBoxCols = 256, kPackJobCols = 512;
 constexpr int kPackBoxBytes = kPackTileRows * kPackBoxCols * 4;
 constexpr int kPackTileBytes = 2 * kPackBoxBytes;
-constexpr int kPackConsumers = 256;
+constexpr int kPackConsumers = 512;  // one per column of a job
 constexpr int kPackSmemBytes = kPackStages * kPackTileBytes + 1024 + 256;
 
 template <bool TERNARY>
@@ -225,71 +225,59 @@ pack_kn_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, int64_t K, int64_
         return;
     }
 
-    // -------------------------------------------------------------------- consumers
+    // -------------------------------------------------------------------- consumers: one column of the job per thread
     const int t = threadIdx.x;
+    const int tile_off = (t >> 8) * (kPackBoxBytes / 4) + (t & 255);  // box of this column, column inside the box
     int stage = 0;
     uint32_t phase = 0;
     for (int64_t job = blockIdx.x; job < jobs; job += gridDim.x) {
         const int64_t strip = job % strips, chunk = job / strips;
-        const int64_t n0 = strip * kPackJobCols + t, n1 = n0 + kPackBoxCols;
-        uint32_t negw[2][4], posw[2][4];
-        float sum[2] = {0.f, 0.f}, cnt[2] = {0.f, 0.f};
+        const int64_t n = strip * kPackJobCols + t;
+        uint32_t negw[4], posw[4];
+        float sum = 0.f, cnt = 0.f;
 #pragma unroll
         for (int sub = 0; sub < 4; ++sub) {
             if (!ptx::mbar_wait(bar_full + 8 * stage, phase, err_word, kErrPackWaitFull)) return;
-            const float* tile = tiles + stage * (kPackTileBytes / 4) + t;
+            const float* tile = tiles + stage * (kPackTileBytes / 4) + tile_off;
             const int64_t k0 = chunk * kChunkK + sub * kPackTileRows;
             const int rows = static_cast<int>(min(static_cast<int64_t>(kPackTileRows), K - k0));  // <= 0 past the end
-            uint32_t nb[2] = {0u, 0u}, pb[2] = {0u, 0u};
+            uint32_t nb = 0u, pb = 0u;
 #pragma unroll
             for (int r = 0; r < kPackTileRows; ++r) {
-                const float e[2] = {tile[r * kPackBoxCols], tile[kPackBoxBytes / 4 + r * kPackBoxCols]};
+                const float e = tile[r * kPackBoxCols];
                 if (r < rows) {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const uint32_t c = classify<TERNARY>(e[j], lo, hi, ge);
-                        nb[j] |= (c & 1u) << r;
-                        if (TERNARY) {
-                            pb[j] |= (c >> 1) << r;
-                            if (c) {
-                                sum[j] += fabsf(e[j]);
-                                cnt[j] += 1.0f;
-                            }
-                        } else {
-                            sum[j] += fabsf(e[j]);
+                    const uint32_t c = classify<TERNARY>(e, lo, hi, ge);
+                    nb |= (c & 1u) << r;
+                    if (TERNARY) {
+                        pb |= (c >> 1) << r;
+                        if (c) {
+                            sum += fabsf(e);
+                            cnt += 1.0f;
                         }
+                    } else {
+                        sum += fabsf(e);
                     }
                 }
             }
             // The stage goes back to the producer only after every value read above has arrived in registers:
             // the arrive is made to depend on them.
-            ptx::mbar_arrive_after(bar_empty + 8 * stage, nb[0] ^ nb[1] ^ pb[0] ^ pb[1] ^ __float_as_uint(sum[0]) ^ __float_as_uint(sum[1]));
+            ptx::mbar_arrive_after(bar_empty + 8 * stage, nb ^ pb ^ __float_as_uint(sum));
             if (++stage == kPackStages) {
                 stage = 0;
                 phase ^= 1u;
             }
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                negw[j][sub] = nb[j];
-                posw[j][sub] = pb[j];
-            }
+            negw[sub] = nb;
+            posw[sub] = pb;
         }
-        const int64_t ns[2] = {n0, n1};
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int64_t n = ns[j];
-            if (n >= N_pad) continue;
-            const bool real = n < N;  // columns N .. N_pad-1 are padding: all bits 0
-            const int64_t widx = n * KW + chunk * 4;
-            *reinterpret_cast<uint4*>(neg_words + widx) =
-                real ? make_uint4(negw[j][0], negw[j][1], negw[j][2], negw[j][3]) : make_uint4(0u, 0u, 0u, 0u);
-            if (TERNARY)
-                *reinterpret_cast<uint4*>(pos_words + widx) =
-                    real ? make_uint4(posw[j][0], posw[j][1], posw[j][2], posw[j][3]) : make_uint4(0u, 0u, 0u, 0u);
-            if (part_sum && real) {
-                part_sum[chunk * N + n] = sum[j];
-                if (TERNARY) part_cnt[chunk * N + n] = cnt[j];
-            }
+        if (n >= N_pad) continue;
+        const bool real = n < N;  // columns N .. N_pad-1 are padding: all bits 0
+        const int64_t widx = n * KW + chunk * 4;
+        *reinterpret_cast<uint4*>(neg_words + widx) = real ? make_uint4(negw[0], negw[1], negw[2], negw[3]) : make_uint4(0u, 0u, 0u, 0u);
+        if (TERNARY)
+            *reinterpret_cast<uint4*>(pos_words + widx) = real ? make_uint4(posw[0], posw[1], posw[2], posw[3]) : make_uint4(0u, 0u, 0u, 0u);
+        if (part_sum && real) {
+            part_sum[chunk * N + n] = sum;
+            if (TERNARY) part_cnt[chunk * N + n] = cnt;
         }
     }
 }
