@@ -44,9 +44,11 @@ int32_t get_pipeline(Pipeline** out) {
     return TBN_SUCCESS;
 }
 
-// Rows per chunk: about eight chunks, whole 128-row tiles.
+// Rows per chunk: about sixteen chunks (the first upload and the last download are not overlapped, so shorter
+// chunks shorten the call as long as a chunk still fills the GPU for several waves), whole 128-row tiles.
 int64_t chunk_rows(int64_t M) {
-    const int64_t target = (M + 7) / 8;
+    const int64_t parts = M >= 8192 ? 16 : 8;  // measured at 16384^3: 8 -> 25.1 ms, 16 -> 23.9 ms, 32 -> 26 ms
+    const int64_t target = (M + parts - 1) / parts;
     return std::min<int64_t>(round_up(std::max<int64_t>(target, 128), 128), round_up(M, 128));
 }
 
