@@ -16,6 +16,9 @@ struct Pipeline {
     cudaStream_t h2d = nullptr, compute = nullptr, d2h = nullptr;
     cudaEvent_t a_ready[2] = {nullptr, nullptr}, c_done[2] = {nullptr, nullptr}, d2h_done[2] = {nullptr, nullptr};
     cudaEvent_t begin = nullptr, end_compute = nullptr;
+    // Held while one call enqueues its work: the streams and events above are shared by every call on the device,
+    // so two host threads (or two caller streams) must not interleave their records and waits.
+    std::mutex enqueue;
 };
 constexpr int kMaxDev = 64;
 Pipeline g_pipe[kMaxDev];
@@ -95,6 +98,7 @@ int32_t tbn_gemm_fxb_host(const float* h_a, int64_t M, int64_t K, int64_t lda, c
     Pipeline* p = nullptr;
     int32_t rc = get_pipeline(&p);
     if (rc) return rc;
+    std::lock_guard<std::mutex> enqueue_lock(p->enqueue);
     uint8_t* ws = static_cast<uint8_t*>(d_workspace);
     float* a_slot[2] = {reinterpret_cast<float*>(ws), reinterpret_cast<float*>(ws + l.a_bytes)};
     float* c_slot[2] = {reinterpret_cast<float*>(ws + 2 * l.a_bytes), reinterpret_cast<float*>(ws + 2 * l.a_bytes + l.c_bytes)};

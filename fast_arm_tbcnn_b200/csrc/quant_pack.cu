@@ -503,10 +503,14 @@ extern "C" {
 int32_t tbn_quant_pack_binary_noalloc(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t layout, float thr,
                                       int32_t ge, uint32_t* d_words, float* d_alpha, void* stream) {
     TBN_REQUIRE(K > 0 && N > 0, TBN_INVALID_SHAPE, "tbn_quant_pack_binary_noalloc: K and N must be positive");
-    const int64_t chunks = round_up(K, 128) / kChunkK;
-    if (static_cast<size_t>(chunks) * static_cast<size_t>(N) > kNoAllocScratchFloats) {
+    TBN_REQUIRE(K < (int64_t(1) << 40) && N < (int64_t(1) << 40), TBN_INVALID_SHAPE,
+                "tbn_quant_pack_binary_noalloc: dimension too large");
+    // The scratch holds the partial sums of the per-column scale: without d_alpha none is used and any size goes.
+    const size_t chunks = static_cast<size_t>(round_up(K, 128) / kChunkK);
+    const size_t partials = chunks * static_cast<size_t>(N);  // < 2^80 / 128: no overflow after the check above
+    if (d_alpha != nullptr && partials > kNoAllocScratchFloats) {
         return fail(TBN_INVALID_ARGUMENT,
-                    "tbn_quant_pack_binary_noalloc: ceil(K/128)*N = " + std::to_string(chunks * N) +
+                    "tbn_quant_pack_binary_noalloc: ceil(K/128)*N = " + std::to_string(partials) +
                         " exceeds the built-in scratch of " + std::to_string(kNoAllocScratchFloats) +
                         " partial sums; use tbn_quant_pack_binary with a caller workspace");
     }

@@ -184,7 +184,8 @@ class Session:
             return out_name, y
         # float x binary: fold a following Relu (and Add + Relu of a residual block) into the epilogue.
         epilogue, residual = 0, None
-        if self.fuse and consumers.get(out_name, 0) == 1 and idx + 1 < len(nodes):
+        # (a value that is also a graph output keeps its own name: nothing is folded over it)
+        if self.fuse and consumers.get(out_name, 0) == 1 and out_name not in self.graph["outputs"] and idx + 1 < len(nodes):
             nxt = nodes[idx + 1]
             if nxt["op"] == "Relu" and nxt["inputs"] == [out_name]:
                 epilogue |= capi.EPI_RELU
@@ -192,7 +193,7 @@ class Session:
                 out_name = nxt["outputs"][0]
             elif (nxt["op"] == "Add" and out_name in nxt["inputs"] and idx + 2 < len(nodes)
                   and nodes[idx + 2]["op"] == "Relu" and nodes[idx + 2]["inputs"] == nxt["outputs"]
-                  and consumers.get(nxt["outputs"][0], 0) == 1):
+                  and consumers.get(nxt["outputs"][0], 0) == 1 and nxt["outputs"][0] not in self.graph["outputs"]):
                 other = [i for i in nxt["inputs"] if i != out_name]
                 if len(other) == 1 and vals.get(other[0]) is not None:
                     residual = vals[other[0]]

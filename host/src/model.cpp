@@ -221,7 +221,11 @@ void TBNModel::Session::execute_conv(const ModelNode& node, size_t idx) {
     // Float mode.  Fold a following Relu, or Add (with an existing fp32 tensor) + Relu, into the epilogue.
     bool relu_fused = false;
     const Tensor* residual = nullptr;
-    if (optimize_ && readers_[out_name].size() == 1 && idx + 1 < nodes.size()) {
+    // A value that is also a graph output must exist under its own name: nothing is folded over it.
+    auto is_graph_output = [&](const std::string& name) {
+        return std::find(graph_->outputs.begin(), graph_->outputs.end(), name) != graph_->outputs.end();
+    };
+    if (optimize_ && readers_[out_name].size() == 1 && !is_graph_output(out_name) && idx + 1 < nodes.size()) {
         const ModelNode& nxt = nodes[idx + 1];
         if (nxt.op_type == "Relu" && nxt.inputs.size() == 1 && nxt.inputs[0] == out_name) {
             relu_fused = true;
@@ -229,7 +233,8 @@ void TBNModel::Session::execute_conv(const ModelNode& node, size_t idx) {
             out_name = nxt.outputs.at(0);
         } else if (nxt.op_type == "Add" && nxt.inputs.size() == 2 && (nxt.inputs[0] == out_name || nxt.inputs[1] == out_name) &&
                    idx + 2 < nodes.size() && nodes[idx + 2].op_type == "Relu" && nodes[idx + 2].inputs.size() == 1 &&
-                   nodes[idx + 2].inputs[0] == nxt.outputs.at(0) && readers_[nxt.outputs[0]].size() == 1) {
+                   nodes[idx + 2].inputs[0] == nxt.outputs.at(0) && readers_[nxt.outputs[0]].size() == 1 &&
+                   !is_graph_output(nxt.outputs[0])) {
             const std::string& other = nxt.inputs[0] == out_name ? nxt.inputs[1] : nxt.inputs[0];
             auto rit = intermediate_tensors_.find(other);
             if (other != out_name && rit != intermediate_tensors_.end() && rit->second.dtype() == DataType::FLOAT32) {

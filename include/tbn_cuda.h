@@ -146,7 +146,12 @@ int32_t tbn_quant_pack_binary(const float* d_w, int64_t K, int64_t N, int64_t ld
  *     refused with TBN_INVALID_ARGUMENT and a message naming the limit;
  *   - every GPU that loads the library holds the 4 MiB until the process exits;
  *   - the first call on each device looks up the array's device address (no allocation); make that
- *     first call before any stream capture begins;
+ *     first call before any stream capture begins.  The address is kept for the life of the process: after a
+ *     cudaDeviceReset the library has to be loaded again.  With CUDA's lazy module loading the first launch of each
+ *     kernel variant (small, vectorised, TMA-streamed, [N,K] layout, scale finalisation) also loads its code onto
+ *     the device: a host that must see no change in free memory on the request path warms up, during start-up,
+ *     one call for every shape class it will use;
+ *   - the limit concerns the scale only: with d_alpha == NULL no scratch is used and any size is accepted;
  *   - all calls on a device share the array, so two calls whose kernels may overlap on the GPU
  *     (different streams, different host threads) race on it: issue them on one stream or order
  *     them yourself.  Nothing needs clearing between calls: each call writes every partial sum
@@ -208,7 +213,10 @@ int32_t tbn_gemm_fxb_multi(const float* d_a, int64_t M, int64_t K, int64_t lda, 
  * (page-locked memory gives full PCIe speed; pageable memory works, slower); the packed weights, alpha and
  * bias stay on the device.  Rows are processed in chunks so that upload, multiply and download overlap on
  * three internal streams.  All of it is ordered after the work already queued on `stream`, and `stream`
- * waits for the last download: synchronise `stream` before reading h_c. */
+ * waits for the last download: synchronise `stream` before reading h_c.  The internal streams and events are
+ * one set per device: calls on the same device -- from several host threads or on several caller streams --
+ * are safe (each call enqueues under a per-device lock) but run one after the other on the GPU, each call's
+ * uploads waiting for the previous call's work on those streams. */
 size_t tbn_gemm_fxb_host_workspace_bytes(int64_t M, int64_t K, int64_t N, int32_t mode);
 int32_t tbn_gemm_fxb_host(const float* h_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,
                           const uint32_t* d_pos, int64_t N, const float* d_alpha, float scale,

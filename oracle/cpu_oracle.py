@@ -31,12 +31,17 @@ _u32p = C.POINTER(C.c_uint32)
 _i64p = C.POINTER(C.c_int64)
 
 
+def reference_tree():
+    """Where the reference's sources lie: $TBN_REFERENCE, else a checkout named "reference" beside this repository."""
+    return os.environ.get("TBN_REFERENCE") or os.path.abspath(os.path.join(_HERE, "..", "..", "reference"))
+
+
 def build(force=False):
     """Compiles liboracle.so (and _ref when the reference tree is present)."""
     if force or not os.path.exists(ORACLE_SO) or \
             os.path.getmtime(ORACLE_SO) < os.path.getmtime(os.path.join(_HERE, "tbn_oracle.c")):
         subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
-    ref_root = os.environ.get("TBN_REFERENCE", "/root/reference")
+    ref_root = reference_tree()
     if os.path.isdir(os.path.join(ref_root, "GeMM", "05-final")):
         if force or not os.path.exists(REF_SO) or \
                 os.path.getmtime(REF_SO) < os.path.getmtime(os.path.join(_HERE, "ref_shim.cpp")):

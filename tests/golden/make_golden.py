@@ -42,7 +42,7 @@ def parse_cpp_arrays(path):
 
 
 def main():
-    ref_root = os.environ.get("TBN_REFERENCE", "/root/reference")
+    ref_root = co.reference_tree()
     ref = co.Reference()
 
     arrs = parse_cpp_arrays(os.path.join(ref_root, "GeMM/05-final/matrices_to_test.hpp"))

@@ -98,6 +98,36 @@ def test_tbn_mode_bit_exact(tbn, oracle, M, K, N):
     assert np.array_equal(out.cpu().numpy(), oracle.qlinear_matmul_binary(A, qb, 0.37))
 
 
+@pytest.mark.parametrize("name", ["gemm_tbn_128", "gemm_tbn_64"])
+def test_reference_golden_sign_vectors_on_the_gpu(tbn, golden, name):
+    """The reference's own golden vectors (GeMM/05-final/test_final.cpp:23-70, matrices_to_test.hpp; the 64 x 64
+    set of GeMM/03-blocked) through the CUDA kernels: A in {-1, 0, +1} given as fp32 survives the +-0.1
+    ternarisation unchanged and B in {-1, +1} given as fp32 packs by sign, so tbn_gemm_tbn must return A @ B exactly
+    and its sign must equal the stored signs.  The one-term tensor-core mode is exact on these values too
+    (every operand is representable in bf16, every sum is a small integer), which runs the same vectors through
+    gemm_tc_kernel as well as the CUDA-core kernel."""
+    import torch
+    g = golden[name]
+    A, B, Cs = g["A"].astype(np.float32), g["B"].astype(np.float32), g["C"]
+    expect = g["A"].astype(np.int32) @ g["B"].astype(np.int32)
+    assert np.array_equal(np.sign(expect).astype(np.int8), Cs)  # the fixture is self-consistent
+    dA = torch.from_numpy(A).cuda()
+    words, _ = tbn.lib.quant_pack_binary(torch.from_numpy(B).cuda(), want_alpha=False)
+    N = B.shape[1]
+    ws, _ = tbn.lib.gemm_workspace(A.shape[0], A.shape[1], tbn.MODE_TC_BF16X1, dA.device)
+    results = {
+        "tbn_gemm_tbn": tbn.lib.gemm_tbn(dA, words, N, workspace=ws),
+        "tbn_gemm_fxb simt": tbn.lib.gemm_fxb(dA, words, N, mode=tbn.MODE_SIMT),
+        "tbn_gemm_fxb one-term tensor core": tbn.lib.gemm_fxb(dA, words, N, mode=tbn.MODE_TC_BF16X1, workspace=ws),
+        "tbn_gemm_fxb two-term tensor core": tbn.lib.gemm_fxb(dA, words, N, mode=tbn.MODE_TC_BF16X2),
+    }
+    tbn.lib.sync()
+    for what, out in results.items():
+        got = out.cpu().numpy()
+        assert np.array_equal(got, expect.astype(np.float32)), what
+        assert np.array_equal(np.sign(got).astype(np.int8), Cs), what
+
+
 def test_tbn_mode_session_epilogue(tbn, oracle):
     """(acc + bias) * alpha -- the order of Session::execute_conv's cached path."""
     import torch

@@ -148,3 +148,36 @@ def test_cpp_session_graph_optimisations_change_no_bit(host, tmp_path):
     fast = _run(host[1], tmp_path, net, x, False, (2, 10), False, repeat=2)
     plain = _run(host[1], tmp_path, net, x, False, (2, 10), False, repeat=2, extra=["noopt"])
     assert np.array_equal(fast, plain) and np.abs(fast).sum() > 0
+
+
+@pytest.mark.gpu
+def test_conv_output_that_is_also_a_graph_output(host, oracle, tmp_path):
+    """Conv -> Relu where the convolution's own result is a graph output too: the Relu must not be folded into
+    the convolution's epilogue (the pre-activation values would be lost); both outputs come back, from the C++
+    Session and from the Python one."""
+    from oracle import graphs
+    from fast_arm_tbcnn_b200.session import Session
+    net = graphs.conv_layer(batch=2)
+    net["nodes"][0]["outputs"] = ["pre"]
+    net["nodes"].append({"op": "Relu", "name": "act", "inputs": ["pre"], "outputs": ["output"], "attrs": {}})
+    net["outputs"] = {"pre": (2, 128, 14, 14), "output": (2, 128, 14, 14)}
+    x = np.random.default_rng(4).standard_normal((2, 64, 14, 14), dtype=np.float32)
+    keep = {}
+    expect_out = graphs.run_float(net, x, oracle, keep=keep)
+    from oracle import graphs as og
+    spec, blob, _ = og.to_spec(net, dequantised=True)
+    (tmp_path / "spec.txt").write_text(spec)
+    blob.tofile(tmp_path / "blob.f32")
+    x.tofile(tmp_path / "x.f32")
+    for name, expect in (("pre", keep["pre"]), ("output", keep["output"])):
+        out = tmp_path / f"{name}.f32"
+        proc = subprocess.run([host[1], str(tmp_path / "spec.txt"), str(tmp_path / "blob.f32"), str(tmp_path / "x.f32"),
+                               "input", name, "0", str(out)], capture_output=True, text=True)
+        assert proc.returncode == 0, proc.stderr
+        assert rel_l2(np.fromfile(out, dtype=np.float32).reshape(expect.shape), expect) <= 1e-5
+    sess = Session(net)
+    sess.set_input("input", x)
+    sess.run()
+    assert rel_l2(sess.get_output("pre").cpu().numpy(), keep["pre"]) <= 1e-5
+    assert rel_l2(sess.get_output("output").cpu().numpy(), keep["output"]) <= 1e-5
+    assert float(sess.get_output("pre").min()) < 0.0   # really the pre-activation values

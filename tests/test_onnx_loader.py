@@ -13,7 +13,9 @@ from fast_arm_tbcnn_b200 import graphs, host_build
 
 import onnx_schema
 
-REFERENCE_TREE = os.environ.get("TBN_REFERENCE", "/root/reference")
+from oracle import cpu_oracle
+
+REFERENCE_TREE = cpu_oracle.reference_tree()
 
 
 @pytest.fixture(scope="module")

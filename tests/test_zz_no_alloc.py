@@ -67,7 +67,33 @@ def test_sizes_beyond_the_built_in_scratch_are_refused(tbn):
     K, N = 16384, 16384  # 128 chunks x 16384 columns = 2 Mi partial sums > 1 Mi
     w = torch.zeros((8, 8), device="cuda")  # never read: the call is refused on its sizes alone
     words = torch.zeros((8, 8), dtype=torch.int32, device="cuda")
+    alpha = torch.zeros(8, device="cuda")
     status = tbn.lib.h.tbn_quant_pack_binary_noalloc(w.data_ptr(), K, N, N, tbn.LAYOUT_KN, 0.0, 0, words.data_ptr(),
-                                                     None, None)
+                                                     alpha.data_ptr(), None)
     assert status == -1
-    assert "exceeds the built-in scratch" in tbn.last_error()
+    assert "exceeds the built-in scratch" in tbn.last_error() and str(128 * 16384) in tbn.last_error()
+
+
+def test_words_match_the_oracle_and_device_memory_is_untouched(tbn, oracle):
+    """The packed words against the CPU oracle (not only against the regular entry point), and -- after one
+    warm-up call has loaded the kernels -- the free device memory reported by the driver is the same before
+    and after a call: nothing was allocated or freed."""
+    import torch
+    from util import u32
+    rng = np.random.default_rng(21)
+    W = rng.standard_normal((1000, 520), dtype=np.float32)
+    w = torch.from_numpy(W).cuda()
+    Kp, Np = tbn.lib.packed_dims(1000, 520)
+    words = torch.zeros((Np, Kp // 32), dtype=torch.int32, device="cuda")
+    alpha = torch.zeros(520, dtype=torch.float32, device="cuda")
+    tbn.lib.quant_pack_binary_noalloc(w, words, alpha)      # warm-up: loads this shape class's kernels
+    tbn.lib.sync()
+    words.zero_()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    tbn.lib.quant_pack_binary_noalloc(w, words, alpha)
+    tbn.lib.sync()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert np.array_equal(u32(words), oracle.binary_pack_padded(oracle.quantize_to_binary(W)))
+    np.testing.assert_allclose(alpha.cpu().numpy(), oracle.column_abs_mean(W), rtol=1e-5)
