@@ -10,7 +10,7 @@ import os
 from . import build as _build
 
 EPI_ADD_RESIDUAL = 4
-MODE_AUTO, MODE_TC_BF16X1, MODE_TC_BF16X2, MODE_TC_BF16X3, MODE_SIMT = 0, 1, 2, 3, 4
+MODE_AUTO, MODE_TC_BF16X1, MODE_TC_BF16X2, MODE_TC_BF16X3, MODE_SIMT, MODE_TC_FP16X1 = 0, 1, 2, 3, 4, 5
 EPI_RELU, EPI_BIAS_BEFORE_ALPHA = 1, 2
 LAYOUT_KN, LAYOUT_NK = 0, 1
 CONV_WEIGHTS_REFERENCE, CONV_WEIGHTS_TAP_MAJOR = 0, 1

@@ -31,10 +31,13 @@ __global__ void conv_tap_table_kernel(int2* __restrict__ table, int K, int K_pad
 // One block transposes a 64-channel x 32-pixel tile of one image through shared memory; pixels are taken along the
 // flattened h*W + w index, so that reads are 128 contiguous bytes per channel whatever the image width, and writes
 // are 128 bytes per pixel.  HBM bound: 4 B read + 2 NPASS B written per element.
-template <int NPASS, bool TERNARISE>
+// F16: one fp16 term of x * 2^e, e from *amax_bits (the one-pass fp16 mode, see f16_scale_exponent).
+template <int NPASS, bool TERNARISE, bool F16 = false>
 __global__ void __launch_bounds__(256) nhwc_split_kernel(const float* __restrict__ x, int C, int HW, int tiles_per_image,
                                                          __nv_bfloat16* __restrict__ xs, int64_t term_stride, float lo,
-                                                         float hi) {
+                                                         float hi, const uint32_t* __restrict__ amax_bits = nullptr) {
+    static_assert(!F16 || (NPASS == 1 && !TERNARISE), "the fp16 mode has one term");
+    const float mul = F16 ? f16_scale_mul(__ldg(amax_bits)) : 1.0f;
     __shared__ float tile[64][33];
     const int64_t n = blockIdx.x / tiles_per_image;  // grid.x: the only dimension that may exceed 65535
     const int p0 = static_cast<int>(blockIdx.x - n * tiles_per_image) * 32;
@@ -52,7 +55,8 @@ __global__ void __launch_bounds__(256) nhwc_split_kernel(const float* __restrict
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         uint16_t term[NPASS];
-        split_terms<NPASS, TERNARISE>(tile[chunk * 8 + e][pp], lo, hi, term);
+        if (F16) term[0] = __half_as_ushort(__float2half_rn(__fmul_rn(tile[chunk * 8 + e][pp], mul)));
+        else split_terms<NPASS, TERNARISE>(tile[chunk * 8 + e][pp], lo, hi, term);
 #pragma unroll
         for (int q = 0; q < NPASS; ++q) {
             if (e & 1) packed[q][e >> 1] |= static_cast<uint32_t>(term[q]) << 16;
@@ -81,14 +85,14 @@ __global__ void permute_filters_kernel(const float* __restrict__ w, int64_t M, i
 // of the convolutions, expanded once per call so that the GEMM kernel takes it by TMA.  One word (32 k, 64 output
 // bytes) per thread; a warp writes 2 KB contiguous.
 __global__ void expand_words_kernel(const uint32_t* __restrict__ neg, const uint32_t* __restrict__ pos, int64_t words,
-                                    uint4* __restrict__ out) {
+                                    uint4* __restrict__ out, uint32_t one16) {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += stride) {
         const uint32_t nw = __ldg(neg + i), pw = pos ? __ldg(pos + i) : 0u;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const uint32_t nb = (nw >> (8 * q)) & 0xffu, pb = (pw >> (8 * q)) & 0xffu;
-            out[i * 4 + q] = pos ? unpack8<true>(nb, pb) : unpack8<false>(nb, pb);
+            out[i * 4 + q] = pos ? unpack8<true>(nb, pb, one16) : unpack8<false>(nb, pb, one16);
         }
     }
 }
@@ -182,6 +186,7 @@ struct ConvArgs {
     int32_t weight_order = 0;  // TBN_CONV_WEIGHTS_*
     const void* x_cl = nullptr;  // input already as channels-last bf16 terms [2][N][H][W][C] (skips the pre-pass)
     void* y_cl = nullptr;        // also / instead write the output as channels-last bf16 terms [2][N][OH][OW][M_out]
+    bool f16 = false;            // one-pass fp16 mode (tap-major filters, NCHW fp32 input): see TBN_MODE_TC_FP16X1
 };
 
 size_t xs_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int npass) {
@@ -245,6 +250,7 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     const int64_t K_pad = round_up(K, 128), N_pad = round_up(N, 8), M_pad = round_up(M, tc::BM);
     const bool fast = a.weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR;
     TBN_REQUIRE(a.weight_order == TBN_CONV_WEIGHTS_REFERENCE || fast, TBN_INVALID_ARGUMENT, "conv2d: unknown weight order");
+    const bool f16 = a.f16 && fast && !a.x_cl && !a.y_cl && !a.dense_w && !tern_act && npass == 1;
     TBN_REQUIRE(!fast || a.C % 64 == 0, TBN_INVALID_ARGUMENT,
                 "conv2d: tap-major weights need a channel count that is a multiple of 64");
     FoldGeom fold;
@@ -258,7 +264,9 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     const size_t folded_w_bytes = fold.ok ? static_cast<size_t>(round_up(terms_w * N_pad * fold.K2_pad * 2, 256)) : 0;
     const size_t front_bytes = fast ? xs_bytes(a.N, a.C, a.H, a.W, npass)
                                     : (fold.ok ? static_cast<size_t>(fold.t_bytes) : table_bytes(K_pad));
-    const size_t need = front_bytes + scratch_bytes() + (a.dense_w ? 0 : expanded_bytes(K_pad, N_pad)) + folded_w_bytes;
+    // fp16 mode: a 256-byte slot at the very end holds max |x| of the call.
+    const size_t need = front_bytes + scratch_bytes() + (a.dense_w ? 0 : expanded_bytes(K_pad, N_pad)) + folded_w_bytes + (f16 ? 256 : 0);
+    uint32_t* amax_slot = f16 ? reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a.ws) + need - 256) : nullptr;
     TBN_REQUIRE(a.ws && a.ws_bytes >= need, TBN_INVALID_ARGUMENT,
                 "conv2d: workspace too small (see tbn_conv2d_workspace_bytes)");
     TBN_REQUIRE(reinterpret_cast<uintptr_t>(a.ws) % 128 == 0, TBN_INVALID_ARGUMENT,
@@ -305,7 +313,17 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                     "conv2d: input too large for the pre-pass grid");
         dim3 grid(static_cast<unsigned>(a.N * tiles_per_image), static_cast<unsigned>(a.C / 64));
         profile_begin(kProfSplit, a.st);
-        if (tern_act)
+        if (f16) {
+            TBN_CUDA_TRY(cudaMemsetAsync(amax_slot, 0, sizeof(uint32_t), a.st));
+            const int64_t total = a.N * a.C * HW;
+            const int vec_ok = total % 4 == 0 && reinterpret_cast<uintptr_t>(a.x) % 16 == 0;
+            const int gmax = static_cast<int>(std::max<int64_t>(1, std::min((total / (vec_ok ? 4 : 1) + 255) / 256, static_cast<int64_t>(std::max(sm_count(), 1)) * 16)));
+            absmax_kernel<<<gmax, 256, 0, a.st>>>(a.x, 1, total, total, vec_ok, amax_slot);
+            rc = launched("absmax_kernel");
+            if (rc) return rc;
+            nhwc_split_kernel<1, false, true><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(HW),
+                                                                      static_cast<int>(tiles_per_image), xs, term_stride, 0.f, 0.f, amax_slot);
+        } else if (tern_act)
             nhwc_split_kernel<1, true><<<grid, 256, 0, a.st>>>(a.x, static_cast<int>(a.C), static_cast<int>(HW),
                                                                static_cast<int>(tiles_per_image), xs, term_stride, lo, hi);
         else if (npass == 1)
@@ -352,7 +370,7 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
         uint4* expanded = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.ws) + front_bytes + scratch_bytes());
         const int64_t words = N_pad * (K_pad / 32);
         const int grid = static_cast<int>(std::max<int64_t>(1, std::min((words + 255) / 256, static_cast<int64_t>(std::max(sm_count(), 1)) * 8)));
-        expand_words_kernel<<<grid, 256, 0, a.st>>>(a.neg, a.pos, words, expanded);
+        expand_words_kernel<<<grid, 256, 0, a.st>>>(a.neg, a.pos, words, expanded, f16 ? kOneF16 : kOneBf16);
         rc = launched("expand_words_kernel");
         if (rc) return rc;
         rc = make_split_map(encode, expanded, K_pad, N_pad, 1, bn, &maps.neg);
@@ -415,6 +433,8 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     p.conv.pw = a.pw;
     p.conv.act_lo = lo;
     p.conv.act_hi = hi;
+    p.f16 = f16 ? 1 : 0;
+    p.amax_bits = amax_slot;
     // Patch mode: when the channels-last copy exists and the geometry fits a TMA box, an m-tile is a rectangle of
     // output pixels (whole output rows first, then several rows, then several images) of at most 128 pixels, and
     // the activation operand of one tap and 64 channels is one tiled TMA load.
@@ -519,7 +539,7 @@ size_t tbn_conv2d_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, in
         folded = static_cast<size_t>(round_up(2 * round_up(M_out, 8) * round_up((kh / 2 + 2) * 64, 128) * 2, 256));
     }
     return front + static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float) +
-           expanded_bytes(K_pad, round_up(M_out, 8)) + folded;
+           expanded_bytes(K_pad, round_up(M_out, 8)) + folded + 256;
 }
 
 int32_t tbn_permute_filters(const float* d_w, int64_t M, int64_t C, int64_t taps, float* d_out, void* stream) {
@@ -537,12 +557,15 @@ int32_t tbn_conv2d_fxb(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                        int32_t pw, int32_t dh, int32_t dw, const float* d_alpha, float scale, const float* d_bias,
                        const float* d_residual, float* d_y, int32_t mode, uint32_t epilogue, int32_t weight_order,
                        void* d_workspace, size_t workspace_bytes, void* stream) {
-    TBN_REQUIRE(mode == TBN_MODE_AUTO || mode == TBN_MODE_TC_BF16X1 || mode == TBN_MODE_TC_BF16X2, TBN_NOT_IMPLEMENTED,
-                "tbn_conv2d_fxb: modes are AUTO (= two bf16 terms), TC_BF16X1 and TC_BF16X2");
-    const ConvArgs a{nullptr, d_x, N, C, H, W, d_neg, d_pos, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
-                     Epilogue{d_alpha, d_bias, d_residual, scale, epilogue}, d_y, d_workspace, workspace_bytes,
-                     as_stream(stream), weight_order};
-    return conv_common(a, mode == TBN_MODE_TC_BF16X1 ? 1 : 2, false, 0.f, 0.f);
+    TBN_REQUIRE(mode == TBN_MODE_AUTO || mode == TBN_MODE_TC_BF16X1 || mode == TBN_MODE_TC_BF16X2 || mode == TBN_MODE_TC_FP16X1,
+                TBN_NOT_IMPLEMENTED, "tbn_conv2d_fxb: modes are AUTO (= two bf16 terms), TC_BF16X1, TC_BF16X2 and TC_FP16X1");
+    ConvArgs a{nullptr, d_x, N, C, H, W, d_neg, d_pos, M_out, kh, kw, sh, sw, ph, pw, dh, dw,
+               Epilogue{d_alpha, d_bias, d_residual, scale, epilogue}, d_y, d_workspace, workspace_bytes,
+               as_stream(stream), weight_order};
+    // The one-pass fp16 form exists for the channels-last path; other geometries run the two-term form, which is
+    // more accurate than what was asked for.
+    a.f16 = mode == TBN_MODE_TC_FP16X1 && weight_order == TBN_CONV_WEIGHTS_TAP_MAJOR;
+    return conv_common(a, (mode == TBN_MODE_TC_BF16X1 || a.f16) ? 1 : 2, false, 0.f, 0.f);
 }
 
 int32_t tbn_conv2d_fxb_chain(const float* d_x, const void* d_x_cl, int64_t N, int64_t C, int64_t H, int64_t W,

@@ -40,11 +40,14 @@ namespace {
 // =====================================================================================
 
 // One thread converts 8 consecutive k of one row and writes one 16-byte vector per pass.
-template <int NPASS, bool TERNARISE>
+// F16: one fp16 term of a * 2^e instead of bf16 terms, e from *amax_bits (see f16_scale_exponent).
+template <int NPASS, bool TERNARISE, bool F16 = false>
 __global__ void __launch_bounds__(256) split_activations_kernel(const float* __restrict__ a, int64_t M, int64_t K,
                                                                 int64_t lda, int64_t M_pad, int64_t K_pad,
                                                                 __nv_bfloat16* __restrict__ out, float lo, float hi,
-                                                                int vec_ok) {
+                                                                int vec_ok, const uint32_t* __restrict__ amax_bits = nullptr) {
+    static_assert(!F16 || (NPASS == 1 && !TERNARISE), "the fp16 mode has one term");
+    const float mul = F16 ? f16_scale_mul(__ldg(amax_bits)) : 1.0f;
     const int64_t k8_per_row = K_pad / 8;
     const int64_t total = M_pad * k8_per_row;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -65,7 +68,8 @@ __global__ void __launch_bounds__(256) split_activations_kernel(const float* __r
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             uint16_t term[NPASS];
-            split_terms<NPASS, TERNARISE>(v[i], lo, hi, term);
+            if (F16) term[0] = __half_as_ushort(__float2half_rn(__fmul_rn(v[i], mul)));
+            else split_terms<NPASS, TERNARISE>(v[i], lo, hi, term);
 #pragma unroll
             for (int p = 0; p < NPASS; ++p) {
                 if (i & 1) packed[p][i >> 1] |= static_cast<uint32_t>(term[p]) << 16;
@@ -178,6 +182,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const float* __restrict_
 
 int npass_of(int mode) {
     switch (mode) {
+        case TBN_MODE_TC_FP16X1:
         case TBN_MODE_TC_BF16X1: return 1;
         case TBN_MODE_TC_BF16X2: return 2;
         case TBN_MODE_TC_BF16X3: return 3;
@@ -200,6 +205,26 @@ int32_t launch_split(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_
     return launched("split_activations_kernel");
 }
 
+// fp16 mode pre-pass: max |a| of the call into *slot, then the scaled one-term split.
+int32_t launch_split_f16(const float* d_a, int64_t M, int64_t K, int64_t lda, int64_t M_pad, int64_t K_pad,
+                         __nv_bfloat16* out, uint32_t* slot, cudaStream_t st) {
+    TBN_CUDA_TRY(cudaMemsetAsync(slot, 0, sizeof(uint32_t), st));
+    const int vec_ok = (lda % 4 == 0) && (K % 4 == 0) && (reinterpret_cast<uintptr_t>(d_a) % 16 == 0);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    const int64_t units = vec_ok ? M * (K / 4) : M * K;
+    const int grid_max = static_cast<int>(std::max<int64_t>(1, std::min((units + 255) / 256, cap)));
+    profile_begin(kProfSplit, st);
+    absmax_kernel<<<grid_max, 256, 0, st>>>(d_a, M, K, lda, vec_ok, slot);
+    int32_t rc = launched("absmax_kernel");
+    if (rc) return rc;
+    const int64_t total = M_pad * (K_pad / 8);
+    const int grid = static_cast<int>(std::max<int64_t>(1, std::min((total + 255) / 256, cap)));
+    const int vec8 = (lda % 4 == 0) && (reinterpret_cast<uintptr_t>(d_a) % 16 == 0);
+    split_activations_kernel<1, false, true><<<grid, 256, 0, st>>>(d_a, M, K, lda, M_pad, K_pad, out, 0.f, 0.f, vec8, slot);
+    profile_end(kProfSplit, st);
+    return launched("split_activations_kernel<fp16>");
+}
+
 std::atomic<int> g_fused_split{1};
 // 0 never, 1 when the weights have a single column tile, 2 always.
 bool fused_split_wanted(int64_t N) {
@@ -211,10 +236,12 @@ bool fused_split_wanted(int64_t N) {
 int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bool ternarise_act, float act_lo,
                          float act_hi, int npass, const uint32_t* d_neg, const uint32_t* d_pos, int64_t N,
                          const Epilogue& ep, float* d_c, int64_t ldc, void* d_ws, size_t ws_bytes, cudaStream_t st,
-                         float* const* outs = nullptr, int num_out = 0, const void* dense_w = nullptr) {
+                         float* const* outs = nullptr, int num_out = 0, const void* dense_w = nullptr, bool f16 = false) {
     const int64_t M_pad = round_up(M, tc::BM), K_pad = round_up(K, 128), N_pad = round_up(N, 8);
     const size_t split_bytes = static_cast<size_t>(npass) * M_pad * K_pad * sizeof(__nv_bfloat16);
-    const size_t need = split_bytes + scratch_bytes();
+    // fp16 mode: a 256-byte slot after the partial-sum tiles holds max |a| of the call.
+    const size_t need = split_bytes + scratch_bytes() + (f16 ? 256 : 0);
+    uint32_t* amax_slot = f16 ? reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(d_ws) + split_bytes + scratch_bytes()) : nullptr;
     TBN_REQUIRE(d_ws && ws_bytes >= need, TBN_INVALID_ARGUMENT,
                 "gemm: workspace too small (see tbn_gemm_workspace_bytes)");
     TBN_REQUIRE(reinterpret_cast<uintptr_t>(d_ws) % 128 == 0, TBN_INVALID_ARGUMENT,
@@ -228,10 +255,11 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     // Two-term products whose A rows can be read as float4 may skip the split pass: the GEMM's build warps read
     // the fp32 rows and split them in registers (same arithmetic, bit-identical operands) -- once per column
     // tile of the weights, so by default only when there is a single one.
-    const bool fused_split = fused_split_wanted(N) && !ternarise_act && npass == 2 && !dense_w && K % 4 == 0 &&
+    const bool fused_split = !f16 && fused_split_wanted(N) && !ternarise_act && npass == 2 && !dense_w && K % 4 == 0 &&
                              lda % 4 == 0 && reinterpret_cast<uintptr_t>(d_a) % 16 == 0;
     int32_t rc = TBN_SUCCESS;
     if (fused_split) {}
+    else if (f16) rc = launch_split_f16(d_a, M, K, lda, M_pad, K_pad, split, amax_slot, st);
     else if (ternarise_act) rc = launch_split<1, true>(d_a, M, K, lda, M_pad, K_pad, split, act_lo, act_hi, st);
     else if (npass == 1) rc = launch_split<1, false>(d_a, M, K, lda, M_pad, K_pad, split, 0.f, 0.f, st);
     else if (npass == 2) rc = launch_split<2, false>(d_a, M, K, lda, M_pad, K_pad, split, 0.f, 0.f, st);
@@ -245,7 +273,7 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     const cuuint64_t gstride[2] = {static_cast<cuuint64_t>(K_pad) * 2, static_cast<cuuint64_t>(M_pad) * K_pad * 2};
     const cuuint32_t box[3] = {tc::BK, tc::BM, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, split, gdim, gstride, box, estr,
+    const CUresult cr = encode(&tmap, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, split, gdim, gstride, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
@@ -288,6 +316,8 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.a_rows = d_a;
     p.lda = lda;
     p.K = static_cast<int>(K);
+    p.f16 = f16 ? 1 : 0;
+    p.amax_bits = amax_slot;
     if (fused_split)
         return d_pos ? dispatch_bn<2, true, 3, false>(bn, maps, p, st) : dispatch_bn<2, false, 3, false>(bn, maps, p, st);
     if (dense_w) {
@@ -357,7 +387,7 @@ size_t tbn_gemm_workspace_bytes(int64_t M, int64_t K, int32_t mode) {
     if (np == 0) np = 2;  // AUTO resolves to at most the two-term split
     // Split activations + the per-SM partial-sum tiles (sized for the largest SM count in use).
     return static_cast<size_t>(np) * round_up(M, tc::BM) * round_up(K, 128) * sizeof(__nv_bfloat16) +
-           static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float);
+           static_cast<size_t>(std::max(sm_count(), 160)) * tc::BM * 256 * sizeof(float) + 256;
 }
 
 int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const uint32_t* d_neg,
@@ -366,13 +396,13 @@ int32_t tbn_gemm_fxb(const float* d_a, int64_t M, int64_t K, int64_t lda, const 
                      size_t workspace_bytes, void* stream) {
     int32_t rc = check_gemm_args(d_a, M, K, lda, d_neg, N, d_c, ldc);
     if (rc) return rc;
-    TBN_REQUIRE(mode >= TBN_MODE_AUTO && mode <= TBN_MODE_SIMT, TBN_INVALID_ARGUMENT, "tbn_gemm_fxb: unknown mode");
+    TBN_REQUIRE(mode >= TBN_MODE_AUTO && mode <= TBN_MODE_TC_FP16X1, TBN_INVALID_ARGUMENT, "tbn_gemm_fxb: unknown mode");
     const Epilogue ep{d_alpha, d_bias, nullptr, scale, epilogue & ~TBN_EPI_ADD_RESIDUAL};
     if (mode == TBN_MODE_AUTO) mode = prefer_simt(M, N, K) ? TBN_MODE_SIMT : TBN_MODE_TC_BF16X2;
     if (mode == TBN_MODE_SIMT)
         return gemm_simt(d_a, M, K, lda, false, 0.f, 0.f, d_neg, d_pos, N, ep, d_c, ldc, as_stream(stream));
     return gemm_tensor_core(d_a, M, K, lda, false, 0.f, 0.f, npass_of(mode), d_neg, d_pos, N, ep, d_c, ldc, d_workspace,
-                            workspace_bytes, as_stream(stream));
+                            workspace_bytes, as_stream(stream), nullptr, 0, nullptr, mode == TBN_MODE_TC_FP16X1);
 }
 
 size_t tbn_dense_pack_bytes(int64_t K, int64_t N) {
@@ -423,7 +453,8 @@ int32_t tbn_gemm_fxb_multi(const float* d_a, int64_t M, int64_t K, int64_t lda, 
     TBN_REQUIRE(npass_of(mode) != 0, TBN_INVALID_ARGUMENT, "tbn_gemm_fxb_multi: a tensor-core mode is required");
     const Epilogue ep{d_alpha, d_bias, nullptr, scale, epilogue & ~TBN_EPI_ADD_RESIDUAL};
     return gemm_tensor_core(d_a, M, K, lda, false, 0.f, 0.f, npass_of(mode), d_neg, d_pos, N, ep, d_c_list[0], ldc,
-                            d_workspace, workspace_bytes, as_stream(stream), d_c_list, num_out);
+                            d_workspace, workspace_bytes, as_stream(stream), d_c_list, num_out, nullptr,
+                            mode == TBN_MODE_TC_FP16X1);
 }
 
 int32_t tbn_gemm_tbn(const float* d_a, int64_t M, int64_t K, int64_t lda, float lo, float hi, const uint32_t* d_neg,

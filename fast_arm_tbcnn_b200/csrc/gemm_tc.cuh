@@ -32,6 +32,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 #include <climits>
@@ -44,23 +45,40 @@
 namespace tbn_cuda {
 namespace {
 
-// 8 packed bits -> 8 bf16 (+1 = 0x3F80, -1 = 0xBF80, 0 = 0x0000)
+// Bit pattern of +1.0 in the 16-bit operand type: bf16 0x3F80, fp16 0x3C00 (-1.0 sets bit 15 in both, 0 is 0).
+constexpr uint32_t kOneBf16 = 0x3F80u, kOneF16 = 0x3C00u;
+
+// 8 packed bits -> 8 sixteen-bit values (+1 = one16, -1 = one16 | 0x8000, 0 = 0x0000)
 template <bool TERNARY>
-__device__ __forceinline__ uint4 unpack8(uint32_t neg_byte, uint32_t pos_byte) {
+__device__ __forceinline__ uint4 unpack8(uint32_t neg_byte, uint32_t pos_byte, uint32_t one16 = kOneBf16) {
     uint32_t o[4];
+    const uint32_t one2 = one16 | (one16 << 16);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const uint32_t n0 = (neg_byte >> (2 * j)) & 1u, n1 = (neg_byte >> (2 * j + 1)) & 1u;
         if (TERNARY) {
             const uint32_t p0 = (pos_byte >> (2 * j)) & 1u, p1 = (pos_byte >> (2 * j + 1)) & 1u;
-            const uint32_t lo16 = ((n0 | p0) * 0x3F80u) | (n0 << 15);
-            const uint32_t hi16 = ((n1 | p1) * 0x3F80u) | (n1 << 15);
+            const uint32_t lo16 = ((n0 | p0) * one16) | (n0 << 15);
+            const uint32_t hi16 = ((n1 | p1) * one16) | (n1 << 15);
             o[j] = lo16 | (hi16 << 16);
         } else {
-            o[j] = 0x3F803F80u | (n0 << 15) | (n1 << 31);
+            o[j] = one2 | (n0 << 15) | (n1 << 31);
         }
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// The one-pass fp16 mode scales the activations of a call by a power of two so that the largest magnitude lands in
+// [2^14, 2^15): nothing overflows fp16 and values down to 2^-28 of the largest stay normal.  `amax_bits` is the
+// bit pattern of max |a| (a non-negative float).  mul * inv == 1 exactly; the epilogue multiplies by inv.
+__host__ __device__ __forceinline__ uint32_t f16_scale_exponent(uint32_t amax_bits) {
+    int mb = 268 - static_cast<int>((amax_bits >> 23) & 0xffu);  // biased exponent of 2^(14 - floor(log2 amax))
+    mb = mb < 1 ? 1 : (mb > 253 ? 253 : mb);
+    return static_cast<uint32_t>(mb);
+}
+__device__ __forceinline__ float f16_scale_mul(uint32_t amax_bits) { return __uint_as_float(f16_scale_exponent(amax_bits) << 23); }
+__device__ __forceinline__ float f16_scale_inv(uint32_t amax_bits) {
+    return __uint_as_float((254u - f16_scale_exponent(amax_bits)) << 23);
 }
 
 // fp32 -> NPASS bf16 terms whose sum approximates (NPASS = 3: equals) the input; or its ternarisation.
@@ -82,6 +100,32 @@ __device__ __forceinline__ void split_terms(float v, float lo, float hi, uint16_
             r = (q == 0 && !isfinite(r)) ? 0.0f : __fsub_rn(r, __bfloat162float(h));
         }
     }
+}
+
+// max |a| over a strided matrix as the bit pattern of a non-negative float (for those, integer order = float order;
+// a NaN has the largest pattern and so wins).  *out must be zero before the launch.
+__global__ void __launch_bounds__(256) absmax_kernel(const float* __restrict__ a, int64_t rows, int64_t cols, int64_t ld,
+                                                     int vec_ok, uint32_t* __restrict__ out) {
+    uint32_t best = 0u;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    if (vec_ok) {
+        const int64_t c4 = cols / 4, total = rows * c4;
+        for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+            const int64_t r = i / c4, c = (i - r * c4) * 4;
+            const float4 v = __ldg(reinterpret_cast<const float4*>(a + r * ld + c));
+            best = max(max(best, __float_as_uint(v.x) & 0x7fffffffu), __float_as_uint(v.y) & 0x7fffffffu);
+            best = max(max(best, __float_as_uint(v.z) & 0x7fffffffu), __float_as_uint(v.w) & 0x7fffffffu);
+        }
+    } else {
+        const int64_t total = rows * cols;
+        for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+            const int64_t r = i / cols;
+            best = max(best, __float_as_uint(__ldg(a + r * ld + (i - r * cols))) & 0x7fffffffu);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if ((threadIdx.x & 31) == 0 && best != 0u) atomicMax(out, best);
 }
 
 namespace tc {
@@ -184,6 +228,11 @@ struct Params {
     // p.c may be null when only this form is wanted.
     __nv_bfloat16* out_cl;
     int64_t out_cl_term_stride;
+    // One-pass fp16 mode: both operands are fp16 instead of bf16 (same tiles, same swizzle; only the instruction
+    // descriptor and the bit pattern of +-1 differ) and the result is multiplied by the inverse of the power-of-two
+    // scale the activation pre-pass applied (derived from *amax_bits, the bit pattern of max |a| of this call).
+    int f16;
+    const uint32_t* amax_bits;
     // AMODE 3: the fp32 activation rows themselves (16-byte aligned, lda % 4 == 0, K % 4 == 0).
     const float* a_rows;
     int64_t lda;
@@ -372,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = ptx::umma_idesc_bf16_f32(BM, BN);
+            const uint32_t idesc = p.f16 ? ptx::umma_idesc_f16_f32(BM, BN) : ptx::umma_idesc_bf16_f32(BM, BN);
             int stage = 0;
             uint32_t phase = 0;
             int iter = 0;  // counts (tile, segment) units; each uses one accumulator buffer
@@ -429,6 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         // ------------------------------------------------------------ operand build
         static_assert(BN <= kBuildThreads, "one build thread per weight column of the tile");
         const int r = threadIdx.x - 64;  // weight column (row of the K-major weight tile) of this thread
+        const uint32_t one16 = p.f16 ? kOneF16 : kOneBf16;
         // CONV mode: this thread also builds activation row (r & 127), 16-byte chunks (r >> 7) + {0, 2, 4, 6}.
         const int a_row = r & (BM - 1);
         const int a_chunk0 = r >> 7;
@@ -571,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         const uint32_t nb = (nw[c >> 2] >> (8 * (c & 3))) & 0xffu;
                         const uint32_t pb = (pw[c >> 2] >> (8 * (c & 3))) & 0xffu;
                         // 16-byte chunk c of row r lands at chunk (c ^ (r & 7)): the 128-byte swizzle.
-                        *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8<TERNARY>(nb, pb);
+                        *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8<TERNARY>(nb, pb, one16);
                     }
                 }
                 if (FAST) {
@@ -697,6 +747,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         int iter = 0;
         int tile_iter = 0;
         bool ok = true;
+        // fp16 mode: undo the power-of-two scale of the activations (exact) together with the caller's scale.
+        const float ep_scale = p.amax_bits ? __fmul_rn(p.ep.scale, f16_scale_inv(__ldg(p.amax_bits))) : p.ep.scale;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -783,10 +835,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         for (int j4 = 0; j4 < 8; ++j4) {
                             const int j = j4 * 4;
                             float4 o;
-                            o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags, 0.0f);
-                            o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags, 0.0f);
-                            o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags, 0.0f);
-                            o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags, 0.0f);
+                            o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], ep_scale, p.ep.flags, 0.0f);
+                            o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], ep_scale, p.ep.flags, 0.0f);
+                            o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], ep_scale, p.ep.flags, 0.0f);
+                            o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], ep_scale, p.ep.flags, 0.0f);
                             *reinterpret_cast<float4*>(tbuf + lane * 32 + ((j4 ^ (lane & 7)) << 2)) = o;
                         }
                         // Shared memory written by these lanes -> readable by the TMA engine; then one lane sends the
@@ -809,10 +861,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {
                                 float4 o;
-                                o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], p.ep.scale, p.ep.flags, 0.0f);
-                                o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], p.ep.scale, p.ep.flags, 0.0f);
-                                o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], p.ep.scale, p.ep.flags, 0.0f);
-                                o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], p.ep.scale, p.ep.flags, 0.0f);
+                                o.x = apply_epilogue(v[j + 0], as[j + 0], bs[j + 0], ep_scale, p.ep.flags, 0.0f);
+                                o.y = apply_epilogue(v[j + 1], as[j + 1], bs[j + 1], ep_scale, p.ep.flags, 0.0f);
+                                o.z = apply_epilogue(v[j + 2], as[j + 2], bs[j + 2], ep_scale, p.ep.flags, 0.0f);
+                                o.w = apply_epilogue(v[j + 3], as[j + 3], bs[j + 3], ep_scale, p.ep.flags, 0.0f);
                                 *reinterpret_cast<float4*>(c_row + nc + j) = o;
                             }
                         } else {
@@ -830,8 +882,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     const int j = 4 * j4 + i;
-                                    o[j] = bias_first ? __fmul_rn(__fadd_rn(__fmul_rn(v[j], p.ep.scale), bj[i]), aj[i])
-                                                      : __fadd_rn(__fmul_rn(__fmul_rn(v[j], aj[i]), p.ep.scale), bj[i]);
+                                    o[j] = bias_first ? __fmul_rn(__fadd_rn(__fmul_rn(v[j], ep_scale), bj[i]), aj[i])
+                                                      : __fadd_rn(__fmul_rn(__fmul_rn(v[j], aj[i]), ep_scale), bj[i]);
                                 }
                             }
                             const int ncols = static_cast<int>(min(static_cast<int64_t>(32), p.N - nc));

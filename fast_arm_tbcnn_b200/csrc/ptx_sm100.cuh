@@ -211,6 +211,11 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int m, int n) {
            | (static_cast<uint32_t>(m >> 4) << 24);   // M / 16
 }
 
+// Instruction descriptor, kind::f16: fp16 x fp16 -> fp32, both operands K-major (operand format fields 0).
+__host__ __device__ constexpr uint32_t umma_idesc_f16_f32(int m, int n) {
+    return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {

@@ -43,13 +43,22 @@ extern "C" {
 /* Weights +-1/0 are exact in bf16; the fp32 activations are split into NPASS bf16 terms
  * (hi [+ mid] [+ lo]) that are multiplied on the tcgen05 tensor cores into one fp32
  * accumulator.  Relative L2 error against the fp32 reference: X3 ~1e-7 (exact split),
- * X2 ~2e-6 (default; inside the 1e-5 bar), X1 ~2e-3 (declared bf16-activation variant). */
+ * X2 ~2e-6 (default; inside the 1e-5 bar), X1 ~2e-3 (outside every bar, see TBN_MODE_TC_FP16X1). */
 #define TBN_MODE_AUTO 0
 #define TBN_MODE_TC_BF16X1 1
 #define TBN_MODE_TC_BF16X2 2
 #define TBN_MODE_TC_BF16X3 3
 #define TBN_MODE_SIMT 4 /* CUDA-core add/subtract-by-sign, fp32, k ascending: bit-equal to
                            qlinear_matmul_binary_naive */
+/* The DECLARED lower-precision variant: one tensor-core pass over fp16 activations (11 significant bits,
+ * relative L2 error ~2e-4, inside the 1e-3 bar such a variant is allowed) against +-1/0 weights, which are exact
+ * in fp16, with fp32 accumulation.  A pre-pass finds max |a| of the call and scales the activations by the power
+ * of two that puts it into [2^14, 2^15) -- so no input overflows fp16 and values down to 2^-28 of the largest keep
+ * full precision -- and the epilogue multiplies the exact inverse back in.  About twice the throughput of
+ * TBN_MODE_TC_BF16X2; never chosen by TBN_MODE_AUTO.  TBN_MODE_TC_BF16X1 (8 significant bits, ~2e-3) is outside
+ * every accuracy bar of the float x binary product: it exists for the integer-exact TBN mode, whose ternarised
+ * activations bf16 represents exactly, and is kept selectable only for comparison. */
+#define TBN_MODE_TC_FP16X1 5
 
 /* ---- epilogue flags -------------------------------------------------------------- */
 #define TBN_EPI_RELU 1u

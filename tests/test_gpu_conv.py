@@ -105,6 +105,28 @@ FAST_CASES = [
 
 
 @pytest.mark.parametrize("case", FAST_CASES)
+def test_conv_declared_fp16_variant(tbn, oracle, case):
+    """tbn_conv2d_fxb in the declared one-pass fp16 mode (channels-last path) stays within 1e-3 of the reference's
+    float convolution, also when the input is scaled far outside fp16's own range."""
+    import torch
+    from oracle import graphs
+    x, w, b, p = _conv_inputs(case, seed=12)
+    dw_, db = torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda()
+    words, alpha = tbn.lib.quant_pack_binary(tbn.lib.permute_filters(dw_), tbn.LAYOUT_NK)
+    for scale in (1.0, 2.0 ** 40):
+        xs = (x * np.float32(scale)).astype(np.float32)
+        y = tbn.lib.conv2d_fxb(torch.from_numpy(xs).cuda(), words, w.shape, p, alpha=alpha, bias=db, mode=tbn.MODE_TC_FP16X1,
+                               order=tbn.CONV_WEIGHTS_TAP_MAJOR)
+        tbn.lib.sync()
+        assert rel_l2(y.cpu().numpy(), oracle.conv2d_f32(xs, graphs.dequantise(w), b, p)) <= 1e-3, scale
+    # reference filter order: the library runs its two-term form, inside the fp32 bar
+    words_r, alpha_r = tbn.lib.quant_pack_binary(dw_.reshape(w.shape[0], -1), tbn.LAYOUT_NK)
+    y = tbn.lib.conv2d_fxb(torch.from_numpy(x).cuda(), words_r, w.shape, p, alpha=alpha_r, bias=db, mode=tbn.MODE_TC_FP16X1)
+    tbn.lib.sync()
+    assert rel_l2(y.cpu().numpy(), oracle.conv2d_f32(x, graphs.dequantise(w), b, p)) <= TOL_FP32
+
+
+@pytest.mark.parametrize("case", FAST_CASES)
 def test_conv_channels_last_path(tbn, oracle, case):
     """Tap-major weights + channels-last activation copy: same results as the reference's float convolution
     (float x binary and float filters) and, in TBN mode, bit-equal to the Session's integer path."""

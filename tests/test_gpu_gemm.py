@@ -71,6 +71,46 @@ def test_tensor_core_vs_float_gemm(tbn, oracle, M, K, N, mode):
     assert err <= (TOL_BF16_ACT if mode == "x1" else TOL_FP32), (mode, err)
 
 
+TOL_DECLARED = 1e-3   # the bar of the one declared lower-precision variant (fp16 activations, one pass)
+
+
+@pytest.mark.parametrize("M,K,N", TC_SHAPES + [(4096, 4096, 4096), (4096, 4096, 11008)])
+@pytest.mark.parametrize("ternary", [False, True])
+def test_declared_fp16_variant_meets_its_bar(tbn, oracle, M, K, N, ternary):
+    """TBN_MODE_TC_FP16X1 (fp16 activations scaled by a power of two per call, one tensor-core pass) stays within
+    relative L2 1e-3 of the reference's float GEMM -- on the square ladder, ragged shapes and the MLP-projection
+    shape, binary and ternary weights -- and rescaling A by 2^-100 or 2^+100 changes the result by exactly that
+    factor's effect (the range guard: nothing overflows, nothing is flushed)."""
+    import torch
+    from oracle import graphs
+    if M * K * N > 2 ** 34 and ternary is False and N == 11008:
+        pytest.skip("the projection shape is a ternary case")
+    A, W = make_case(0, 1, M, K, N)
+    bias = np.random.default_rng(2).standard_normal(N, dtype=np.float32)
+    dW, dA = torch.from_numpy(W).cuda(), torch.from_numpy(A).cuda()
+    if ternary:
+        delta = float(np.float32(0.7) * np.abs(W).mean(dtype=np.float32))
+        _, pos, neg, alpha = tbn.lib.quant_pack_ternary(dW, -delta, delta, want_codes=False)
+        t = oracle.quantize_to_ternary(W, -delta, delta).astype(np.float32)
+        Wd = t * oracle.column_abs_mean_nonzero(W, -delta, delta)[None, :]
+    else:
+        neg, alpha = tbn.lib.quant_pack_binary(dW)
+        pos = None
+        Wd = graphs.dequantise(W) if K * N <= 2 ** 22 else np.where(W > 0, 1, -1).astype(np.float32) * oracle.column_abs_mean(W)[None, :]
+    out = tbn.lib.gemm_fxb(dA, neg, N, pos=pos, alpha=alpha, bias=torch.from_numpy(bias).cuda(), mode=tbn.MODE_TC_FP16X1)
+    tbn.lib.sync()
+    rows = np.arange(M) if M * K * N <= 2 ** 31 else np.sort(np.random.default_rng(3).choice(M, size=24, replace=False))
+    expect = oracle.gemm_f32(A[rows], Wd, bias, 1.0, 1.0)
+    err = rel_l2(out[torch.from_numpy(rows).cuda()].cpu().numpy(), expect)
+    assert err <= TOL_DECLARED, err
+    if M * K * N <= 2 ** 27:
+        plain = tbn.lib.gemm_fxb(dA, neg, N, pos=pos, alpha=alpha, mode=tbn.MODE_TC_FP16X1)
+        for e in (-100, 100):
+            scaled = tbn.lib.gemm_fxb(dA * (2.0 ** e), neg, N, pos=pos, alpha=alpha, mode=tbn.MODE_TC_FP16X1)
+            tbn.lib.sync()
+            assert torch.equal(scaled * (2.0 ** -e), plain), e   # power-of-two scaling commutes exactly
+
+
 @pytest.mark.parametrize("M,K,N", [(256, 256, 256), (200, 300, 77), (1000, 512, 1000)])
 def test_x3_matches_exact_sum(tbn, M, K, N):
     """Three bf16 terms reproduce every fp32 activation exactly, so against an fp64 evaluation the
