@@ -44,7 +44,7 @@ def test_pure_host_helpers():
     assert handle.tbn_packed_dims(576, 6, C.byref(kp), C.byref(np_)) == 0
     assert (kp.value, np_.value) == (640, 8)
     assert handle.tbn_packed_dims(-1, 6, C.byref(kp), C.byref(np_)) == -1
-    assert handle.tbn_gemm_workspace_bytes(100, 70, capi.MODE_TC_BF16X2) == 2 * 128 * 128 * 2 + 160 * 128 * 256 * 4
+    assert handle.tbn_gemm_workspace_bytes(100, 70, capi.MODE_TC_BF16X2) == 2 * 128 * 128 * 2 + 160 * 128 * 256 * 4 + 256
     assert handle.tbn_gemm_workspace_bytes(100, 70, capi.MODE_SIMT) == 0
     assert handle.tbn_quant_pack_workspace_bytes(200, 37, 0) == 2 * 37 * 4
     assert handle.tbn_quant_pack_workspace_bytes(200, 37, 1) == 2 * 2 * 37 * 4
