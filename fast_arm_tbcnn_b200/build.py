@@ -28,7 +28,8 @@ def sources():
 
 
 def _headers():
-    return glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(INCLUDE_DIR, "*.h"))
+    return (glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.inc")) +
+            glob.glob(os.path.join(INCLUDE_DIR, "*.h")))
 
 
 def _newer(target, deps):

@@ -30,7 +30,11 @@ SIGNATURES = {
     "tbn_cuda_d2d": (_i32, [_vp, _vp, _sz, _vp]),
     "tbn_cuda_sync": (_i32, [_vp]),
     "tbn_cuda_launch_count": (_i64, []),
+    "tbn_cuda_set_wait_limit_ns": (_i32, [C.c_uint64]),
+    "tbn_cuda_selftest_wait_timeout": (_i32, [_vp]),
     "tbn_cuda_profile_enable": (_i32, [_i32]),
+    "tbn_gemm_plan": (_i32, [_i64, _i64, _i64, C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32)]),
+    "tbn_gemm_plan_override": (_i32, [_i32, _i32, _i32, _i32]),
     "tbn_cuda_set_fused_split": (_i32, [_i32]),
     "tbn_cuda_profile_read": (_i32, [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(_i64)]),
     "tbn_dense_pack_bytes": (_sz, [_i64, _i64]),
@@ -151,6 +155,18 @@ class _Lib:
         """0: always run the separate activation-split kernel; 1 (default): split inside the GEMM when N <= 256;
         2: split inside the GEMM whenever A's alignment allows."""
         check(self.h.tbn_cuda_set_fused_split(int(value)))
+
+    def gemm_plan(self, M, N, K):
+        """The library's per-shape choice for TBN_MODE_AUTO -> dict(kernel, bn, group_m, fused_split)."""
+        k, b, g, f = _i32(), _i32(), _i32(), _i32()
+        check(self.h.tbn_gemm_plan(M, N, K, C.byref(k), C.byref(b), C.byref(g), C.byref(f)))
+        return {"kernel": "cuda-core" if k.value else "tcgen05", "bn": b.value, "group_m": g.value, "fused_split": bool(f.value)}
+
+    def describe_choice(self, M, N, K):
+        return self.gemm_plan(M, N, K)
+
+    def gemm_plan_override(self, kernel=-1, bn=-1, group_m=-1, fused_split=-1):
+        check(self.h.tbn_gemm_plan_override(int(kernel), int(bn), int(group_m), int(fused_split)))
 
     def profile_enable(self, on=True):
         check(self.h.tbn_cuda_profile_enable(int(on)))

@@ -55,6 +55,7 @@ enum DeviceError : int {
     kErrWaitTmemEmpty = 5,  // MMA waited for the epilogue to drain the accumulator
     kErrPackWaitFull = 6,   // weight pack: consumers waited for a TMA tile
     kErrPackWaitEmpty = 7,  // weight pack: the producer waited for a free stage
+    kErrSelfTest = 8,       // tbn_cuda_selftest_wait_timeout: the wait that nothing completes
 };
 
 // ---- epilogue ----------------------------------------------------------------------

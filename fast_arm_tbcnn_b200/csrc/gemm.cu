@@ -31,6 +31,7 @@
 //                             naive reference loop); used for tiny problems and as a cross-check.
 #include <atomic>
 #include "gemm_tc.cuh"
+#include "plan.cuh"
 
 namespace tbn_cuda {
 namespace {
@@ -226,10 +227,10 @@ int32_t launch_split_f16(const float* d_a, int64_t M, int64_t K, int64_t lda, in
 }
 
 std::atomic<int> g_fused_split{1};
-// 0 never, 1 when the weights have a single column tile, 2 always.
-bool fused_split_wanted(int64_t N) {
+// 0 never, 1 as the per-shape plan says (by default: when the weights have a single column tile), 2 always.
+bool fused_split_wanted(const GemmPlan& plan) {
     const int v = g_fused_split.load(std::memory_order_relaxed);
-    return v == 2 || (v == 1 && N <= 256);
+    return v == 2 || (v == 1 && plan.fused_split != 0);
 }
 
 // Tensor-core path: split (or ternarise) A into the workspace, then the tcgen05 kernel.
@@ -255,7 +256,8 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     // Two-term products whose A rows can be read as float4 may skip the split pass: the GEMM's build warps read
     // the fp32 rows and split them in registers (same arithmetic, bit-identical operands) -- once per column
     // tile of the weights, so by default only when there is a single one.
-    const bool fused_split = !f16 && fused_split_wanted(N) && !ternarise_act && npass == 2 && !dense_w && K % 4 == 0 &&
+    const GemmPlan plan = gemm_plan(M, N, K);
+    const bool fused_split = !f16 && fused_split_wanted(plan) && !ternarise_act && npass == 2 && !dense_w && K % 4 == 0 &&
                              lda % 4 == 0 && reinterpret_cast<uintptr_t>(d_a) % 16 == 0;
     int32_t rc = TBN_SUCCESS;
     if (fused_split) {}
@@ -279,7 +281,7 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
                 "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(cr)));
 
-    const int bn = pick_bn(N);
+    const int bn = plan.bn;
     if (dense_w) {
         TBN_REQUIRE(reinterpret_cast<uintptr_t>(dense_w) % 16 == 0, TBN_INVALID_ARGUMENT,
                     "gemm: split dense weights must be 16-byte aligned");
@@ -300,6 +302,7 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.num_kb = static_cast<int>((K + tc::BK - 1) / tc::BK);  // k-blocks that hold real k; the operands are zero beyond K
     p.tiles_m = static_cast<int>(M_pad / tc::BM);
     p.tiles_n = static_cast<int>((N + bn - 1) / bn);
+    p.group_m = plan.group_m;
     p.c = d_c;
     p.ldc = ldc;
     p.ep = ep;
@@ -362,10 +365,10 @@ int32_t check_gemm_args(const float* d_a, int64_t M, int64_t K, int64_t lda, con
     return TBN_SUCCESS;
 }
 
-// Per-shape choice between the CUDA-core and the tensor-core kernel, from a measured sweep (CUDA events, B200):
-// the two meet around 256^3 (16-18 us each, launch bound); above it the tensor-core path wins, also for a handful
-// of rows (M = 1..8, K = N = 4096: 0.055 ms against 0.183 ms), because the CUDA-core kernel is FMA bound.
-bool prefer_simt(int64_t M, int64_t N, int64_t K) { return M * N * K <= (1LL << 24); }
+// Per-shape choice between the CUDA-core and the tensor-core kernel: the plan table (plan.cuh), measured with CUDA
+// events on a B200; classes without an entry use the rule "CUDA cores up to M*N*K = 2^24" (the two kernels meet
+// around 256^3, where both are launch bound; above it the tensor-core path wins, also for a handful of rows).
+bool prefer_simt(int64_t M, int64_t N, int64_t K) { return gemm_plan(M, N, K).kernel == 1 && M <= 65535LL * kSimtBM; }
 
 }  // namespace
 }  // namespace tbn_cuda

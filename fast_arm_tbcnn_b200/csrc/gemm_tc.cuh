@@ -137,10 +137,7 @@ constexpr int A_TILE_BYTES = BM * BK * 2;
 constexpr int kProducerWarp = 0, kMmaWarp = 1;
 constexpr int kBuildThreads = 256, kEpilogueThreads = 128;
 constexpr int kThreads = 64 + kBuildThreads + kEpilogueThreads;
-#ifndef TBN_GROUP_M
-#define TBN_GROUP_M 4
-#endif
-constexpr int kGroupM = TBN_GROUP_M;  // rasterisation: this many m-tiles share a sweep over n for L2 reuse
+constexpr int kDefaultGroupM = 4;  // rasterisation: this many m-tiles share a sweep over n for L2 reuse (Params::group_m)
 // Ring of packed-word tiles, each covering 2 k-blocks (128 k): 2 slots keep the GEMM fed; the convolutions,
 // whose k-blocks are short-lived, run 4 slots ahead.
 constexpr int kWordStagesGemm = 2, kWordStagesConv = 4;
@@ -206,6 +203,7 @@ struct Params {
     int M, N;
     int num_kb;            // K_pad / 64
     int tiles_m, tiles_n;
+    int group_m;           // rasterisation group (>= 1): m-tiles that share one sweep over the column tiles
     float* c;
     int64_t ldc;           // row-major output: row stride
     int out_nchw;          // 1: output element (m, n) lives at ((img*N + n)*OH*OW + pixel)
@@ -240,11 +238,11 @@ struct Params {
     ConvGeom conv;
 };
 
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-    const int group_size = kGroupM * tiles_n;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+    const int group_size = group_m * tiles_n;
     const int g = t / group_size;
-    const int first_m = g * kGroupM;
-    const int gm = min(tiles_m - first_m, kGroupM);
+    const int first_m = g * group_m;
+    const int gm = min(tiles_m - first_m, group_m);
     const int r = t - g * group_size;
     tm = first_m + r % gm;
     tn = r / gm;
@@ -347,7 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int tm, tn;
-                tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+                tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
                 // Patch mode: input coordinates of the patch's first pixel under tap (0, 0), and the tap state.
                 int pw0 = 0, ph0 = 0, pimg0 = 0, p_cb = 0, p_ti = 0, p_tj = 0;
                 if (PATCH) {
@@ -499,7 +497,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             if (pf_t < total_tiles) {
                 if (pf_kb == 0) {
                     int tn_unused;
-                    tile_coords(pf_t, p.tiles_m, p.tiles_n, pf_tm, tn_unused);
+                    tile_coords(pf_t, p.tiles_m, p.tiles_n, p.group_m, pf_tm, tn_unused);
                 }
                 const int k0 = pf_kb * BK + (r & 15) * 4;
                 const float* src = p.a_rows + (static_cast<int64_t>(pf_tm) * BM + (r >> 4)) * p.lda + k0;
@@ -524,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
         for (int t = blockIdx.x; kBuiltOperands && t < total_tiles && ok; t += gridDim.x) {
             int tm, tn;
-            tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
             // Window origin of this thread's output pixel (CONV modes).  Element-wise gather: one pixel per
             // thread (lanes = consecutive pixels).  Channels-last copy: four pixels per thread, rows
             // (r >> 3) + 32*j, and ONE 16-byte chunk r & 7, so that 8 lanes cover one pixel's 128 bytes and a
@@ -751,7 +749,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         const float ep_scale = p.amax_bits ? __fmul_rn(p.ep.scale, f16_scale_inv(__ldg(p.amax_bits))) : p.ep.scale;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
             int tm, tn;
-            tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
             const int sbuf = tile_iter & 1;
             const int64_t n0 = static_cast<int64_t>(tn) * BN;
             for (int j = e; j < BN; j += kEpiThreads) {
@@ -1033,8 +1031,10 @@ int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) 
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
+    tc::Params q = p;
+    if (q.group_m < 1) q.group_m = tc::kDefaultGroupM;
     profile_begin(kProfGemm, st);
-    kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, maps.out, p);
+    kernel<<<grid, tc::kThreads, C::SMEM_BYTES, st>>>(maps.a, maps.neg, maps.pos, maps.out, q);
     profile_end(kProfGemm, st);
     return launched(tc::is_conv_mode(AMODE) ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
 }

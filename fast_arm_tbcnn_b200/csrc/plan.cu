@@ -1,0 +1,122 @@
+// The per-shape plan table (see plan.cuh) and its C entry points.  Host code only.
+#include "plan.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <climits>
+
+#include "common.cuh"
+
+namespace tbn_cuda {
+namespace {
+
+struct TableLine {
+    int mi, ni, ki, kernel, bn, group_m, fused_split;
+};
+const TableLine kLines[] = {
+#include "gemm_plan_table.inc"
+    {-1, -1, -1, 0, 0, 0, 0}};
+
+struct Table {
+    GemmPlan e[kPlanClassesM][kPlanClassesN][kPlanClassesK];
+    bool has[kPlanClassesM][kPlanClassesN][kPlanClassesK] = {};
+    Table() {
+        for (const TableLine& l : kLines)
+            if (l.mi >= 0 && l.mi < kPlanClassesM && l.ni >= 0 && l.ni < kPlanClassesN && l.ki >= 0 && l.ki < kPlanClassesK) {
+                e[l.mi][l.ni][l.ki] = GemmPlan{l.kernel, l.bn, l.group_m, l.fused_split};
+                has[l.mi][l.ni][l.ki] = true;
+            }
+    }
+};
+const Table& table() {
+    static const Table t;
+    return t;
+}
+
+// Largest tile whose padding waste stays within ~12 % of the best candidate.
+int bn_by_padding(int64_t N) {
+    const int cand[3] = {256, 128, 64};
+    int64_t best = INT64_MAX;
+    for (int bn : cand) best = std::min<int64_t>(best, round_up(N, bn));
+    for (int bn : cand)
+        if (round_up(N, bn) * 8 <= best * 9) return bn;
+    return 64;
+}
+
+std::atomic<int> g_override[4] = {{-1}, {-1}, {-1}, {-1}};
+
+int class_of(int64_t v, const int64_t* bounds, int n) {
+    for (int i = 0; i < n - 1; ++i)
+        if (v <= bounds[i]) return i;
+    return n - 1;
+}
+
+}  // namespace
+
+int plan_class_m(int64_t M) {
+    static const int64_t b[] = {16, 128, 512, 2048, 8192};
+    return class_of(M, b, kPlanClassesM);
+}
+int plan_class_n(int64_t N) {
+    static const int64_t b[] = {64, 128, 256, 1024, 4096};
+    return class_of(N, b, kPlanClassesN);
+}
+int plan_class_k(int64_t K) {
+    static const int64_t b[] = {256, 1024, 4096};
+    return class_of(K, b, kPlanClassesK);
+}
+
+GemmPlan gemm_plan(int64_t M, int64_t N, int64_t K) {
+    // Built-in rule: the two kernels meet around 256^3, where both are launch bound; padding decides the tile.
+    GemmPlan p{M * N * K <= (1LL << 24) ? 1 : 0, bn_by_padding(N), 4, N <= 256 ? 1 : 0};
+    const Table& t = table();
+    const int mi = plan_class_m(M), ni = plan_class_n(N), ki = plan_class_k(K);
+    if (t.has[mi][ni][ki]) {
+        p = t.e[mi][ni][ki];
+        // The class was measured at one representative N: keep its tile only while this N pads no worse.
+        const int64_t best = round_up(N, bn_by_padding(N));
+        if (p.bn != 64 && p.bn != 128 && p.bn != 256) p.bn = bn_by_padding(N);
+        else if (round_up(N, p.bn) * 8 > best * 9) p.bn = bn_by_padding(N);
+        if (p.group_m < 1) p.group_m = 4;
+    }
+    const int o0 = g_override[0].load(std::memory_order_relaxed), o1 = g_override[1].load(std::memory_order_relaxed);
+    const int o2 = g_override[2].load(std::memory_order_relaxed), o3 = g_override[3].load(std::memory_order_relaxed);
+    if (o0 >= 0) p.kernel = o0;
+    if (o1 > 0) p.bn = o1;
+    if (o2 > 0) p.group_m = o2;
+    if (o3 >= 0) p.fused_split = o3;
+    return p;
+}
+
+}  // namespace tbn_cuda
+
+using namespace tbn_cuda;
+
+extern "C" {
+
+int32_t tbn_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t* kernel, int32_t* bn, int32_t* group_m, int32_t* fused_split) {
+    TBN_REQUIRE(M > 0 && N > 0 && K > 0, TBN_INVALID_SHAPE, "tbn_gemm_plan: M, N and K must be positive");
+    const GemmPlan p = gemm_plan(M, N, K);
+    if (kernel) *kernel = p.kernel;
+    if (bn) *bn = p.bn;
+    if (group_m) *group_m = p.group_m;
+    if (fused_split) *fused_split = p.fused_split;
+    return TBN_SUCCESS;
+}
+
+int32_t tbn_gemm_plan_override(int32_t kernel, int32_t bn, int32_t group_m, int32_t fused_split) {
+    TBN_REQUIRE(kernel >= -1 && kernel <= 1, TBN_INVALID_ARGUMENT, "tbn_gemm_plan_override: kernel must be -1, 0 or 1");
+    TBN_REQUIRE(bn == -1 || bn == 64 || bn == 128 || bn == 256, TBN_INVALID_ARGUMENT,
+                "tbn_gemm_plan_override: bn must be -1, 64, 128 or 256");
+    TBN_REQUIRE(group_m == -1 || (group_m >= 1 && group_m <= 1024), TBN_INVALID_ARGUMENT,
+                "tbn_gemm_plan_override: group_m must be -1 or 1..1024");
+    TBN_REQUIRE(fused_split >= -1 && fused_split <= 1, TBN_INVALID_ARGUMENT,
+                "tbn_gemm_plan_override: fused_split must be -1, 0 or 1");
+    g_override[0].store(kernel, std::memory_order_relaxed);
+    g_override[1].store(bn, std::memory_order_relaxed);
+    g_override[2].store(group_m, std::memory_order_relaxed);
+    g_override[3].store(fused_split, std::memory_order_relaxed);
+    return TBN_SUCCESS;
+}
+
+}  // extern "C"

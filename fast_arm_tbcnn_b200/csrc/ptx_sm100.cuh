@@ -89,8 +89,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  `err_word` is the library's device error word; a non-zero value there
-// (set by this or any other thread) makes every waiter give up.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+// (set by this or any other thread) makes every waiter give up.  The 64-bit word two ints further on holds the
+// limit in nanoseconds (tbn_cuda_set_wait_limit_ns; 2 s unless changed); it is read only on the slow path.
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;  // 2 s
+constexpr int kWaitLimitWordOffset = 2;                  // in ints from the error word (8-byte aligned)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_word, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
@@ -98,7 +100,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ffu) == 0) {
             if (*reinterpret_cast<volatile int*>(err_word) != 0) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t limit = *reinterpret_cast<volatile uint64_t*>(err_word + kWaitLimitWordOffset);
+            if (globaltimer_ns() - t0 > limit) {
                 atomicCAS(err_word, 0, code);
                 return false;
             }

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace tbn_cuda {
 
@@ -93,6 +94,19 @@ void profile_end(ProfileKind kind, cudaStream_t st) {
     g_open[kind] = nullptr;
 }
 
+namespace {
+// One thread waits on a barrier that nothing ever completes: the wait must run out by itself.
+__global__ void wait_selftest_kernel(int* err_word) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        const uint32_t b = ptx::smem_u32(&bar);
+        ptx::mbar_init(b, 1);
+        ptx::fence_barrier_init();
+        ptx::mbar_wait(b, 0, err_word, kErrSelfTest);
+    }
+}
+}  // namespace
+
 }  // namespace tbn_cuda
 
 using namespace tbn_cuda;
@@ -124,6 +138,7 @@ int32_t tbn_cuda_init(int32_t device) {
     s.sms = prop.multiProcessorCount;
     TBN_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&s.err_host), 64, cudaHostAllocMapped));
     std::memset(s.err_host, 0, 64);
+    *reinterpret_cast<volatile uint64_t*>(s.err_host + ptx::kWaitLimitWordOffset) = ptx::kDefaultWaitLimitNs;
     TBN_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.err_dev), s.err_host, 0));
     s.ready = true;
     return TBN_SUCCESS;
@@ -194,6 +209,25 @@ int32_t tbn_cuda_sync(void* stream) {
         }
     }
     return TBN_SUCCESS;
+}
+
+int32_t tbn_cuda_set_wait_limit_ns(uint64_t limit_ns) {
+    TBN_REQUIRE(limit_ns >= 1000 && limit_ns <= 60000000000ull, TBN_INVALID_ARGUMENT,
+                "tbn_cuda_set_wait_limit_ns: the limit must lie between 1 microsecond and 60 seconds");
+    int dev = 0;
+    TBN_CUDA_TRY(cudaGetDevice(&dev));
+    TBN_REQUIRE(dev >= 0 && dev < kMaxDevices && g_dev[dev].ready, TBN_RUNTIME_ERROR,
+                "tbn_cuda_init was not called on this device");
+    *reinterpret_cast<volatile uint64_t*>(g_dev[dev].err_host + ptx::kWaitLimitWordOffset) = limit_ns;
+    return TBN_SUCCESS;
+}
+
+
+int32_t tbn_cuda_selftest_wait_timeout(void* stream) {
+    int* w = device_error_word();
+    TBN_REQUIRE(w != nullptr, TBN_RUNTIME_ERROR, "tbn_cuda_init was not called on this device");
+    wait_selftest_kernel<<<1, 32, 0, as_stream(stream)>>>(w);
+    return launched("wait_selftest_kernel");
 }
 
 int64_t tbn_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -35,7 +35,7 @@ def build(force=False):
     inc = ["-I", os.path.join(HOST, "include"), "-I", os.path.join(ROOT, "include")]
     cuda_dir = os.path.dirname(cuda_lib)
     if force or _stale(LIB, srcs + hdrs + [cuda_lib]):
-        cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-o", LIB] + inc + srcs + [
+        cmd = [cxx, "-std=c++20", "-O2", "-fPIC", "-shared", "-Wall", "-o", LIB] + inc + srcs + [
             "-L", cuda_dir, "-ltbn_cuda", "-Wl,-rpath,$ORIGIN/../../fast_arm_tbcnn_b200/lib"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
@@ -43,7 +43,7 @@ def build(force=False):
             raise RuntimeError("g++ failed building " + LIB)
     driver = os.path.join(HOST, "tests", "run_graph.cpp")
     if force or _stale(RUN_GRAPH, [driver, LIB] + hdrs):
-        cmd = [cxx, "-std=c++17", "-O2", "-Wall", "-o", RUN_GRAPH] + inc + [driver, "-L", os.path.dirname(LIB), "-ltbn_host",
+        cmd = [cxx, "-std=c++20", "-O2", "-Wall", "-o", RUN_GRAPH] + inc + [driver, "-L", os.path.dirname(LIB), "-ltbn_host",
                "-L", cuda_dir, "-ltbn_cuda", "-Wl,-rpath,$ORIGIN/../lib", "-Wl,-rpath,$ORIGIN/../../fast_arm_tbcnn_b200/lib"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
@@ -58,7 +58,7 @@ def build_python_module(force=False, cxx="g++", inc=(), cuda_dir="", hdrs=()):
     import pybind11
     src = os.path.join(HOST, "python", "bindings.cpp")
     if force or _stale(PY_MODULE, [src, LIB] + list(hdrs)):
-        cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-o", PY_MODULE,
+        cmd = [cxx, "-std=c++20", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-o", PY_MODULE,
                "-I", sysconfig.get_paths()["include"], "-I", pybind11.get_include()] + list(inc) + [
                src, "-L", os.path.dirname(LIB), "-ltbn_host", "-L", cuda_dir, "-ltbn_cuda", "-Wl,-rpath,$ORIGIN",
                "-Wl,-rpath,$ORIGIN/../../fast_arm_tbcnn_b200/lib"]

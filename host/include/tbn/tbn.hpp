@@ -1,6 +1,7 @@
 // Umbrella header of the tbn:: API (reference: tbn-runtime/include/tbn/tbn.hpp).
 #pragma once
 #include "onnx_integration/onnx_parser.hpp"
+#include "gemm/packed_matrix.hpp"
 #include "operators/ops.hpp"
 #include "runtime/attribute.hpp"
 #include "runtime/model.hpp"

@@ -6,6 +6,7 @@
 //   run_graph --dump-onnx <model.onnx>     canonical text listing of the loaded graph (no GPU work)
 // Also exercises the error paths a reference user relies on (exception types), printing "errors ok".
 #include <algorithm>
+#include <array>
 #include <cstdint>
 #include <chrono>
 #include <cstdio>
@@ -139,9 +140,81 @@ static int error_paths() {
     return bad;
 }
 
+// Known-answer vectors of the packed layouts (host types only, no GPU): the three vectors the oracle is pinned on.
+static int packed_layout() {
+    using namespace tbn;
+    int bad = 0;
+    std::vector<std::int8_t> w(128 * 8, 1);
+    w[37 * 8 + 3] = -1;
+    w[64 * 8 + 0] = -1;
+    BinaryMatrix b = BinaryMatrix::pack(w, 128, 8);
+    std::vector<std::uint32_t> words(b.view().bits.size() / 4);
+    std::memcpy(words.data(), b.view().bits.data(), b.view().bits.size());
+    for (size_t i = 0; i < words.size(); ++i)
+        if (words[i] != (i == 13 ? 0x20u : (i == 2 ? 0x1u : 0u))) ++bad;
+    std::vector<float> a(8 * 64, 0.0f);
+    a[1 * 64 + 9] = 0.5f; a[2 * 64 + 33] = -0.5f; a[0] = 0.1f; a[1] = -0.1f;
+    TernaryMatrix t = TernaryMatrix::pack_from_float(a.data(), 8, 64);
+    std::vector<std::uint32_t> pos(t.view().positive.size() / 4), neg(pos.size());
+    std::memcpy(pos.data(), t.view().positive.data(), t.view().positive.size());
+    std::memcpy(neg.data(), t.view().negative.data(), t.view().negative.size());
+    for (size_t i = 0; i < pos.size(); ++i) {
+        if (pos[i] != (i == 2 ? 0x200u : 0u)) ++bad;
+        if (neg[i] != (i == 5 ? 0x2u : 0u)) ++bad;
+    }
+    try { (void)BinaryMatrix::pack(std::vector<std::int8_t>(60 * 8, 1), 60, 8); ++bad; } catch (const std::invalid_argument&) {}
+    try { (void)BinaryMatrix::pack(std::vector<std::int8_t>(64 * 8, 0), 64, 8); ++bad; } catch (const std::invalid_argument&) {}
+    try { (void)TernaryMatrix::pack(std::vector<std::int8_t>(8 * 64, 2), 8, 64); ++bad; } catch (const std::invalid_argument&) {}
+    PackedBinaryWeights pw = PackedBinaryWeights::from_int8(std::vector<std::int8_t>(70 * 5, -1), 70, 5, TilingParams::default_128x128());
+    if (!pw.valid() || pw.b_packed.rows() != 128 || pw.b_packed.cols() != 8 || pw.original_n != 5) ++bad;
+    std::printf(bad ? "packed layout FAILED (%d)\n" : "packed layout ok\n", bad);
+    return bad;
+}
+
+// Operators on pre-packed operands (GPU): both must equal qlinear_matmul_binary on the unpacked operands, bit for bit.
+static int prepacked() {
+    using namespace tbn;
+    int bad = 0;
+    const TilingParams tp = TilingParams::default_128x128();
+    std::uint64_t s = 88172645463325252ull;
+    auto rnd = [&]() { s ^= s << 13; s ^= s >> 7; s ^= s << 17; return s; };
+    for (const auto& dims : std::vector<std::array<int, 3>>{{40, 200, 24}, {130, 576, 128}, {16, 64, 8}, {33, 300, 20}}) {
+        const int M = dims[0], K = dims[1], N = dims[2];
+        const int Kp = (K + 127) / 128 * 128, Np = (N + 7) / 8 * 8, Mp = (M + 15) / 16 * 16;
+        std::vector<float> a(static_cast<size_t>(M) * K);
+        for (auto& v : a) v = static_cast<float>(static_cast<int>(rnd() % 2001) - 1000) / 2000.0f;   // [-0.5, 0.5]
+        std::vector<BinaryWeight> bq(static_cast<size_t>(K) * N);
+        for (auto& v : bq) v = static_cast<BinaryWeight>(rnd() & 1);
+        Tensor A = make_tensor(Shape{M, K}, a), B = make_tensor(Shape{K, N}, bq);
+        Tensor expect = qlinear_matmul_binary(A, B, 0.37f, tp);
+        // pad K to 128 and N to 8 with +1, as the reference's callers do (quantized_gemm_neon.cpp:199-214)
+        std::vector<std::int8_t> bi(static_cast<size_t>(Kp) * Np, 1);
+        for (int k = 0; k < K; ++k)
+            for (int n = 0; n < N; ++n) bi[static_cast<size_t>(k) * Np + n] = bq[static_cast<size_t>(k) * N + n] ? 1 : -1;
+        BinaryMatrix Bp = BinaryMatrix::pack(bi, Kp, Np);
+        Tensor got = qlinear_matmul_binary_blocked_packed(A, Bp, N, 0.37f, tp);
+        if (std::memcmp(got.typed_data<float>(), expect.typed_data<float>(), static_cast<size_t>(M) * N * 4) != 0) ++bad;
+        std::vector<float> ap(static_cast<size_t>(Mp) * Kp, 0.0f);
+        for (int m = 0; m < M; ++m) std::memcpy(&ap[static_cast<size_t>(m) * Kp], &a[static_cast<size_t>(m) * K], static_cast<size_t>(K) * 4);
+        TernaryMatrix Ap = TernaryMatrix::pack_from_float(ap.data(), Mp, Kp);
+        Tensor got2 = qlinear_matmul_binary_blocked_prepacked(Ap, Bp, M, N, 0.37f, tp);
+        if (std::memcmp(got2.typed_data<float>(), expect.typed_data<float>(), static_cast<size_t>(M) * N * 4) != 0) ++bad;
+        // weights padded only to 64 rows (PackedBinaryWeights::from_int8): K = 200 -> 256 plane rows vs 256: same; K = 64 -> 64 vs 128
+        std::vector<std::int8_t> braw(static_cast<size_t>(K) * N);
+        for (size_t i = 0; i < braw.size(); ++i) braw[i] = bq[i] ? 1 : -1;
+        PackedBinaryWeights pw = PackedBinaryWeights::from_int8(braw, K, N, tp);
+        Tensor got3 = qlinear_matmul_binary_blocked_packed(A, pw.b_packed, N, 0.37f, tp);
+        if (std::memcmp(got3.typed_data<float>(), expect.typed_data<float>(), static_cast<size_t>(M) * N * 4) != 0) ++bad;
+    }
+    std::printf(bad ? "prepacked FAILED (%d)\n" : "prepacked ok\n", bad);
+    return bad;
+}
+
 int main(int argc, char** argv) {
     try {
         if (argc == 2 && std::strcmp(argv[1], "--errors") == 0) return error_paths();
+        if (argc == 2 && std::strcmp(argv[1], "--packed-layout") == 0) return packed_layout();
+        if (argc == 2 && std::strcmp(argv[1], "--prepacked") == 0) return prepacked();
         if (argc == 3 && std::strcmp(argv[1], "--dump-onnx") == 0) return dump_onnx(argv[2]);
         if (argc >= 8 && std::strcmp(argv[1], "--onnx") == 0) return run_onnx(argc, argv);
         if (argc < 8) {

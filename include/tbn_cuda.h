@@ -92,6 +92,17 @@ int32_t tbn_cuda_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream)
 /* Waits for `stream` and reports any device-side error recorded by the kernels
  * (TBN_CUDA_TIMEOUT when a bounded wait expired). */
 int32_t tbn_cuda_sync(void* stream);
+/* Every wait inside the kernels (on a shared-memory barrier that a TMA copy, an MMA or another warp completes) is
+ * bounded: when it has lasted longer than the limit the kernel records a code, every other waiter of the device
+ * gives up as well, the kernel frees its tensor memory and returns, and the next tbn_cuda_sync reports
+ * TBN_CUDA_TIMEOUT; the context stays usable.  Default 2 s per device; settable between 1 us and 60 s (takes
+ * effect for waits that start polling after the call). */
+int32_t tbn_cuda_set_wait_limit_ns(uint64_t limit_ns);
+/* Launches a one-warp kernel whose only thread waits on a barrier that nothing completes: the wait runs out after
+ * the limit above and the following tbn_cuda_sync returns TBN_CUDA_TIMEOUT.  Lets a host check, at start-up and
+ * without any fault, that a stuck kernel would be reported instead of hanging the stream.  (No counterpart in the
+ * reference.) */
+int32_t tbn_cuda_selftest_wait_timeout(void* stream);
 /* Number of kernels this library has launched so far in this process. */
 int64_t tbn_cuda_launch_count(void);
 /* Per-kernel device timing for benchmarks: while enabled, the GEMM entry points bracket their
@@ -109,6 +120,20 @@ int32_t tbn_cuda_profile_read(double* gemm_ms, int64_t* gemm_launches, double* s
  * 23.2 ms fused against 11.4 + 0.35 ms separate).  value 1 (default): fuse when N <= 256; 0: never; 2: always.
  * All three give bit-identical results.  Process-wide; not meant to be flipped while calls are in flight. */
 int32_t tbn_cuda_set_fused_split(int32_t value);
+
+/* Per-shape kernel choice of TBN_MODE_AUTO.  Stands in for TilingParams / auto_tune_gemm of the reference
+ * (GeMM/05-final/GeMM.hpp:16-43, tbn-runtime/src/operators/gemm.cpp:524-536): instead of tile sizes handed in by
+ * the caller, a table measured on the GPU and compiled into the library maps the class of (M, N, K) to
+ *   kernel       0 = tcgen05 tensor-core kernel, 1 = CUDA-core add/subtract-by-sign kernel
+ *   bn           column tile of the tensor-core kernel (64 / 128 / 256)
+ *   group_m      rasterisation group: m-tiles that share one sweep over the column tiles (L2 reuse)
+ *   fused_split  1 = the kernel splits the fp32 activation rows itself instead of a separate pass
+ * tbn_gemm_plan reports the choice for a shape (a host may store it beside its packed weights; any out pointer
+ * may be NULL).  tbn_gemm_plan_override forces fields for every following call of the process (-1 = as the table
+ * says); it is what the tuner (python -m fast_arm_tbcnn_b200.tune) uses to measure the variants. */
+int32_t tbn_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t* kernel, int32_t* bn, int32_t* group_m,
+                      int32_t* fused_split);
+int32_t tbn_gemm_plan_override(int32_t kernel, int32_t bn, int32_t group_m, int32_t fused_split);
 
 /* Padded dims of the packed layouts: K_pad = ceil128(K), N_pad = ceil8(N)
  * (PaddedDimensions, tbn-runtime/src/operators/quantized_gemm_neon.cpp:38-58). */

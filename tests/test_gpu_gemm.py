@@ -396,3 +396,35 @@ def test_full_size_linearity_and_sampled_rows(tbn, oracle):
     tbn.lib.sync()
     assert torch.equal(out2[128:], out[128:])
     assert torch.equal(out2[:128], -out[:128])
+
+
+def test_bounded_wait_runs_out_and_is_reported(tbn):
+    """A wait that nothing completes ends by itself after the (here: 5 ms) limit, tbn_cuda_sync reports
+    TBN_CUDA_TIMEOUT (-101), and the device keeps working: an ordinary GEMM right after it is correct.  Nothing
+    traps or faults; the 2 s default is restored."""
+    import time
+    import torch
+    h = tbn.lib.h
+    tbn.lib.sync()
+    try:
+        tbn.check(h.tbn_cuda_set_wait_limit_ns(5_000_000))
+        t0 = time.perf_counter()
+        tbn.check(h.tbn_cuda_selftest_wait_timeout(None))
+        with pytest.raises(tbn.TbnError) as e:
+            tbn.lib.sync()
+        waited = time.perf_counter() - t0
+        assert e.value.status == -101 and "bounded device-side wait expired (code 8)" in str(e.value)
+        assert 0.004 <= waited < 1.0, waited
+    finally:
+        tbn.check(h.tbn_cuda_set_wait_limit_ns(2_000_000_000))
+    tbn.lib.sync()   # the error was consumed: clean again
+    g = torch.Generator(device="cuda").manual_seed(1)
+    A = torch.randn((300, 512), generator=g, device="cuda")
+    W = torch.randn((512, 256), generator=g, device="cuda")
+    words, _ = tbn.lib.quant_pack_binary(W, want_alpha=False)
+    out = tbn.lib.gemm_fxb(A, words, 256, mode=tbn.MODE_TC_BF16X3)
+    tbn.lib.sync()
+    exact = A.double() @ torch.where(W > 0, 1.0, -1.0).double()
+    assert float((out.double() - exact).norm() / exact.norm()) <= 5e-6
+    with pytest.raises(tbn.TbnError):
+        tbn.check(h.tbn_cuda_set_wait_limit_ns(10))

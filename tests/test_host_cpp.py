@@ -26,7 +26,10 @@ def test_host_layer_builds_and_exports_reference_names(host):
                  "tbn::load_onnx_model_from_buffer(", "tbn::load_model(", "tbn::load_model_from_buffer(", "tbn::get_version(",
                  "tbn::OnnxParser::parse_from_file(", "tbn::OnnxParser::parse_from_buffer(", "tbn::OnnxParser::get_graph(",
                  "tbn::TBNModel::Session::set_input(", "tbn::TBNModel::Session::run(",
-                 "tbn::TBNModel::Session::get_output(", "tbn::Tensor::to_device("]:
+                 "tbn::TBNModel::Session::get_output(", "tbn::Tensor::to_device(",
+                 "tbn::qlinear_matmul_binary_blocked_packed(", "tbn::qlinear_matmul_binary_blocked_prepacked(",
+                 "tbn::BinaryMatrix::pack(", "tbn::TernaryMatrix::pack_from_float(", "tbn::TernaryMatrix::pack(",
+                 "tbn::PackedBinaryWeights::from_int8("]:
         assert name in out, name
     assert os.access(driver, os.X_OK)
 
@@ -181,3 +184,18 @@ def test_conv_output_that_is_also_a_graph_output(host, oracle, tmp_path):
     assert rel_l2(sess.get_output("pre").cpu().numpy(), keep["pre"]) <= 1e-5
     assert rel_l2(sess.get_output("output").cpu().numpy(), keep["output"]) <= 1e-5
     assert float(sess.get_output("pre").min()) < 0.0   # really the pre-activation values
+
+
+def test_packed_matrix_types_layout_known_answers(host):
+    """BinaryMatrix / TernaryMatrix / PackedBinaryWeights of the C++ layer (host types, no GPU needed): the layout
+    known-answer vectors the oracle is pinned on, and the reference's std::invalid_argument checks."""
+    proc = subprocess.run([host[1], "--packed-layout"], capture_output=True, text=True)
+    assert proc.returncode == 0 and "packed layout ok" in proc.stdout, proc.stdout + proc.stderr
+
+
+@pytest.mark.gpu
+def test_operators_on_prepacked_operands(host):
+    """qlinear_matmul_binary_blocked_packed / _blocked_prepacked == qlinear_matmul_binary (itself bit-equal to the
+    oracle) on the same operands, including weights padded to 64 instead of 128 rows."""
+    proc = subprocess.run([host[1], "--prepacked"], capture_output=True, text=True)
+    assert proc.returncode == 0 and "prepacked ok" in proc.stdout, proc.stdout + proc.stderr
