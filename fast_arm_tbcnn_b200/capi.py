@@ -35,6 +35,7 @@ SIGNATURES = {
     "tbn_cuda_profile_enable": (_i32, [_i32]),
     "tbn_gemm_plan": (_i32, [_i64, _i64, _i64, C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32)]),
     "tbn_gemm_plan_override": (_i32, [_i32, _i32, _i32, _i32]),
+    "tbn_gemm_plan_bn": (_i32, [_i64, _i64, _i32]),
     "tbn_cuda_set_fused_split": (_i32, [_i32]),
     "tbn_cuda_profile_read": (_i32, [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(_i64)]),
     "tbn_dense_pack_bytes": (_sz, [_i64, _i64]),
@@ -161,6 +162,9 @@ class _Lib:
         k, b, g, f = _i32(), _i32(), _i32(), _i32()
         check(self.h.tbn_gemm_plan(M, N, K, C.byref(k), C.byref(b), C.byref(g), C.byref(f)))
         return {"kernel": "cuda-core" if k.value else "tcgen05", "bn": b.value, "group_m": g.value, "fused_split": bool(f.value)}
+
+    def wave_model_bn(self, M, N, preferred):
+        return int(self.h.tbn_gemm_plan_bn(M, N, preferred))
 
     def describe_choice(self, M, N, K):
         return self.gemm_plan(M, N, K)

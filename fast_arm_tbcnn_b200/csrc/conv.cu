@@ -8,6 +8,7 @@
 // K = C*kh*kw in the reference's (c, i, j) order, N = output channels; the weights are packed from
 // [M_out, C*kh*kw] with TBN_LAYOUT_NK, which yields the same words as the Session's transpose + pack.
 #include "gemm_tc.cuh"
+#include "plan.cuh"
 
 namespace tbn_cuda {
 namespace {
@@ -358,7 +359,7 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     }
     if (rc) return rc;
 
-    const int bn = pick_bn(N);
+    const int bn = gemm_plan(M, N, K).bn;  // the class's measured column tile, adjusted to this shape's tile count
     TensorMaps maps;
     if (a.dense_w) {
         rc = make_split_map(encode, a.dense_w, K_pad, N_pad, 2, bn, &maps.neg);

@@ -43,6 +43,27 @@ int bn_by_padding(int64_t N) {
     return 64;
 }
 
+// Column tile by a wave model: the persistent kernel runs ceil(tiles / SMs) waves and a tile costs about bn + 48
+// (operand unpacking and MMA time grow with bn; the +48 stands for the per-tile fixed part).  `preferred` (the
+// class's measured tile) wins when it is within 10 % of the model's best.  Matches the measured sweep on shapes
+// between the class representatives (e.g. 3136 x 512: 128, not the 256 measured at N = 1024).
+int bn_by_waves(int64_t M, int64_t N, int preferred) {
+    const int64_t sms = std::max(sm_count(), 1) > 1 ? sm_count() : 148;
+    const int64_t tiles_m = (M + 127) / 128;
+    const int cand[3] = {256, 128, 64};
+    int64_t cost[3], best = INT64_MAX;
+    for (int i = 0; i < 3; ++i) {
+        const int64_t tiles = tiles_m * ((N + cand[i] - 1) / cand[i]);
+        cost[i] = ((tiles + sms - 1) / sms) * (cand[i] + 48);
+        best = std::min(best, cost[i]);
+    }
+    for (int i = 0; i < 3; ++i)
+        if (cand[i] == preferred && cost[i] * 10 <= best * 11) return preferred;
+    for (int i = 0; i < 3; ++i)
+        if (cost[i] == best) return cand[i];
+    return 64;
+}
+
 std::atomic<int> g_override[4] = {{-1}, {-1}, {-1}, {-1}};
 
 int class_of(int64_t v, const int64_t* bounds, int n) {
@@ -73,12 +94,10 @@ GemmPlan gemm_plan(int64_t M, int64_t N, int64_t K) {
     const int mi = plan_class_m(M), ni = plan_class_n(N), ki = plan_class_k(K);
     if (t.has[mi][ni][ki]) {
         p = t.e[mi][ni][ki];
-        // The class was measured at one representative N: keep its tile only while this N pads no worse.
-        const int64_t best = round_up(N, bn_by_padding(N));
-        if (p.bn != 64 && p.bn != 128 && p.bn != 256) p.bn = bn_by_padding(N);
-        else if (round_up(N, p.bn) * 8 > best * 9) p.bn = bn_by_padding(N);
         if (p.group_m < 1) p.group_m = 4;
     }
+    // The class was measured at one representative shape: its tile is kept only while the wave model agrees.
+    p.bn = bn_by_waves(M, N, p.bn);
     const int o0 = g_override[0].load(std::memory_order_relaxed), o1 = g_override[1].load(std::memory_order_relaxed);
     const int o2 = g_override[2].load(std::memory_order_relaxed), o3 = g_override[3].load(std::memory_order_relaxed);
     if (o0 >= 0) p.kernel = o0;
@@ -102,6 +121,10 @@ int32_t tbn_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t* kernel, int32_t*
     if (group_m) *group_m = p.group_m;
     if (fused_split) *fused_split = p.fused_split;
     return TBN_SUCCESS;
+}
+
+int32_t tbn_gemm_plan_bn(int64_t M, int64_t N, int32_t preferred) {
+    return bn_by_waves(M > 0 ? M : 1, N > 0 ? N : 1, preferred);
 }
 
 int32_t tbn_gemm_plan_override(int32_t kernel, int32_t bn, int32_t group_m, int32_t fused_split) {

@@ -13,9 +13,11 @@ import argparse
 import os
 import sys
 
-M_REPS = [8, 64, 256, 1024, 4096, 16384]
+# One representative per class: the class's upper bound (the largest class: 16384), so that a choice is made for
+# the heaviest shape it will serve.
+M_REPS = [16, 128, 512, 2048, 8192, 16384]
 N_REPS = [64, 128, 256, 1024, 4096, 16384]
-K_REPS = [128, 576, 4096, 16384]
+K_REPS = [256, 1024, 4096, 16384]
 M_CLASSES = ["<=16", "<=128", "<=512", "<=2048", "<=8192", ">8192"]
 N_CLASSES = ["<=64", "<=128", "<=256", "<=1024", "<=4096", ">4096"]
 K_CLASSES = ["<=256", "<=1024", "<=4096", ">4096"]
@@ -86,6 +88,11 @@ def main():
             for group in (1, 2, 8, 16):
                 timings[("tcgen05", best[1], group, best[3])] = time_variant(M, N, K, 0, best[1], group, best[3])
         best = min(timings, key=lambda k: timings[k])
+        # Run-to-run noise is a few per cent: the default rasterisation group (4) stays unless another one is
+        # more than 2 % faster.
+        dflt = (best[0], best[1], 4, best[3])
+        if best[0] == "tcgen05" and best[2] != 4 and dflt in timings and timings[dflt] <= timings[best] * 1.02:
+            best = dflt
         return best, timings
 
     lines, report = [], ["| class M | class N | class K | shape | chosen | ms | all variants (ms) |", "|---|---|---|---|---|---|---|"]
@@ -132,7 +139,7 @@ def main():
             continue
         best, timings = sweep(M, N, K)
         kernel, bn, group, fused = ent
-        bn = min(bn, max(64, (N + 63) // 64 * 64))
+        bn = L.wave_model_bn(M, N, bn)   # the adjustment the library applies to the class's tile
         mine = time_variant(M, N, K, kernel, bn if kernel == 0 else -1, group if kernel == 0 else -1, fused if kernel == 0 else -1)
         name = "cuda-core" if kernel else f"tcgen05 bn{bn} g{group}" + (" fused" if fused else "")
         report.append(f"| {M}x{N}x{K} | {name} | {mine:.4f} | {best[0]} bn{best[1]} g{best[2]}{' fused' if best[3] else ''} | "

@@ -134,6 +134,10 @@ int32_t tbn_cuda_set_fused_split(int32_t value);
 int32_t tbn_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t* kernel, int32_t* bn, int32_t* group_m,
                       int32_t* fused_split);
 int32_t tbn_gemm_plan_override(int32_t kernel, int32_t bn, int32_t group_m, int32_t fused_split);
+/* The column tile the library derives for an (M, N) from a class's tile `preferred`: a class is measured at one
+ * representative shape, and a shape whose tile count fills the SMs differently takes the tile a wave model
+ * prefers (returns 64, 128 or 256). */
+int32_t tbn_gemm_plan_bn(int64_t M, int64_t N, int32_t preferred);
 
 /* Padded dims of the packed layouts: K_pad = ceil128(K), N_pad = ceil8(N)
  * (PaddedDimensions, tbn-runtime/src/operators/quantized_gemm_neon.cpp:38-58). */

@@ -48,3 +48,30 @@ def test_pure_host_helpers():
     assert handle.tbn_gemm_workspace_bytes(100, 70, capi.MODE_SIMT) == 0
     assert handle.tbn_quant_pack_workspace_bytes(200, 37, 0) == 2 * 37 * 4
     assert handle.tbn_quant_pack_workspace_bytes(200, 37, 1) == 2 * 2 * 37 * 4
+
+
+def test_gemm_plan_table_choices():
+    """The compiled-in per-shape table (host code, no GPU): the benchmark shapes get the tensor-core kernel with
+    the column tile the sweep and the wave model give, tiny products the CUDA-core kernel, and an override is
+    reported back and can be cleared."""
+    from fast_arm_tbcnn_b200 import capi
+    L = capi.lib
+    capi.load()
+    assert L.gemm_plan(16384, 16384, 16384)["kernel"] == "tcgen05" and L.gemm_plan(16384, 16384, 16384)["bn"] == 256
+    assert L.gemm_plan(4096, 11008, 4096)["bn"] == 256
+    assert L.gemm_plan(4096, 4096, 4096) == dict(L.gemm_plan(4096, 4096, 4096), kernel="tcgen05", bn=256, fused_split=False)
+    assert L.gemm_plan(3136, 512, 2304)["bn"] == 128      # 25 x 2 tiles of 256 would leave two thirds of the SMs idle
+    assert L.gemm_plan(8, 4096, 4096)["bn"] == 64
+    assert L.gemm_plan(1, 10, 256)["kernel"] == "cuda-core"
+    assert L.gemm_plan(200704, 64, 576)["fused_split"] is True
+    assert L.gemm_plan(16384, 16384, 16384)["fused_split"] is False
+    try:
+        L.gemm_plan_override(kernel=1, bn=64, group_m=7, fused_split=0)
+        assert L.gemm_plan(16384, 16384, 16384) == {"kernel": "cuda-core", "bn": 64, "group_m": 7, "fused_split": False}
+    finally:
+        L.gemm_plan_override()
+    assert L.gemm_plan(16384, 16384, 16384)["kernel"] == "tcgen05"
+    import pytest
+    with pytest.raises(capi.TbnError):
+        L.gemm_plan_override(bn=100)
+    assert L.wave_model_bn(8192, 256, 256) == 128 and L.wave_model_bn(16384, 16384, 256) == 256
