@@ -57,6 +57,49 @@ __global__ void pool2d_kernel(int kind, const float* __restrict__ x, int64_t NC,
     }
 }
 
+// 3 x 3 / stride 2 / pad 1 max pool (the stem pool of the ResNet graphs), W % 4 == 0: one warp per output row of one
+// plane.  Each lane loads four input columns of the three input rows as float4 (fully coalesced; neighbouring
+// warps of the block share the rows through L1/L2), takes the column to its left from the lane before it, and
+// forms two outputs with the comparisons in the same tap order (i, then j) and with the same `best > v ? best : v`
+// rule as the general kernel -- bit-identical to it, NaNs included.  HBM bound: every input row is read from DRAM
+// once, the output written once.
+__global__ void __launch_bounds__(256) maxpool_3x3s2p1_kernel(const float* __restrict__ x, int64_t rows_total, int H, int W,
+                                                              int OH, int OW, float* __restrict__ y) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (plane, oh)
+    if (row >= rows_total) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t plane = row / OH;
+    const int oh = static_cast<int>(row - plane * OH);
+    const float* in = x + plane * H * W;
+    float* out = y + plane * OH * OW + static_cast<int64_t>(oh) * OW;
+    for (int c0 = 0; c0 < W; c0 += 128) {
+        const int col = c0 + 4 * lane;  // this lane's four input columns; outputs ow0 = col / 2 and ow0 + 1
+        float best0 = -INFINITY, best1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const int ih = 2 * oh - 1 + i;
+            const bool row_in = ih >= 0 && ih < H;  // warp-uniform
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row_in && col < W) v = __ldg(reinterpret_cast<const float4*>(in + static_cast<int64_t>(ih) * W + col));
+            float left = __shfl_up_sync(0xffffffffu, v.w, 1);
+            if (lane == 0 && row_in && c0 > 0) left = __ldg(in + static_cast<int64_t>(ih) * W + c0 - 1);
+            if (!row_in) continue;
+            // output ow0: columns col-1, col, col+1; output ow0+1: columns col+1, col+2, col+3 (all < W when col < W)
+            if (col > 0) best0 = best0 > left ? best0 : left;
+            best0 = best0 > v.x ? best0 : v.x;
+            best0 = best0 > v.y ? best0 : v.y;
+            best1 = best1 > v.y ? best1 : v.y;
+            best1 = best1 > v.z ? best1 : v.z;
+            best1 = best1 > v.w ? best1 : v.w;
+        }
+        const int ow0 = col >> 1;
+        if (col < W) {
+            if (ow0 + 1 < OW) *reinterpret_cast<float2*>(out + ow0) = make_float2(best0, best1);
+            else if (ow0 < OW) out[ow0] = best0;
+        }
+    }
+}
+
 // One warp per (n, c) plane.
 __global__ void global_avgpool_kernel(const float* __restrict__ x, int64_t NC, int64_t HW, float* __restrict__ y) {
     const int64_t plane = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -151,6 +194,14 @@ int32_t tbn_pool2d(int32_t kind, const float* d_x, int64_t N, int64_t C, int64_t
     const int64_t OH = ceil_mode ? (H + 2 * ph - kh + sh - 1) / sh + 1 : (H + 2 * ph - kh) / sh + 1;
     const int64_t OW = ceil_mode ? (W + 2 * pw - kw + sw - 1) / sw + 1 : (W + 2 * pw - kw) / sw + 1;
     TBN_REQUIRE(OH > 0 && OW > 0 && H < (1 << 30) && W < (1 << 30), TBN_INVALID_SHAPE, "tbn_pool2d: empty output");
+    if (kind == 0 && kh == 3 && kw == 3 && sh == 2 && sw == 2 && ph == 1 && pw == 1 && !ceil_mode && W % 4 == 0 &&
+        reinterpret_cast<uintptr_t>(d_x) % 16 == 0 && reinterpret_cast<uintptr_t>(d_y) % 8 == 0 && OW % 2 == 0 &&
+        N * C * OH < (1LL << 33)) {
+        const int64_t rows = N * C * OH;
+        maxpool_3x3s2p1_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, as_stream(stream)>>>(
+            d_x, rows, static_cast<int>(H), static_cast<int>(W), static_cast<int>(OH), static_cast<int>(OW), d_y);
+        return launched("maxpool_3x3s2p1_kernel");
+    }
     pool2d_kernel<<<grid_for(N * C * OH * OW), 256, 0, as_stream(stream)>>>(
         kind, d_x, N * C, static_cast<int>(H), static_cast<int>(W), static_cast<int>(OH), static_cast<int>(OW), kh, kw,
         sh, sw, ph, pw, count_include_pad, d_y);

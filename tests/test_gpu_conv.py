@@ -245,6 +245,24 @@ def test_glue_operators(tbn, oracle):
     assert np.array_equal(tbn.lib.add(d, torch.from_numpy(y).cuda(), relu=True).cpu().numpy(), np.maximum(x + y, 0))
 
 
+@pytest.mark.parametrize("shape", [(2, 5, 20, 24), (1, 3, 112, 112), (3, 2, 7, 132), (1, 1, 1, 4), (2, 2, 9, 260)])
+def test_stem_maxpool_fast_kernel_is_bit_exact(tbn, oracle, shape):
+    """3 x 3 / stride 2 / pad 1 max pooling with W % 4 == 0 runs a row-per-warp kernel: bit-identical to the
+    reference's maxpool2d (pooling.cpp:10-80), NaN and infinite inputs included (same tap order, same compare)."""
+    import torch
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    flat = x.reshape(-1)
+    idx = rng.choice(flat.size, size=max(1, flat.size // 50), replace=False)
+    flat[idx] = np.resize(np.array([np.nan, np.inf, -np.inf, 0.0, -0.0], dtype=np.float32), idx.size)
+    got = tbn.lib.pool2d(0, torch.from_numpy(x).cuda(), (3, 3, 2, 2, 1, 1)).cpu().numpy()
+    tbn.lib.sync()
+    expect = oracle.pool2d(0, x, (3, 3, 2, 2, 1, 1))
+    assert got.shape == expect.shape
+    assert np.array_equal(got, expect, equal_nan=True)
+    assert np.array_equal(np.signbit(got), np.signbit(expect))
+
+
 @pytest.mark.parametrize("batch", [1, 7, 256])
 def test_lenet_session_float_binary(tbn, oracle, batch):
     """The simple_cnn-shaped binary CNN: every layer within 1e-5 of the reference's float path on the
