@@ -7,6 +7,9 @@
 // Session::execute_conv (tbn/runtime/model.hpp:375-559).  GEMM view: M = N_img*OH*OW output pixels,
 // K = C*kh*kw in the reference's (c, i, j) order, N = output channels; the weights are packed from
 // [M_out, C*kh*kw] with TBN_LAYOUT_NK, which yields the same words as the Session's transpose + pack.
+#include <cstdlib>
+
+#include "conv_rows.cuh"
 #include "gemm_tc.cuh"
 #include "plan.cuh"
 
@@ -471,6 +474,91 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
         const int64_t pbw = std::min<int64_t>(OW, tc::BM);
         const int64_t pbh = std::min<int64_t>(OH, tc::BM / pbw);
         const int64_t pbi = (pbw == OW && pbh == OH) ? std::max<int64_t>(1, std::min<int64_t>(tc::BM / (pbw * pbh), a.N)) : 1;
+        // Row mode (conv_rows.cuh): stride-1 convolutions with at most three filter columns whose tiles are no
+        // emptier than the patch tiles below.  TBN_CONV_ROWS=0 in the environment keeps the patch-mode kernel
+        // (for A/B measurements).
+        {
+            static const bool rows_enabled = [] {
+                const char* v = std::getenv("TBN_CONV_ROWS");
+                return !(v && v[0] == '0');
+            }();
+            const int64_t pitch = round_up(OW + a.kw - 1, 8);
+            const int64_t rpbh = pitch <= tc::BM ? std::min<int64_t>(OH, tc::BM / pitch) : 0;
+            const int64_t patch_tiles = ((OW + pbw - 1) / pbw) * ((OH + pbh - 1) / pbh) * ((a.N + pbi - 1) / pbi);
+            const bool applicable = rows_enabled && !a.dense_w && a.sh == 1 && a.sw == 1 && a.dw == 1 && a.kw <= rows::kMaxTaps &&
+                                    (bn == 64 || bn == 128) && npass * K <= tc::kMaxAccumSteps && rpbh >= 1 &&
+                                    a.N * ((OH + std::max<int64_t>(rpbh, 1) - 1) / std::max<int64_t>(rpbh, 1)) * 20 <= patch_tiles * 21 &&
+                                    a.N * a.H * a.W * a.C * 2 < (1LL << 40) && a.W + a.pw < 32000;
+            if (applicable) {
+                rows::Params rp = {};
+                rp.N = static_cast<int>(N);
+                rp.C = static_cast<int>(a.C);
+                rp.cblocks = static_cast<int>(a.C / 64);
+                rp.kh = static_cast<int>(a.kh);
+                rp.kw = static_cast<int>(a.kw);
+                rp.dh = a.dh;
+                rp.ph = a.ph;
+                rp.pw = a.pw;
+                rp.H = static_cast<int>(a.H);
+                rp.W = static_cast<int>(a.W);
+                rp.OH = static_cast<int>(OH);
+                rp.OW = static_cast<int>(OW);
+                rp.pitch = static_cast<int>(pitch);
+                rp.pbh = static_cast<int>(rpbh);
+                rp.tiles_per_image = static_cast<int>((OH + rpbh - 1) / rpbh);
+                const int64_t tiles_m = a.N * rp.tiles_per_image;
+                rp.tiles_n = static_cast<int>((N + bn - 1) / bn);
+                rp.a_box_bytes = static_cast<int>(npass * pitch * rpbh * 128);
+                rp.n_btiles = static_cast<int>(K / 64);
+                rp.f16 = f16 ? 1 : 0;
+                rp.amax_bits = amax_slot;
+                rp.y = a.y;
+                rp.y_cl = static_cast<__nv_bfloat16*>(a.y_cl);
+                rp.y_cl_term_stride = M * N;
+                rp.ep = a.ep;
+                rp.ep.scale = a.ep.scale;
+                rp.err_word = device_error_word();
+                {
+                    const char* v = std::getenv("TBN_ROWS_DBG");
+                    rp.dbg = v ? std::atoi(v) : 0;
+                }
+                if (tiles_m * rp.tiles_n < (1LL << 31)) {
+                    rp.tiles_m = static_cast<int>(tiles_m);
+                    CUtensorMap map_x;
+                    const cuuint64_t gdim[5] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W), static_cast<cuuint64_t>(a.H),
+                                                static_cast<cuuint64_t>(a.N), static_cast<cuuint64_t>(npass)};
+                    const cuuint64_t gstride[4] = {static_cast<cuuint64_t>(a.C) * 2, static_cast<cuuint64_t>(a.W * a.C) * 2,
+                                                   static_cast<cuuint64_t>(a.H * a.W * a.C) * 2, static_cast<cuuint64_t>(term_stride) * 2};
+                    const cuuint32_t box[5] = {tc::BK, static_cast<cuuint32_t>(pitch), static_cast<cuuint32_t>(rpbh), 1, 1};
+                    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+                    const CUresult cr = encode(&map_x, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, xs, gdim,
+                                               gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    if (cr == CUDA_SUCCESS) {
+                        const bool one_term = tern_act || npass == 1;
+                        // Resident filters when one column tile covers all output channels and they fit beside two stages.
+                        int st_res = 0, st_str = 0;
+                        if (bn == 64) {
+                            st_res = rp.tiles_n == 1 ? (one_term ? rows::stages_that_fit<64, 1, true>(rp.n_btiles) : rows::stages_that_fit<64, 2, true>(rp.n_btiles)) : 0;
+                            st_str = one_term ? rows::stages_that_fit<64, 1, false>(0) : rows::stages_that_fit<64, 2, false>(0);
+                        } else {
+                            st_res = rp.tiles_n == 1 ? (one_term ? rows::stages_that_fit<128, 1, true>(rp.n_btiles) : rows::stages_that_fit<128, 2, true>(rp.n_btiles)) : 0;
+                            st_str = one_term ? rows::stages_that_fit<128, 1, false>(0) : rows::stages_that_fit<128, 2, false>(0);
+                        }
+                        const bool resident = st_res >= 2;
+                        rp.nstages = resident ? st_res : st_str;
+                        if (rp.nstages >= 2) {
+                            if (bn == 64) {
+                                if (one_term) return resident ? rows::launch<64, 1, true>(map_x, maps.neg, rp, a.st) : rows::launch<64, 1, false>(map_x, maps.neg, rp, a.st);
+                                return resident ? rows::launch<64, 2, true>(map_x, maps.neg, rp, a.st) : rows::launch<64, 2, false>(map_x, maps.neg, rp, a.st);
+                            }
+                            if (one_term) return resident ? rows::launch<128, 1, true>(map_x, maps.neg, rp, a.st) : rows::launch<128, 1, false>(map_x, maps.neg, rp, a.st);
+                            return resident ? rows::launch<128, 2, true>(map_x, maps.neg, rp, a.st) : rows::launch<128, 2, false>(map_x, maps.neg, rp, a.st);
+                        }
+                    }
+                }
+            }
+        }
         const bool patch_ok = pbw * a.sw <= 256 && pbh * a.sh <= 256 && a.sw <= 8 && a.sh <= 8 && pbi <= 256 &&
                               a.N * a.H * a.W * a.C * 2 < (1LL << 40);
         if (patch_ok) {
