@@ -682,11 +682,16 @@ def lenet_sweep(args, ctx):
                 res.append({"batch": batch, "error": (proc.stderr or proc.stdout)[-300:]})
                 continue
             byts = batch * (3136.0 + 40.0)
+            adds = batch * 242560.0   # 6*576*25 + 16*64*150 + 256*10 signed adds per image
             res.append({"batch": batch, "ms": ms, "images_per_s": batch / (ms * 1e-3),
-                        "hbm_frac_of_compulsory_bytes": byts / (ms * 1e-3) / 1e9 / ctx.peaks["hbm_gbs"]})
-    return {"through": "C++ tbn::TBNModel::Session (host/bin/run_graph), float x binary mode, wall time per synchronous run",
+                        "hbm_frac_of_compulsory_bytes": byts / (ms * 1e-3) / 1e9 / ctx.peaks["hbm_gbs"],
+                        "cuda_core_add_frac": adds / (ms * 1e-3) / (148 * 128 * 1.965e9)})
+    return {"through": "C++ tbn::TBNModel::Session (host/bin/run_graph), float x binary mode, wall time per synchronous run; "
+                       "the Session runs this graph as one whole-network kernel (add / subtract by sign on the CUDA cores)",
+            "roofline_note": "cuda_core_add_frac = signed adds per second / (148 SMs x 128 lanes x 1.965 GHz); the kernel reads only "
+                             "the image and writes only the logits, so the HBM fraction of the compulsory bytes is given as well",
             "data": "input U[0,1) default_rng(0), weights N(0,0.1) default_rng(1)", "sweep": res,
-            "bound": "launch latency at small batches, HBM at large ones (compulsory bytes: 3136 in + 40 out per image)"}
+            "bound": "launch latency at small batches, the CUDA cores' add rate at large ones"}
 
 
 def run_reference(args):

@@ -53,6 +53,7 @@ SIGNATURES = {
                               _vp, _f32, _vp, _vp, _vp, _i32, _u32, _i32, _vp, _sz, _vp]),
     "tbn_conv2d_tbn": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
                               _i32, _vp, _f32, _vp, _vp, _u32, _i32, _vp, _sz, _vp]),
+    "tbn_lenet_fused_fxb": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tbn_relu": (_i32, [_vp, _i64, _vp, _vp]),
     "tbn_add": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp, _vp]),
     "tbn_pool2d": (_i32, [_i32, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
@@ -471,6 +472,20 @@ class _Lib:
                                               *[int(v) for v in p], _ptr(bias), _ptr(residual), _ptr(y), _ptr(y_cl), epilogue,
                                               CONV_WEIGHTS_TAP_MAJOR, _ptr(workspace), nbytes, _stream()))
         return y, y_cl
+
+    def lenet_fused(self, x, w1, w2, wf, classes, out=None):
+        """x [batch, 1, 28, 28]; w1 / w2 / wf: dicts with "words", "alpha" and optional "bias" (packed as the Session
+        packs them).  One launch for the whole LeNet-shaped network -> logits [batch, classes]."""
+        import torch
+        self.init()
+        x = x.contiguous()
+        batch = x.shape[0]
+        if out is None:
+            out = torch.empty((batch, classes), dtype=torch.float32, device=x.device)
+        check(self.h.tbn_lenet_fused_fxb(_ptr(x), batch, 6, 16, classes, _ptr(w1["words"]), _ptr(w1.get("alpha")), _ptr(w1.get("bias")),
+                                         _ptr(w2["words"]), _ptr(w2.get("alpha")), _ptr(w2.get("bias")), _ptr(wf["words"]),
+                                         _ptr(wf.get("alpha")), _ptr(wf.get("bias")), _ptr(out), _stream()))
+        return out
 
     def relu(self, x):
         import torch

@@ -56,6 +56,50 @@ class Session:
             else:
                 self.weights[name] = {"dense": t}
         self._ws = {}
+        self.whole_net = True   # run a LeNet-shaped graph as one kernel when no intermediate is wanted
+        self._lenet = self._match_lenet()
+
+    def _match_lenet(self):
+        """The LeNet-shaped graph (Conv 5x5, Relu, MaxPool 2, Conv 5x5, Relu, MaxPool 2, Flatten, Gemm; 1 x 28 x 28
+        input, 6 and 16 feature maps, binary weights) -> the three weight records, else None."""
+        g = self.graph
+        nodes = g["nodes"]
+        ops = [n["op"] for n in nodes]
+        if ops != ["Conv", "Relu", "MaxPool", "Conv", "Relu", "MaxPool", "Flatten", "Gemm"] or len(g["outputs"]) != 1:
+            return None
+        if any(nodes[i]["inputs"][0] != nodes[i - 1]["outputs"][0] for i in range(1, 8)):
+            return None
+        if nodes[7]["outputs"][0] not in g["outputs"] or len(g["inputs"]) != 1:
+            return None
+        shape = tuple(next(iter(g["inputs"].values())))
+        if len(shape) != 4 or shape[1:] != (1, 28, 28):
+            return None
+        for c in (0, 3):
+            a = nodes[c]["attrs"]
+            if (list(a.get("strides", [1, 1])) != [1, 1] or any(a.get("pads", [0, 0, 0, 0])) or list(a.get("dilations", [1, 1])) != [1, 1]
+                    or a.get("group", 1) != 1 or a.get("auto_pad", "NOTSET") not in ("NOTSET", "VALID")):
+                return None
+        for c in (2, 5):
+            a = nodes[c]["attrs"]
+            if (list(a.get("kernel_shape", [2, 2])) != [2, 2] or list(a.get("strides", a.get("kernel_shape", [2, 2]))) != [2, 2]
+                    or any(a.get("pads", [0, 0, 0, 0])) or a.get("ceil_mode", 0)):
+                return None
+        a = nodes[7]["attrs"]
+        if nodes[6]["attrs"].get("axis", 1) != 1 or a.get("transA", 0) or a.get("transB", 0) or a.get("alpha", 1.0) != 1.0 or a.get("beta", 1.0) != 1.0:
+            return None
+        recs = []
+        for n, want in ((nodes[0], (6, 1, 5, 5)), (nodes[3], (16, 6, 5, 5)), (nodes[7], None)):
+            w = self.weights.get(n["inputs"][1], {})
+            if "words" not in w or (want is not None and (w["shape"] != want or w.get("order", 0) != capi.CONV_WEIGHTS_REFERENCE)):
+                return None
+            rec = {"words": w["words"], "alpha": w["alpha"]}
+            if len(n["inputs"]) > 2:
+                rec["bias"] = self.weights[n["inputs"][2]]["dense"]
+            recs.append(rec)
+        fshape = self.weights[nodes[7]["inputs"][1]]["shape"]
+        if fshape[0] != 256 or not 1 <= fshape[1] <= 64:
+            return None
+        return recs + [fshape[1]]
 
     # -- weight preparation ----------------------------------------------------------------
     def _pack(self, w):
@@ -105,6 +149,13 @@ class Session:
             raise ValueError("Not all inputs provided")
         vals = dict(self.inputs)
         nodes = self.graph["nodes"]
+        if (self._lenet is not None and self.whole_net and self.fuse and not self.quantization
+                and not getattr(self, "keep_intermediates", True)):
+            w1, w2, wf, classes = self._lenet
+            out = self.L.lenet_fused(next(iter(self.inputs.values())), w1, w2, wf, classes)
+            self.values = {nodes[-1]["outputs"][0]: out}
+            self.intermediates = dict(self.values)
+            return
         consumers = {}
         for n in nodes:
             for i in n["inputs"]:

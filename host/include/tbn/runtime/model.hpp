@@ -101,6 +101,7 @@ public:
             DenseWeights dense_w;
         };
         const CachedWeights* weights_for(const std::string& name, const Tensor& w, bool conv);
+        bool run_lenet_fused();
         void execute_node(const ModelNode& node);
         void execute_conv(const ModelNode& node, size_t idx);
         void execute_gemm(const ModelNode& node);

@@ -6,6 +6,7 @@
 
 #include "tbn/onnx_integration/onnx_parser.hpp"
 #include "tbn/runtime/model.hpp"
+#include "tbn_cuda.h"
 
 namespace tbn {
 
@@ -81,6 +82,10 @@ void TBNModel::Session::run() {
     skip_.clear();
     for (const auto& kv : input_tensors_) intermediate_tensors_[kv.first] = kv.second;
     for (const auto& kv : graph_->initializers) intermediate_tensors_[kv.first] = kv.second;
+    if (optimize_ && !use_quantization_ && run_lenet_fused()) {
+        synchronize();
+        return;
+    }
     const auto& nodes = graph_->nodes;
     std::unordered_map<std::string, size_t> last_use;
     for (size_t i = 0; i < nodes.size(); ++i)
@@ -112,6 +117,98 @@ void TBNModel::Session::run() {
     }
     cl_tensors_.clear();
     synchronize();
+}
+
+// The LeNet-shaped graph (Conv 5x5, Relu, MaxPool 2x2, Conv 5x5, Relu, MaxPool 2x2, Flatten, Gemm on 1 x 28 x 28
+// inputs with 6 and 16 feature maps, all three weight tensors binary) runs as one kernel in float x binary mode:
+// the whole-network fusion of Session::execute_* (tbn/runtime/model.hpp:190-228).  Returns false when the graph is
+// anything else; the node-by-node path then runs.
+bool TBNModel::Session::run_lenet_fused() {
+    const auto& nodes = graph_->nodes;
+    static const char* kOps[8] = {"Conv", "Relu", "MaxPool", "Conv", "Relu", "MaxPool", "Flatten", "Gemm"};
+    if (nodes.size() != 8 || graph_->outputs.size() != 1 || input_tensors_.size() != 1) return false;
+    for (size_t i = 0; i < 8; ++i) {
+        if (nodes[i].op_type != kOps[i] || nodes[i].outputs.size() != 1 || nodes[i].inputs.empty()) return false;
+        if (i > 0 && nodes[i].inputs[0] != nodes[i - 1].outputs[0]) return false;
+    }
+    if (nodes[7].outputs[0] != graph_->outputs[0] || input_tensors_.count(nodes[0].inputs[0]) == 0) return false;
+    auto ints_are = [](const ModelNode& n, const char* key, std::initializer_list<int64_t> want, bool absent_ok) {
+        auto a = n.attributes.find(key);
+        if (a == n.attributes.end()) return absent_ok;
+        if (!a->second.is_ints()) return false;
+        const auto& v = a->second.as_ints();
+        if (v.size() < want.size()) return false;
+        size_t i = 0;
+        for (int64_t w : want)
+            if (v[i++] != w) return false;
+        for (; i < v.size(); ++i)
+            if (v[i] != (std::string(key) == "pads" ? 0 : 1)) return false;
+        return true;
+    };
+    auto int_is = [](const ModelNode& n, const char* key, int64_t want) {
+        auto a = n.attributes.find(key);
+        return a == n.attributes.end() || (a->second.is_int() && a->second.as_int() == want);
+    };
+    auto float_is = [](const ModelNode& n, const char* key, float want) {
+        auto a = n.attributes.find(key);
+        return a == n.attributes.end() || (a->second.is_float() && a->second.as_float() == want);
+    };
+    for (size_t c : {size_t(0), size_t(3)}) {
+        const ModelNode& n = nodes[c];
+        if (n.inputs.size() < 2 || !ints_are(n, "strides", {1, 1}, true) || !ints_are(n, "pads", {0, 0}, true) ||
+            !ints_are(n, "dilations", {1, 1}, true) || !int_is(n, "group", 1))
+            return false;
+        auto ap = n.attributes.find("auto_pad");
+        if (ap != n.attributes.end() && ap->second.is_string() && ap->second.as_string() != "NOTSET" && ap->second.as_string() != "VALID")
+            return false;
+    }
+    for (size_t c : {size_t(2), size_t(5)}) {
+        const ModelNode& n = nodes[c];
+        if (!ints_are(n, "kernel_shape", {2, 2}, true) || !ints_are(n, "strides", {2, 2}, true) || !ints_are(n, "pads", {0, 0}, true) ||
+            !int_is(n, "ceil_mode", 0))
+            return false;
+    }
+    if (!int_is(nodes[6], "axis", 1)) return false;
+    const ModelNode& fc = nodes[7];
+    if (fc.inputs.size() < 2 || !int_is(fc, "transA", 0) || !int_is(fc, "transB", 0) || !float_is(fc, "alpha", 1.0f) ||
+        !float_is(fc, "beta", 1.0f))
+        return false;
+    const Tensor& X = input_tensors_.at(nodes[0].inputs[0]);
+    auto init = [&](const std::string& name) -> const Tensor* {
+        auto it = graph_->initializers.find(name);
+        return it == graph_->initializers.end() ? nullptr : &it->second;
+    };
+    const Tensor *W1 = init(nodes[0].inputs[1]), *W2 = init(nodes[3].inputs[1]), *WF = init(fc.inputs[1]);
+    if (!W1 || !W2 || !WF || X.dtype() != DataType::FLOAT32) return false;
+    const auto& xs = X.shape().dims;
+    if (xs.size() != 4 || xs[1] != 1 || xs[2] != 28 || xs[3] != 28) return false;
+    if (W1->shape().dims != std::vector<int64_t>{6, 1, 5, 5} || W2->shape().dims != std::vector<int64_t>{16, 6, 5, 5}) return false;
+    const auto& fs = WF->shape().dims;
+    if (fs.size() != 2 || fs[0] != 256 || fs[1] < 1 || fs[1] > 64) return false;
+    const Tensor* bias[3] = {nullptr, nullptr, nullptr};
+    const ModelNode* owners[3] = {&nodes[0], &nodes[3], &fc};
+    for (int i = 0; i < 3; ++i)
+        if (owners[i]->inputs.size() >= 3) {
+            bias[i] = init(owners[i]->inputs[2]);
+            const int64_t want = i == 0 ? 6 : (i == 1 ? 16 : fs[1]);
+            if (!bias[i] || bias[i]->dtype() != DataType::FLOAT32 || bias[i]->num_elements() != want) return false;
+        }
+    const CachedWeights* c1 = weights_for(nodes[0].inputs[1], *W1, true);
+    const CachedWeights* c2 = weights_for(nodes[3].inputs[1], *W2, true);
+    const CachedWeights* cf = weights_for(fc.inputs[1], *WF, false);
+    if (!c1 || !c2 || !cf || c1->dense || c2->dense || cf->dense || c1->packed.tap_major || c2->packed.tap_major) return false;
+    const int64_t batch = xs[0], classes = fs[1];
+    Tensor out = Tensor::device_uninitialized(Shape{batch, classes}, DataType::FLOAT32);
+    auto words = [](const PackedWeights& w) { return static_cast<const uint32_t*>(w.neg.device_data()); };
+    auto f32 = [](const Tensor* t) { return t ? static_cast<const float*>(t->device_data()) : nullptr; };
+    detail::check(tbn_lenet_fused_fxb(static_cast<const float*>(X.device_data()), batch, 6, 16, static_cast<int32_t>(classes),
+                                      words(c1->packed), f32(&c1->packed.alpha), f32(bias[0]), words(c2->packed),
+                                      f32(&c2->packed.alpha), f32(bias[1]), words(cf->packed), f32(&cf->packed.alpha), f32(bias[2]),
+                                      static_cast<float*>(out.device_data()), nullptr));
+    out.mark_device_written();
+    intermediate_tensors_[graph_->outputs[0]] = out;
+    output_tensors_[graph_->outputs[0]] = out;
+    return true;
 }
 
 const TBNModel::Session::CachedWeights* TBNModel::Session::weights_for(const std::string& name, const Tensor& w, bool conv) {

@@ -358,6 +358,22 @@ int32_t tbn_conv2d_f32(const float* d_x, int64_t N, int64_t C, int64_t H, int64_
                        uint32_t epilogue, int32_t weight_order, void* d_workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- whole-network kernel ------------------------------------------------------------------------------- */
+
+/* The LeNet-shaped binary CNN in ONE launch, float x binary mode: x [batch, 1, 28, 28] -> Conv 1 -> c1 5x5 + bias,
+ * ReLU, MaxPool 2x2, Conv c1 -> c2 5x5 + bias, ReLU, MaxPool 2x2, Flatten, Gemm c2*16 -> classes + bias, every layer
+ * y = (sum +-x) * alpha + bias.  Stands in for the node-by-node execution of that graph by the reference Session
+ * (tbn/runtime/model.hpp:190-228 with execute_conv / execute_relu / execute_maxpool / execute_gemm); one image and all
+ * its intermediates stay in shared memory, only the image is read and the logits written.
+ *   d_w1 / d_w2: packed filters from tbn_quant_pack_binary(TBN_LAYOUT_NK) of [c1, 25] and [c2, c1*25] (reference tap
+ *   order); d_wf: packed Gemm weights from tbn_quant_pack_binary(TBN_LAYOUT_KN) of [c2*16, classes];
+ *   alphas / biases: nullable fp32 per output channel.  Built for c1 = 6, c2 = 16 (TBN_NOT_IMPLEMENTED otherwise),
+ *   1 <= classes <= 64. */
+int32_t tbn_lenet_fused_fxb(const float* d_x, int64_t batch, int32_t c1, int32_t c2, int32_t classes, const uint32_t* d_w1,
+                            const float* d_alpha1, const float* d_bias1, const uint32_t* d_w2, const float* d_alpha2,
+                            const float* d_bias2, const uint32_t* d_wf, const float* d_alphaf, const float* d_biasf, float* d_y,
+                            void* stream);
+
 /* ---- glue operators of the CNN graphs (device resident, fp32) --------------------------- */
 
 /* y = max(0, x)   (Session::execute_relu, model.hpp:1166-1169) */

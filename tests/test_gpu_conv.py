@@ -290,6 +290,39 @@ def test_lenet_session_float_binary(tbn, oracle, batch):
         s.set_input("nope", x)
 
 
+@pytest.mark.parametrize("batch", [1, 7, 2500])
+def test_lenet_whole_network_kernel(tbn, oracle, batch):
+    """The LeNet-shaped graph as ONE kernel (Session with no intermediates wanted): logits within 1e-5 of the
+    reference's float path on the dequantised weights, predicted classes identical, and equal (to rounding) to the
+    layer-by-layer execution.  2500 images: several images per block and a ragged last wave."""
+    from fast_arm_tbcnn_b200.session import Session
+    from oracle import graphs
+    net = graphs.lenet(batch=batch, seed=1)
+    x = np.random.default_rng(0).random((batch, 1, 28, 28), dtype=np.float32)
+    sub = min(batch, 64)   # the CPU oracle on a sample of the images
+    pick = np.sort(np.random.default_rng(1).choice(batch, size=sub, replace=False))
+    net_sub = graphs.lenet(batch=sub, seed=1)
+    expect = graphs.run_float(net_sub, x[pick], oracle)
+    s = Session(net)
+    s.keep_intermediates = False
+    assert s._lenet is not None
+    launches0 = tbn.lib.launch_count()
+    s.set_input("input", x)
+    s.run()
+    tbn.lib.sync()
+    assert tbn.lib.launch_count() - launches0 == 1   # the whole network is one launch
+    got = s.get_output("output").cpu().numpy()
+    assert rel_l2(got[pick], expect) <= 1e-5
+    assert np.array_equal(got[pick].argmax(axis=1), expect.argmax(axis=1))
+    layered = Session(net)
+    layered.whole_net = False
+    layered.keep_intermediates = False
+    layered.set_input("input", x)
+    layered.run()
+    tbn.lib.sync()
+    assert rel_l2(got, layered.get_output("output").cpu().numpy()) <= 1e-5
+
+
 def test_lenet_session_tbn_mode_bit_exact(tbn, golden):
     """Quantisation on: bit-equal to the reference Session's output stored in the golden fixture."""
     from fast_arm_tbcnn_b200.session import Session
