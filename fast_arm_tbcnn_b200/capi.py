@@ -62,6 +62,9 @@ SIGNATURES = {
     "tbn_binary_elementwise": (_i32, [_i32, _vp, _i64, _vp, _i64, _vp, _vp]),
     "tbn_transpose2d": (_i32, [_vp, _i64, _i64, _vp, _vp]),
     "tbn_gather_cols_permute": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "tbn_ipc_export": (_i32, [_vp, _vp]),
+    "tbn_ipc_open": (_i32, [_vp, C.POINTER(_vp)]),
+    "tbn_ipc_close": (_i32, [_vp]),
     "tbn_packed_dims": (_i32, [_i64, _i64, C.POINTER(_i64), C.POINTER(_i64)]),
     "tbn_quantize_to_binary": (_i32, [_vp, _i64, _f32, _vp, _vp]),
     "tbn_quantize_to_ternary": (_i32, [_vp, _i64, _f32, _f32, _vp, _vp]),

@@ -1,6 +1,7 @@
 // Helper for the column-sharded multi-GPU GEMM: after the all-gather of the per-rank output
 // slabs, interleave them into the row-major result.  HBM-bound copy (read + write of C once).
 #include <algorithm>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -44,4 +45,33 @@ extern "C" int32_t tbn_gather_cols_permute(const float* d_slabs, int64_t G, int6
     if (vec) gather_cols_permute_kernel<true><<<grid, 256, 0, as_stream(stream)>>>(d_slabs, G, M, Nc, d_c, ldc);
     else gather_cols_permute_kernel<false><<<grid, 256, 0, as_stream(stream)>>>(d_slabs, G, M, Nc, d_c, ldc);
     return launched("gather_cols_permute_kernel");
+}
+
+// ---- sharing a device buffer between the processes of one box (one process per GPU) ---------------------
+// The column-sharded GEMM writes its slab into every rank's result matrix; a rank makes its matrix reachable
+// for the others by exporting an inter-process handle, the others open it and get a pointer in their own address
+// space that tbn_gemm_fxb_multi accepts as a destination.  Thin wrappers of the CUDA IPC calls with the library's
+// status convention.
+
+extern "C" int32_t tbn_ipc_export(void* d_ptr, void* handle64) {
+    TBN_REQUIRE(d_ptr && handle64, TBN_INVALID_ARGUMENT, "tbn_ipc_export: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == TBN_IPC_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    TBN_CUDA_TRY(cudaIpcGetMemHandle(&h, d_ptr));
+    std::memcpy(handle64, &h, sizeof h);
+    return TBN_SUCCESS;
+}
+
+extern "C" int32_t tbn_ipc_open(const void* handle64, void** d_ptr) {
+    TBN_REQUIRE(handle64 && d_ptr, TBN_INVALID_ARGUMENT, "tbn_ipc_open: null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof h);
+    *d_ptr = nullptr;
+    TBN_CUDA_TRY(cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return TBN_SUCCESS;
+}
+
+extern "C" int32_t tbn_ipc_close(void* d_ptr) {
+    if (d_ptr) TBN_CUDA_TRY(cudaIpcCloseMemHandle(d_ptr));
+    return TBN_SUCCESS;
 }

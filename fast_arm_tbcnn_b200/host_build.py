@@ -17,6 +17,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HOST = os.path.join(ROOT, "host")
 LIB = os.path.join(HOST, "lib", "libtbn_host.so")
 RUN_GRAPH = os.path.join(HOST, "bin", "run_graph")
+SHARDED_GEMM = os.path.join(HOST, "bin", "sharded_gemm")
 PY_MODULE = os.path.join(HOST, "lib", "_tbn" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 
@@ -49,6 +50,14 @@ def build(force=False):
         if proc.returncode != 0:
             sys.stderr.write(proc.stdout + proc.stderr)
             raise RuntimeError("g++ failed building " + RUN_GRAPH)
+    driver2 = os.path.join(HOST, "tests", "sharded_gemm.cpp")
+    if force or _stale(SHARDED_GEMM, [driver2, LIB] + hdrs):
+        cmd = [cxx, "-std=c++20", "-O2", "-Wall", "-o", SHARDED_GEMM] + inc + [driver2, "-L", os.path.dirname(LIB), "-ltbn_host",
+               "-L", cuda_dir, "-ltbn_cuda", "-Wl,-rpath,$ORIGIN/../lib", "-Wl,-rpath,$ORIGIN/../../fast_arm_tbcnn_b200/lib"]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+            raise RuntimeError("g++ failed building " + SHARDED_GEMM)
     build_python_module(force, cxx, inc, cuda_dir, hdrs)
     return LIB, RUN_GRAPH
 

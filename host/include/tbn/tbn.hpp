@@ -5,6 +5,7 @@
 #include "operators/ops.hpp"
 #include "runtime/attribute.hpp"
 #include "runtime/model.hpp"
+#include "runtime/sharded_gemm.hpp"
 #include "runtime/tensor.hpp"
 #include "runtime/types.hpp"
 #include "utils/errors.hpp"

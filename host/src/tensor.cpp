@@ -1,5 +1,6 @@
 // tbn::Tensor storage on top of the C ABI (tbn_cuda_malloc / h2d / d2h), error mapping, helpers.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -27,7 +28,11 @@ void throw_status(int status) {
 void ensure_runtime() {
     static std::once_flag once;
     static int status = 0;
-    std::call_once(once, [] { status = tbn_cuda_init(0); });
+    // One process drives one GPU: device 0 unless TBN_DEVICE names another (one process per GPU on a multi-GPU box).
+    std::call_once(once, [] {
+        const char* dev = std::getenv("TBN_DEVICE");
+        status = tbn_cuda_init(dev ? std::atoi(dev) : 0);
+    });
     check(status);
 }
 

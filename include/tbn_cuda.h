@@ -415,6 +415,16 @@ int32_t tbn_transpose2d(const float* d_x, int64_t rows, int64_t cols, float* d_y
 int32_t tbn_gather_cols_permute(const float* d_slabs, int64_t G, int64_t M, int64_t Nc, float* d_c,
                                 int64_t ldc, void* stream);
 
+/* Sharing a result matrix between the processes of one box (one process per GPU), for tbn_gemm_fxb_multi: the owner
+ * exports a 64-byte handle of a buffer obtained from tbn_cuda_malloc and sends it to the other ranks by any host
+ * channel; they open it and receive a pointer, valid in their own process, through which their GPU writes the
+ * owner's memory over NVLink (peer access is enabled on first use).  Close every opened pointer before the owner
+ * frees the buffer.  (New: the reference is single-device.) */
+#define TBN_IPC_HANDLE_BYTES 64
+int32_t tbn_ipc_export(void* d_ptr, void* handle64);
+int32_t tbn_ipc_open(const void* handle64, void** d_ptr);
+int32_t tbn_ipc_close(void* d_ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,7 +29,8 @@ def test_host_layer_builds_and_exports_reference_names(host):
                  "tbn::TBNModel::Session::get_output(", "tbn::Tensor::to_device(",
                  "tbn::qlinear_matmul_binary_blocked_packed(", "tbn::qlinear_matmul_binary_blocked_prepacked(",
                  "tbn::BinaryMatrix::pack(", "tbn::TernaryMatrix::pack_from_float(", "tbn::TernaryMatrix::pack(",
-                 "tbn::PackedBinaryWeights::from_int8("]:
+                 "tbn::PackedBinaryWeights::from_int8(", "tbn::ShardedGemm::ShardedGemm(", "tbn::ShardedGemm::connect(",
+                 "tbn::ShardedGemm::multiply(", "tbn::ShardedGemm::export_result("]:
         assert name in out, name
     assert os.access(driver, os.X_OK)
 
@@ -199,3 +200,22 @@ def test_operators_on_prepacked_operands(host):
     oracle) on the same operands, including weights padded to 64 instead of 128 rows."""
     proc = subprocess.run([host[1], "--prepacked"], capture_output=True, text=True)
     assert proc.returncode == 0 and "prepacked ok" in proc.stdout, proc.stdout + proc.stderr
+
+
+@pytest.mark.gpu
+def test_cpp_sharded_gemm_two_processes(host, tmp_path):
+    """tbn::ShardedGemm with one process per GPU: handles exchanged through files, each rank's fused kernel stores
+    its column slab into both result matrices (its own and, over NVLink, the peer's); every rank's C must equal
+    the single-GPU product bit for bit.  Needs two GPUs (skipped on a one-GPU box); with world size 1 the same
+    driver checks the single-rank path."""
+    import torch
+    from fast_arm_tbcnn_b200 import host_build
+    world = 2 if torch.cuda.device_count() >= 2 else 1
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, TBN_DEVICE=str(rank))
+        procs.append(subprocess.Popen([host_build.SHARDED_GEMM, str(rank), str(world), str(tmp_path), "300", "640", "512"],
+                                      stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env))
+    for rank, p in enumerate(procs):
+        out, err = p.communicate(timeout=180)
+        assert p.returncode == 0 and "sharded gemm ok" in out, (rank, out, err)
