@@ -518,10 +518,6 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                 rp.ep = a.ep;
                 rp.ep.scale = a.ep.scale;
                 rp.err_word = device_error_word();
-                {
-                    const char* v = std::getenv("TBN_ROWS_DBG");
-                    rp.dbg = v ? std::atoi(v) : 0;
-                }
                 if (tiles_m * rp.tiles_n < (1LL << 31)) {
                     rp.tiles_m = static_cast<int>(tiles_m);
                     CUtensorMap map_x;

@@ -51,7 +51,6 @@ struct Params {
     int64_t y_cl_term_stride;
     Epilogue ep;
     int* err_word;
-    int dbg;
 };
 
 template <int BN, int NPASS, bool RESIDENT>
@@ -141,16 +140,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                             break;
                         }
                         const uint32_t bar = bar_full + 8 * stage;
-                        ptx::mbar_arrive_expect_tx(bar, ((p.dbg & 4) ? 0u : static_cast<uint32_t>(p.a_box_bytes)) +
+                        ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(p.a_box_bytes) +
                                                             (RESIDENT ? 0u : static_cast<uint32_t>(p.kw) * C::B_TILE_BYTES));
                         const uint32_t a_dst = stages + stage * C::STAGE_BYTES;
                         // Input pixels (x, y) = (-pw .. -pw + pitch - 1, oh0 - ph + ti*dh .. + pbh - 1), channels [64 cb, +64):
                         // tile row bh * pitch + bw holds pixel (bw - pw, oh0 + bh - ph + ti*dh); outside the image: zeros.
-                        if (!(p.dbg & 4)) {
 #pragma unroll
                         for (int q = 0; q < NPASS; ++q)
                             ptx::tma_load_5d(a_dst + q * tc::A_TILE_BYTES, &tmap_x, cb * tc::BK, -p.pw, oh0 - p.ph + ti * p.dh, img, q, bar);
-                        }
                         if (!RESIDENT) {
                             const uint32_t b_dst = a_dst + C::A_BYTES;
                             for (int tj = 0; tj < p.kw; ++tj)
@@ -199,7 +196,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                             for (int q = 0; q < NPASS; ++q) {
 #pragma unroll
                                 for (int k4 = 0; k4 < tc::BK / tc::UMMA_K; ++k4) {
-                                    if ((p.dbg & 2) && (q | k4)) continue;
                                     const uint64_t a_desc =
                                         ptx::umma_desc_k_sw128(a_addr + q * tc::A_TILE_BYTES + tj * 128 + k4 * tc::UMMA_K * 2);
                                     const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * tc::UMMA_K * 2);
@@ -329,7 +325,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                         }
                     }
                 }
-                if ((p.dbg & 1) && o[0] != 123.456f) continue;
                 if (p.y != nullptr) {
                     float* dst = p.y + first;
                     if (ncols == 32) {
