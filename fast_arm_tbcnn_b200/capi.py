@@ -165,7 +165,8 @@ class _Lib:
         """The library's per-shape choice for TBN_MODE_AUTO -> dict(kernel, bn, group_m, fused_split)."""
         k, b, g, f = _i32(), _i32(), _i32(), _i32()
         check(self.h.tbn_gemm_plan(M, N, K, C.byref(k), C.byref(b), C.byref(g), C.byref(f)))
-        return {"kernel": "cuda-core" if k.value else "tcgen05", "bn": b.value, "group_m": g.value, "fused_split": bool(f.value)}
+        return {"kernel": ("tcgen05", "cuda-core", "tcgen05-pair")[k.value], "bn": b.value, "group_m": g.value,
+                "fused_split": bool(f.value)}
 
     def wave_model_bn(self, M, N, preferred):
         return int(self.h.tbn_gemm_plan_bn(M, N, preferred))

@@ -30,6 +30,7 @@
 //   gemm_simt_kernel          CUDA-core add/subtract-by-sign, fp32, k ascending (bit-equal to the
 //                             naive reference loop); used for tiny problems and as a cross-check.
 #include <atomic>
+#include "gemm_pair.cuh"
 #include "gemm_tc.cuh"
 #include "plan.cuh"
 
@@ -257,7 +258,7 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     // the fp32 rows and split them in registers (same arithmetic, bit-identical operands) -- once per column
     // tile of the weights, so by default only when there is a single one.
     const GemmPlan plan = gemm_plan(M, N, K);
-    const bool fused_split = !f16 && fused_split_wanted(plan) && !ternarise_act && npass == 2 && !dense_w && K % 4 == 0 &&
+    const bool fused_split = !f16 && num_out == 0 && fused_split_wanted(plan) && !ternarise_act && npass == 2 && !dense_w && K % 4 == 0 &&
                              lda % 4 == 0 && reinterpret_cast<uintptr_t>(d_a) % 16 == 0;
     int32_t rc = TBN_SUCCESS;
     if (fused_split) {}
@@ -281,7 +282,9 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
                 "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(cr)));
 
-    const int bn = plan.bn;
+    // CTA pairs (gemm_pair.cuh): the plan's choice for large products; 256 x 256 tiles, each CTA holding 128 columns.
+    const bool use_pair = plan.kernel == 2 && !fused_split && !dense_w && num_out == 0;
+    const int bn = use_pair ? pair::BH : plan.bn;  // rows of the packed-word box
     if (dense_w) {
         TBN_REQUIRE(reinterpret_cast<uintptr_t>(dense_w) % 16 == 0, TBN_INVALID_ARGUMENT,
                     "gemm: split dense weights must be 16-byte aligned");
@@ -291,9 +294,10 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     } else {
         TBN_REQUIRE(reinterpret_cast<uintptr_t>(d_neg) % 16 == 0 && (!d_pos || reinterpret_cast<uintptr_t>(d_pos) % 16 == 0),
                     TBN_INVALID_ARGUMENT, "gemm: packed weight planes must be 16-byte aligned");
-        rc = make_word_map(encode, d_neg, K_pad / 32, N_pad, bn, &maps.neg);
+        const int wpr = use_pair ? 4 : gemm_words_per_row(d_pos != nullptr, num_out > 0);
+        rc = make_word_map(encode, d_neg, K_pad / 32, N_pad, bn, &maps.neg, wpr);
         if (rc) return rc;
-        rc = make_word_map(encode, d_pos ? d_pos : d_neg, K_pad / 32, N_pad, bn, &maps.pos);
+        rc = make_word_map(encode, d_pos ? d_pos : d_neg, K_pad / 32, N_pad, bn, &maps.pos, wpr);
         if (rc) return rc;
     }
     tc::Params p = {};
@@ -321,6 +325,14 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
     p.K = static_cast<int>(K);
     p.f16 = f16 ? 1 : 0;
     p.amax_bits = amax_slot;
+    if (use_pair) {
+        p.tiles_m = static_cast<int>((M_pad / tc::BM + 1) / 2);
+        p.tiles_n = static_cast<int>((N + pair::BN - 1) / pair::BN);
+        const bool tern = d_pos != nullptr;
+        if (npass == 1) return tern ? pair::launch<1, true>(maps, p, st) : pair::launch<1, false>(maps, p, st);
+        if (npass == 2) return tern ? pair::launch<2, true>(maps, p, st) : pair::launch<2, false>(maps, p, st);
+        return tern ? pair::launch<3, true>(maps, p, st) : pair::launch<3, false>(maps, p, st);
+    }
     if (fused_split)
         return d_pos ? dispatch_bn<2, true, 3, false>(bn, maps, p, st) : dispatch_bn<2, false, 3, false>(bn, maps, p, st);
     if (dense_w) {
@@ -328,6 +340,16 @@ int32_t gemm_tensor_core(const float* d_a, int64_t M, int64_t K, int64_t lda, bo
         return dispatch_bn<2, false, 0, false, 1>(bn, maps, p, st);
     }
     const bool ternary_w = d_pos != nullptr;
+    if (num_out > 0) {  // multi-destination epilogue
+        if (npass == 1)
+            return ternary_w ? dispatch_bn<1, true, 0, false, 0, true>(bn, maps, p, st)
+                             : dispatch_bn<1, false, 0, false, 0, true>(bn, maps, p, st);
+        if (npass == 2)
+            return ternary_w ? dispatch_bn<2, true, 0, false, 0, true>(bn, maps, p, st)
+                             : dispatch_bn<2, false, 0, false, 0, true>(bn, maps, p, st);
+        return ternary_w ? dispatch_bn<3, true, 0, false, 0, true>(bn, maps, p, st)
+                         : dispatch_bn<3, false, 0, false, 0, true>(bn, maps, p, st);
+    }
     if (npass == 1)
         return ternary_w ? dispatch_bn<1, true, 0, false>(bn, maps, p, st)
                          : dispatch_bn<1, false, 0, false>(bn, maps, p, st);

@@ -151,17 +151,25 @@ constexpr int kMaxAccumSteps = 4096;
 // Operand modes that lower a convolution (see AMODE at the kernel).
 __host__ __device__ constexpr bool is_conv_mode(int amode) { return amode == 1 || amode == 2 || amode == 4; }
 
-template <int BN, int NPASS, bool TERNARY, int BSRC = 0, bool CONV = false>
+// MULTI: the multi-destination epilogue (column-sharded multi-GPU GEMM) is compiled in, with its staging buffers.
+template <int BN, int NPASS, bool TERNARY, int BSRC = 0, bool CONV = false, bool MULTI = false>
 struct Cfg {
     static constexpr bool DENSE = BSRC == 1;
+    // k-blocks covered by one packed-word tile.  A TMA box is delivered row by row (a row here = the words of one
+    // column), so longer rows mean fewer rows per k-block for the TMA unit: 32-byte rows (4 k-blocks) where the
+    // shared memory allows it, 16-byte rows (2 k-blocks) with two planes or with the staging buffers of MULTI.
+    // (Measured A/B at 16384^3 on one box: 11.74-11.82 ms against 11.67-11.85 ms -- no difference; the kernel is
+    // not bound by the TMA unit.  Kept: it halves the word-tile loads.)
+    static constexpr int WORD_KB = (!TERNARY && !MULTI && !CONV && BSRC == 0) ? 4 : 2;
     static constexpr int kWordStages = BSRC != 0 ? 1 : (CONV ? kWordStagesConv : kWordStagesGemm);  // TMA-fed weights use no words
     static constexpr int B_TILE_BYTES = BN * BK * 2;
     static constexpr int B_TERMS = DENSE ? 2 : 1;  // dense weights: hi and lo bf16 terms
     static constexpr int B_BYTES = B_TERMS * B_TILE_BYTES;
     static constexpr int STAGE_BYTES = B_BYTES + NPASS * A_TILE_BYTES;
-    static constexpr int WORD_TILE_BYTES = BN * 16 * (TERNARY ? 2 : 1);  // 4 words per column and plane
-    // barriers + alpha/bias staging (x2 buffers) + packed-word ring + epilogue transposition buffers
-    static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4 + kWordStages * WORD_TILE_BYTES + kStageOutBytes;
+    static constexpr int WORD_ROW_BYTES = 8 * WORD_KB;  // two words per k-block and column
+    static constexpr int WORD_TILE_BYTES = BN * WORD_ROW_BYTES * (TERNARY ? 2 : 1);
+    // barriers + alpha/bias staging (x2 buffers) + packed-word ring (+ epilogue transposition buffers)
+    static constexpr int AUX_BYTES = kAuxBarrierBytes + 4 * BN * 4 + kWordStages * WORD_TILE_BYTES + (MULTI ? kStageOutBytes : 0);
     static constexpr int RAW_STAGES = (kSmemLimit - 1024 - AUX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = RAW_STAGES > 6 ? 6 : RAW_STAGES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;  // + alignment slack
@@ -258,7 +266,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 // filter tap and 64 channels is ONE tiled TMA box of the channels-last copy [term][img][h][w][c] (the hardware
 // zero-fills the halo, the tensor map's element strides implement the convolution stride): no thread touches
 // the operands.
-template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC>
+template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_neg,
                                                               const __grid_constant__ CUtensorMap tmap_pos,
@@ -273,8 +281,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     constexpr bool TMA_B = BSRC != 0;      // the weight tile arrives by TMA instead of being unpacked here
     static_assert(!(ROWS && TMA_B), "TMA-fed weights take their activations by TMA or by the convolution gathers");
     static_assert(BSRC != 2 || !TERNARY, "expanded weights carry their zeros themselves");
-    using C = Cfg<BN, NPASS, TERNARY, BSRC, CONV>;
+    using C = Cfg<BN, NPASS, TERNARY, BSRC, CONV, MULTI>;
     constexpr int kWordStages = C::kWordStages;
+    constexpr int WORD_KB = C::WORD_KB;
+    static_assert(!MULTI || (AMODE == 0 && BSRC == 0), "the multi-destination epilogue belongs to the plain GEMM");
     static_assert(!DENSE || (NPASS == 2 && !TERNARY && !TERN_ACT), "dense weights use the two-term split on both sides");
     // Which operands arrive by TMA (signalled on full_a) and which are built by the build warps (full_b).
     constexpr bool kTmaOperands = !BUILT_A || TMA_B;
@@ -356,8 +366,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     ph0 = py * p.conv.pbh * p.conv.sh - p.conv.ph;
                 }
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!TMA_B && (kb & 1) == 0) {
-                        // Packed words of k-blocks kb and kb+1 for the BN columns of this tile
+                    if (!TMA_B && (kb % WORD_KB) == 0) {
+                        // Packed words of k-blocks kb .. kb + WORD_KB - 1 for the BN columns of this tile
                         // (rows past the end of the plane are zero-filled by TMA).
                         if (!ptx::mbar_wait(bar_empty_w + 8 * wstage, wphase ^ 1u, p.err_word, kErrWaitEmpty)) {
                             ok = false;
@@ -367,7 +377,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         const uint32_t wdst = word_ring + wstage * C::WORD_TILE_BYTES;
                         ptx::mbar_arrive_expect_tx(wbar, C::WORD_TILE_BYTES);
                         ptx::tma_load_2d(wdst, &tmap_neg, kb * 2, tn * BN, wbar);
-                        if (TERNARY) ptx::tma_load_2d(wdst + BN * 16, &tmap_pos, kb * 2, tn * BN, wbar);
+                        if (TERNARY) ptx::tma_load_2d(wdst + BN * C::WORD_ROW_BYTES, &tmap_pos, kb * 2, tn * BN, wbar);
                         if (++wstage == kWordStages) {
                             wstage = 0;
                             wphase ^= 1u;
@@ -484,6 +494,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         uint32_t phase = 0, wphase = 0;
         bool ok = true;
         uint4 wn = make_uint4(0u, 0u, 0u, 0u), wp = make_uint4(0u, 0u, 0u, 0u);
+        uint4 wn2 = make_uint4(0u, 0u, 0u, 0u);  // words of the third and fourth k-block of a 4-k-block tile
         // FAST: oldest stage whose copies are in flight and whose arrive is still owed, and how many are owed.
         constexpr int kCopyLag = C::STAGES >= 4 ? 2 : 1;
         int pending_stage = 0, pending_count = 0;
@@ -562,20 +573,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 }
             }
             for (int kb = 0; kb < p.num_kb; ++kb) {
-                if (!TMA_B && (kb & 1) == 0) {
-                    // Words of this and the next k-block: shared memory -> registers, then free the slot.
+                if (!TMA_B && (kb % WORD_KB) == 0) {
+                    // Words of this and the next k-block(s): shared memory -> registers, then free the slot.
                     if (!ptx::mbar_wait(bar_full_w + 8 * wstage, wphase, p.err_word, kErrWaitFullB)) {
                         ok = false;
                         break;
                     }
                     if (r < BN) {
-                        const uint32_t wt = word_ring + wstage * C::WORD_TILE_BYTES + r * 16;
+                        const uint32_t wt = word_ring + wstage * C::WORD_TILE_BYTES + r * C::WORD_ROW_BYTES;
                         wn = ptx::ld_shared_v4(wt);
-                        if (TERNARY) wp = ptx::ld_shared_v4(wt + BN * 16);
+                        if (WORD_KB == 4) wn2 = ptx::ld_shared_v4(wt + 16);
+                        if (TERNARY) wp = ptx::ld_shared_v4(wt + BN * C::WORD_ROW_BYTES);
                     }
                     // The slot may be refilled by TMA as soon as this arrive lands, so the loads above
                     // must have returned their data first: the arrive is made to depend on them.
-                    ptx::mbar_arrive_after(bar_empty_w + 8 * wstage, wn.x ^ wn.w ^ wp.x ^ wp.w);
+                    ptx::mbar_arrive_after(bar_empty_w + 8 * wstage, wn.x ^ wn.w ^ wp.x ^ wp.w ^ wn2.x ^ wn2.w);
                     if (++wstage == kWordStages) {
                         wstage = 0;
                         wphase ^= 1u;
@@ -612,7 +624,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 uint8_t* stage_ptr = base_ptr + stage * C::STAGE_BYTES;
                 if (!TMA_B && r < BN) {
                     uint8_t* row = stage_ptr + r * 128;
-                    const uint32_t nw[2] = {(kb & 1) ? wn.z : wn.x, (kb & 1) ? wn.w : wn.y};
+                    const uint4 wsel = (WORD_KB == 4 && (kb & 2)) ? wn2 : wn;
+                    const uint32_t nw[2] = {(kb & 1) ? wsel.z : wsel.x, (kb & 1) ? wsel.w : wsel.y};
                     const uint32_t pw[2] = {(kb & 1) ? wp.z : wp.x, (kb & 1) ? wp.w : wp.y};
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
@@ -819,7 +832,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         for (int j4 = 0; j4 < 8; ++j4)
                             __stcg(scratch + (c * 8 + j4) * kEpilogueThreads,
                                    make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]));
-                    } else if (p.num_out > 0) {
+                    } else if (MULTI && p.num_out > 0) {
                         const int64_t nc = n0 + c * 32;
                         const float* as = alpha_s + sbuf * BN + c * 32;
                         const float* bs = bias_s + sbuf * BN + c * 32;
@@ -1004,10 +1017,10 @@ inline int32_t make_out_map(EncodeTiledFn encode, float* base, int64_t M, int64_
 
 // Packed-word plane [N_pad][KW] uint32 -> box of 4 words (128 k) x BN columns, no swizzle.
 inline int32_t make_word_map(EncodeTiledFn encode, const uint32_t* words, int64_t KW, int64_t N_pad, int bn,
-                             CUtensorMap* out) {
+                             CUtensorMap* out, int words_per_row = 4) {
     const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(KW), static_cast<cuuint64_t>(N_pad)};
     const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(KW) * 4};
-    const cuuint32_t box[2] = {4, static_cast<cuuint32_t>(bn)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(words_per_row), static_cast<cuuint32_t>(bn)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult cr = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(words), gdim, gstride, box,
                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -1024,10 +1037,10 @@ inline void set_segments(tc::Params& p, int npass) {
     p.kb_per_seg = (p.num_kb + p.num_seg - 1) / p.num_seg;
 }
 
-template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC = 0>
+template <int BN, int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC = 0, bool MULTI = false>
 int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
-    using C = tc::Cfg<BN, NPASS, TERNARY, BSRC, tc::is_conv_mode(AMODE)>;
-    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>;
+    using C = tc::Cfg<BN, NPASS, TERNARY, BSRC, tc::is_conv_mode(AMODE), MULTI>;
+    auto kernel = tc::gemm_tc_kernel<BN, NPASS, TERNARY, AMODE, TERN_ACT, BSRC, MULTI>;
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
@@ -1039,14 +1052,17 @@ int32_t launch_tc(const TensorMaps& maps, const tc::Params& p, cudaStream_t st) 
     return launched(tc::is_conv_mode(AMODE) ? "gemm_tc_kernel<conv>" : "gemm_tc_kernel");
 }
 
-template <int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC = 0>
+template <int NPASS, bool TERNARY, int AMODE, bool TERN_ACT, int BSRC = 0, bool MULTI = false>
 int32_t dispatch_bn(int bn, const TensorMaps& maps, const tc::Params& p, cudaStream_t st) {
     switch (bn) {
-        case 256: return launch_tc<256, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>(maps, p, st);
-        case 128: return launch_tc<128, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>(maps, p, st);
-        default: return launch_tc<64, NPASS, TERNARY, AMODE, TERN_ACT, BSRC>(maps, p, st);
+        case 256: return launch_tc<256, NPASS, TERNARY, AMODE, TERN_ACT, BSRC, MULTI>(maps, p, st);
+        case 128: return launch_tc<128, NPASS, TERNARY, AMODE, TERN_ACT, BSRC, MULTI>(maps, p, st);
+        default: return launch_tc<64, NPASS, TERNARY, AMODE, TERN_ACT, BSRC, MULTI>(maps, p, st);
     }
 }
+
+// Words per row of the packed-word box that the kernel instantiation (plain GEMM, AMODE 0 or 3) expects.
+inline int gemm_words_per_row(bool ternary, bool multi) { return (!ternary && !multi) ? 8 : 4; }
 
 // Tensor map over bf16 terms laid out [terms][rows_pad][K_pad] (split activations or split dense weights):
 // box = 64 k x `box_rows` rows x 1 term, 128-byte swizzle.

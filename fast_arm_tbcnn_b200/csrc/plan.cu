@@ -128,7 +128,7 @@ int32_t tbn_gemm_plan_bn(int64_t M, int64_t N, int32_t preferred) {
 }
 
 int32_t tbn_gemm_plan_override(int32_t kernel, int32_t bn, int32_t group_m, int32_t fused_split) {
-    TBN_REQUIRE(kernel >= -1 && kernel <= 1, TBN_INVALID_ARGUMENT, "tbn_gemm_plan_override: kernel must be -1, 0 or 1");
+    TBN_REQUIRE(kernel >= -1 && kernel <= 2, TBN_INVALID_ARGUMENT, "tbn_gemm_plan_override: kernel must be -1, 0, 1 or 2");
     TBN_REQUIRE(bn == -1 || bn == 64 || bn == 128 || bn == 256, TBN_INVALID_ARGUMENT,
                 "tbn_gemm_plan_override: bn must be -1, 64, 128 or 256");
     TBN_REQUIRE(group_m == -1 || (group_m >= 1 && group_m <= 1024), TBN_INVALID_ARGUMENT,

@@ -9,7 +9,8 @@
 namespace tbn_cuda {
 
 struct GemmPlan {
-    int kernel;       // 0: tcgen05 tensor-core kernel (two bf16 terms), 1: CUDA-core add/subtract-by-sign kernel
+    int kernel;       // 0: tcgen05 tensor-core kernel, 1: CUDA-core add/subtract-by-sign kernel,
+                      // 2: tcgen05 on CTA pairs (cta_group::2, 256 x 256 tiles; large products)
     int bn;           // column tile of the tensor-core kernel: 64, 128 or 256
     int group_m;      // rasterisation group: m-tiles that share one sweep over the column tiles
     int fused_split;  // 1: the GEMM kernel reads the fp32 rows and splits them in registers (no separate split pass)

@@ -83,6 +83,8 @@ def main():
         for bn in bns:
             for fused in ((0, 1) if (N <= 1024 and K % 4 == 0) else (0,)):
                 timings[("tcgen05", bn, 4, fused)] = time_variant(M, N, K, 0, bn, 4, fused)
+        if M >= 256 and N >= 256:   # CTA pairs (cta_group::2): 256 x 256 tiles
+            timings[("tcgen05-pair", 256, 4, 0)] = time_variant(M, N, K, 2, -1, 4, 0)
         best = min((k for k in timings if k[0] == "tcgen05"), key=lambda k: timings[k])
         if (M + 127) // 128 > 1 and (N + best[1] - 1) // best[1] > 1:
             for group in (1, 2, 8, 16):
@@ -102,13 +104,13 @@ def main():
                 if args.quick and M * N * K > 2 ** 40:
                     continue
                 best, timings = sweep(M, N, K)
-                kernel = 1 if best[0] == "cuda-core" else 0
-                bn, group, fused = (best[1], best[2], best[3]) if kernel == 0 else (64, 4, 0)
+                kernel = {"tcgen05": 0, "cuda-core": 1, "tcgen05-pair": 2}[best[0]]
+                bn, group, fused = (best[1], best[2], best[3]) if kernel != 1 else (64, 4, 0)
                 lines.append(f"{{{mi}, {ni}, {ki}, {kernel}, {bn}, {group}, {fused}}},")
-                allv = "; ".join(f"{k[0]}" + (f" bn{k[1]} g{k[2]}" + (" fused" if k[3] else "") if k[0] == "tcgen05" else "") +
+                allv = "; ".join(f"{k[0]}" + (f" bn{k[1]} g{k[2]}" + (" fused" if k[3] else "") if k[0] != "cuda-core" else "") +
                                  f" {v:.4f}" for k, v in sorted(timings.items(), key=lambda kv: kv[1]))
                 report.append(f"| {M_CLASSES[mi]} | {N_CLASSES[ni]} | {K_CLASSES[ki]} | {M}x{N}x{K} | {best[0]}"
-                              + (f" bn{bn} g{group}" + (" fused" if fused else "") if kernel == 0 else "") +
+                              + (f" bn{bn} g{group}" + (" fused" if fused else "") if kernel != 1 else "") +
                               f" | {timings[best]:.4f} | {allv} |")
                 sys.stderr.write(report[-1] + "\n")
     header = ("// {class of M, class of N, class of K, kernel, bn, group_m, fused_split}; written by fast_arm_tbcnn_b200/tune.py.\n"
@@ -140,8 +142,8 @@ def main():
         best, timings = sweep(M, N, K)
         kernel, bn, group, fused = ent
         bn = L.wave_model_bn(M, N, bn)   # the adjustment the library applies to the class's tile
-        mine = time_variant(M, N, K, kernel, bn if kernel == 0 else -1, group if kernel == 0 else -1, fused if kernel == 0 else -1)
-        name = "cuda-core" if kernel else f"tcgen05 bn{bn} g{group}" + (" fused" if fused else "")
+        mine = time_variant(M, N, K, kernel, bn if kernel == 0 else -1, group if kernel != 1 else -1, fused if kernel == 0 else -1)
+        name = "cuda-core" if kernel == 1 else ("tcgen05-pair" if kernel == 2 else f"tcgen05 bn{bn} g{group}" + (" fused" if fused else ""))
         report.append(f"| {M}x{N}x{K} | {name} | {mine:.4f} | {best[0]} bn{best[1]} g{best[2]}{' fused' if best[3] else ''} | "
                       f"{timings[best]:.4f} | {mine / timings[best]:.2f} |")
         sys.stderr.write(report[-1] + "\n")

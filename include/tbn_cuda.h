@@ -124,7 +124,8 @@ int32_t tbn_cuda_set_fused_split(int32_t value);
 /* Per-shape kernel choice of TBN_MODE_AUTO.  Stands in for TilingParams / auto_tune_gemm of the reference
  * (GeMM/05-final/GeMM.hpp:16-43, tbn-runtime/src/operators/gemm.cpp:524-536): instead of tile sizes handed in by
  * the caller, a table measured on the GPU and compiled into the library maps the class of (M, N, K) to
- *   kernel       0 = tcgen05 tensor-core kernel, 1 = CUDA-core add/subtract-by-sign kernel
+ *   kernel       0 = tcgen05 tensor-core kernel, 1 = CUDA-core add/subtract-by-sign kernel, 2 = tcgen05 on CTA pairs
+ *                (cta_group::2: one 256 x 256 tile per pair of SMs, each unpacking half of the weight tile)
  *   bn           column tile of the tensor-core kernel (64 / 128 / 256)
  *   group_m      rasterisation group: m-tiles that share one sweep over the column tiles (L2 reuse)
  *   fused_split  1 = the kernel splits the fp32 activation rows itself instead of a separate pass

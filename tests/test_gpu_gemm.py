@@ -428,3 +428,45 @@ def test_bounded_wait_runs_out_and_is_reported(tbn):
     assert float((out.double() - exact).norm() / exact.norm()) <= 5e-6
     with pytest.raises(tbn.TbnError):
         tbn.check(h.tbn_cuda_set_wait_limit_ns(10))
+
+
+@pytest.mark.parametrize("shape", [(256, 128, 256), (512, 640, 512), (300, 200, 300), (1000, 4100, 520), (128, 64, 64),
+                                   (4096, 8192, 1024), (2304, 16384, 768)])
+@pytest.mark.parametrize("ternary", [False, True])
+def test_cta_pair_kernel_equals_single_cta_kernel(tbn, shape, ternary):
+    """The cta_group::2 kernel (pairs of CTAs, 256 x 256 tiles, each CTA unpacking half of the weight tile) gives
+    the same bits as the one-CTA kernel: ragged M and N, an odd number of 128-row tiles (the last pair's second CTA
+    works on rows past the matrix), K with several accumulation segments, binary and ternary weights, with bias and
+    ReLU; and it is within the fp32 bar of an fp64 evaluation."""
+    import torch
+    M, K, N = shape
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    A = torch.randn((M, K), generator=g, device="cuda")
+    W = torch.randn((K, N), generator=g, device="cuda")
+    bias = torch.randn(N, generator=g, device="cuda")
+    if ternary:
+        _, pos, neg, alpha = tbn.lib.quant_pack_ternary(W, -0.3, 0.3, want_codes=False)
+    else:
+        neg, alpha = tbn.lib.quant_pack_binary(W)
+        pos = None
+    run = lambda mode, epi: tbn.lib.gemm_fxb(A, neg, N, pos=pos, alpha=alpha, bias=bias, mode=mode, epilogue=epi)
+    for mode in (tbn.MODE_TC_BF16X2, tbn.MODE_TC_BF16X1):
+        try:
+            tbn.lib.gemm_plan_override(kernel=0, fused_split=0)
+            single = run(mode, tbn.EPI_RELU).clone()
+            tbn.lib.sync()
+            tbn.lib.gemm_plan_override(kernel=2, fused_split=0)
+            paired = run(mode, tbn.EPI_RELU)
+            tbn.lib.sync()
+        finally:
+            tbn.lib.gemm_plan_override()
+        assert torch.equal(paired, single), mode
+    sign = torch.where(W > 0.3, 1.0, torch.where(W < -0.3, -1.0, 0.0)) if ternary else torch.where(W > 0, 1.0, -1.0)
+    try:
+        tbn.lib.gemm_plan_override(kernel=2, fused_split=0)
+        out = run(tbn.MODE_TC_BF16X2, 0)
+        tbn.lib.sync()
+    finally:
+        tbn.lib.gemm_plan_override()
+    exact = (A.double() @ sign.double()) * alpha.double()[None, :] + bias.double()[None, :]
+    assert float((out.double() - exact).norm() / exact.norm()) <= 1e-5
