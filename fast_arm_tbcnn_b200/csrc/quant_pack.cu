@@ -10,6 +10,7 @@
 // K_pad = ceil128(K), N_pad = ceil8(N); padding bits are 0.
 // Comparisons are IEEE (no flush-to-zero on the compare, NaN compares false).
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -166,18 +167,23 @@ __global__ void __launch_bounds__(128) pack_kn_vec4_kernel(const float* __restri
 // Jobs are numbered strip-fastest, so CTAs running at the same time read neighbouring 2 KB pieces of the same
 // rows.  The partial |w| sums per 128-row chunk are accumulated in the same order as in the other kernels.
 constexpr int kPackStages = 3;
-constexpr int kPackTileRows = 32, kPackBoxCols = 256, kPackJobCols = 512;
-constexpr int kPackBoxBytes = kPackTileRows * kPackBoxCols * 4;
-constexpr int kPackTileBytes = 2 * kPackBoxBytes;
-constexpr int kPackConsumers = 512;  // one per column of a job
+constexpr int kPackBoxCols = 256;
+constexpr int kPackTileBytes = 64 * 1024;
+constexpr int kPackConsumers = 512;  // one per column (CPT = 1) or per pair of columns 512 apart (CPT = 2) of a job
 constexpr int kPackSmemBytes = kPackStages * kPackTileBytes + 1024 + 256;
 
-template <bool TERNARY>
+// CPT = columns per consumer thread.  The job is 128 (k) x 512 CPT (n); a tile is 32 / CPT rows of it (64 KB either
+// way): CPT = 2 halves the rows per tile and doubles their length, so that every row piece read from HBM is 4 KB
+// contiguous instead of 2 KB.
+template <bool TERNARY, int CPT>
 __global__ void __launch_bounds__(kPackConsumers + 32, 1)
 pack_kn_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, int64_t K, int64_t N, float lo, float hi, int ge,
                    uint32_t* __restrict__ neg_words, uint32_t* __restrict__ pos_words, int64_t KW, int64_t N_pad,
                    float* __restrict__ part_sum, float* __restrict__ part_cnt, int64_t strips, int64_t jobs,
                    int* err_word) {
+    constexpr int kTileRows = 32 / CPT, kBoxes = 2 * CPT, kBoxBytes = kTileRows * kPackBoxCols * 4;
+    constexpr int kJobCols = 512 * CPT, kTilesPerJob = kChunkK / kTileRows;
+    static_assert(kBoxes * kBoxBytes == kPackTileBytes, "a tile is 64 KB");
     extern __shared__ uint8_t pack_smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(pack_smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -192,6 +198,9 @@ pack_kn_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, int64_t K, int64_
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&tmap_w);
     }
+    // Lets the blocks of alpha_finalize_kernel (launched next in the stream) take their places now; they wait for
+    // this whole grid to complete before they read anything.
+    asm volatile("griddepcontrol.launch_dependents;");
     __syncthreads();
 
     if (threadIdx.x >= kPackConsumers) {
@@ -202,18 +211,19 @@ pack_kn_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, int64_t K, int64_
             for (int64_t job = blockIdx.x; job < jobs; job += gridDim.x) {
                 const int64_t strip = job % strips, chunk = job / strips;
                 bool ok = true;
-                for (int sub = 0; sub < 4 && ok; ++sub) {
+                for (int sub = 0; sub < kTilesPerJob && ok; ++sub) {
                     if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, err_word, kErrPackWaitEmpty)) {
                         ok = false;
                         break;
                     }
                     const uint32_t bar = bar_full + 8 * stage;
                     const uint32_t dst = base + stage * kPackTileBytes;
-                    const int x = static_cast<int>(strip * kPackJobCols);
-                    const int y = static_cast<int>(chunk * kChunkK + sub * kPackTileRows);
+                    const int x = static_cast<int>(strip * kJobCols);
+                    const int y = static_cast<int>(chunk * kChunkK + sub * kTileRows);
                     ptx::mbar_arrive_expect_tx(bar, kPackTileBytes);
-                    ptx::tma_load_2d(dst, &tmap_w, x, y, bar);                       // out-of-range parts arrive as zeros
-                    ptx::tma_load_2d(dst + kPackBoxBytes, &tmap_w, x + kPackBoxCols, y, bar);
+#pragma unroll
+                    for (int b = 0; b < kBoxes; ++b)   // out-of-range parts arrive as zeros
+                        ptx::tma_load_2d(dst + b * kBoxBytes, &tmap_w, x + b * kPackBoxCols, y, bar);
                     if (++stage == kPackStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -225,59 +235,83 @@ pack_kn_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, int64_t K, int64_
         return;
     }
 
-    // -------------------------------------------------------------------- consumers: one column of the job per thread
+    // -------------------------------------------------------------------- consumers
     const int t = threadIdx.x;
-    const int tile_off = (t >> 8) * (kPackBoxBytes / 4) + (t & 255);  // box of this column, column inside the box
+    // Column i of this thread is job column t + 512 i: box (t >> 8) + 2 i, column t & 255 inside the box.
+    const int tile_off = (t >> 8) * (kBoxBytes / 4) + (t & 255);
     int stage = 0;
     uint32_t phase = 0;
     for (int64_t job = blockIdx.x; job < jobs; job += gridDim.x) {
         const int64_t strip = job % strips, chunk = job / strips;
-        const int64_t n = strip * kPackJobCols + t;
-        uint32_t negw[4], posw[4];
-        float sum = 0.f, cnt = 0.f;
+        uint32_t negw[CPT][4], posw[CPT][4];
+        float sum[CPT], cnt[CPT];
 #pragma unroll
-        for (int sub = 0; sub < 4; ++sub) {
+        for (int i = 0; i < CPT; ++i) sum[i] = cnt[i] = 0.f;
+        uint32_t nb[CPT], pb[CPT];
+#pragma unroll
+        for (int sub = 0; sub < kTilesPerJob; ++sub) {
             if (!ptx::mbar_wait(bar_full + 8 * stage, phase, err_word, kErrPackWaitFull)) return;
             const float* tile = tiles + stage * (kPackTileBytes / 4) + tile_off;
-            const int64_t k0 = chunk * kChunkK + sub * kPackTileRows;
-            const int rows = static_cast<int>(min(static_cast<int64_t>(kPackTileRows), K - k0));  // <= 0 past the end
-            uint32_t nb = 0u, pb = 0u;
+            const int64_t k0 = chunk * kChunkK + sub * kTileRows;
+            const int rows = static_cast<int>(min(static_cast<int64_t>(kTileRows), K - k0));  // <= 0 past the end
+            if (sub % CPT == 0) {
 #pragma unroll
-            for (int r = 0; r < kPackTileRows; ++r) {
-                const float e = tile[r * kPackBoxCols];
-                if (r < rows) {
-                    const uint32_t c = classify<TERNARY>(e, lo, hi, ge);
-                    nb |= (c & 1u) << r;
-                    if (TERNARY) {
-                        pb |= (c >> 1) << r;
-                        if (c) {
-                            sum += fabsf(e);
-                            cnt += 1.0f;
+                for (int i = 0; i < CPT; ++i) nb[i] = pb[i] = 0u;
+            }
+            const int bit0 = (sub % CPT) * kTileRows;
+#pragma unroll
+            for (int r = 0; r < kTileRows; ++r) {
+#pragma unroll
+                for (int i = 0; i < CPT; ++i) {
+                    const float e = tile[2 * i * (kBoxBytes / 4) + r * kPackBoxCols];
+                    if (r < rows) {
+                        const uint32_t c = classify<TERNARY>(e, lo, hi, ge);
+                        nb[i] |= (c & 1u) << (bit0 + r);
+                        if (TERNARY) {
+                            pb[i] |= (c >> 1) << (bit0 + r);
+                            if (c) {
+                                sum[i] += fabsf(e);
+                                cnt[i] += 1.0f;
+                            }
+                        } else {
+                            sum[i] += fabsf(e);
                         }
-                    } else {
-                        sum += fabsf(e);
                     }
                 }
             }
             // The stage goes back to the producer only after every value read above has arrived in registers:
             // the arrive is made to depend on them.
-            ptx::mbar_arrive_after(bar_empty + 8 * stage, nb ^ pb ^ __float_as_uint(sum));
+            uint32_t dep = 0u;
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) dep ^= nb[i] ^ pb[i] ^ __float_as_uint(sum[i]);
+            ptx::mbar_arrive_after(bar_empty + 8 * stage, dep);
             if (++stage == kPackStages) {
                 stage = 0;
                 phase ^= 1u;
             }
-            negw[sub] = nb;
-            posw[sub] = pb;
+            if (sub % CPT == CPT - 1) {
+#pragma unroll
+                for (int i = 0; i < CPT; ++i) {
+                    negw[i][sub / CPT] = nb[i];
+                    posw[i][sub / CPT] = pb[i];
+                }
+            }
         }
-        if (n >= N_pad) continue;
-        const bool real = n < N;  // columns N .. N_pad-1 are padding: all bits 0
-        const int64_t widx = n * KW + chunk * 4;
-        *reinterpret_cast<uint4*>(neg_words + widx) = real ? make_uint4(negw[0], negw[1], negw[2], negw[3]) : make_uint4(0u, 0u, 0u, 0u);
-        if (TERNARY)
-            *reinterpret_cast<uint4*>(pos_words + widx) = real ? make_uint4(posw[0], posw[1], posw[2], posw[3]) : make_uint4(0u, 0u, 0u, 0u);
-        if (part_sum && real) {
-            part_sum[chunk * N + n] = sum;
-            if (TERNARY) part_cnt[chunk * N + n] = cnt;
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int64_t n = strip * kJobCols + t + 512 * i;
+            if (n >= N_pad) continue;
+            const bool real = n < N;  // columns N .. N_pad-1 are padding: all bits 0
+            const int64_t widx = n * KW + chunk * 4;
+            *reinterpret_cast<uint4*>(neg_words + widx) =
+                real ? make_uint4(negw[i][0], negw[i][1], negw[i][2], negw[i][3]) : make_uint4(0u, 0u, 0u, 0u);
+            if (TERNARY)
+                *reinterpret_cast<uint4*>(pos_words + widx) =
+                    real ? make_uint4(posw[i][0], posw[i][1], posw[i][2], posw[i][3]) : make_uint4(0u, 0u, 0u, 0u);
+            if (part_sum && real) {
+                part_sum[chunk * N + n] = sum[i];
+                if (TERNARY) part_cnt[chunk * N + n] = cnt[i];
+            }
         }
     }
 }
@@ -334,15 +368,42 @@ __global__ void __launch_bounds__(128) pack_nk_kernel(const float* __restrict__ 
 }
 
 // alpha[n] = (sum over chunks, in chunk order) / (K or number of non-zero weights).
-__global__ void alpha_finalize_kernel(const float* __restrict__ part_sum, const float* __restrict__ part_cnt,
-                                      int64_t chunks, int64_t N, int64_t K, float* __restrict__ alpha) {
-    const int64_t n = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (n >= N) return;
+// Launched with programmatic stream serialisation: its blocks may become resident while the pack kernel before it in
+// the stream still runs (the streaming pack kernel releases them at its start) and wait here until that grid has
+// completed and its partial sums are visible, which takes the launch latency off the critical path.
+// A block owns 32 columns.  Its sixteen warps fetch 128 chunks' partial sums at once into shared memory (a serial
+// loop over chunks per column is bound by memory latency: one round trip per few chunks), then one warp adds them
+// per column in chunk order.
+constexpr int kFinalizeCols = 32, kFinalizeWarps = 16, kFinalizeBatch = 128;
+__global__ void __launch_bounds__(kFinalizeCols * kFinalizeWarps)
+alpha_finalize_kernel(const float* __restrict__ part_sum, const float* __restrict__ part_cnt, int64_t chunks, int64_t N,
+                      int64_t K, float* __restrict__ alpha) {
+    __shared__ float sum_s[kFinalizeBatch][kFinalizeCols];
+    __shared__ float cnt_s[kFinalizeBatch][kFinalizeCols];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t n = static_cast<int64_t>(blockIdx.x) * kFinalizeCols + lane;
     float s = 0.0f, c = 0.0f;
-    for (int64_t i = 0; i < chunks; ++i) {
-        s += part_sum[i * N + n];
-        if (part_cnt) c += part_cnt[i * N + n];
+    for (int64_t c0 = 0; c0 < chunks; c0 += kFinalizeBatch) {
+        const int in_batch = static_cast<int>(min(static_cast<int64_t>(kFinalizeBatch), chunks - c0));
+#pragma unroll
+        for (int u = 0; u < kFinalizeBatch / kFinalizeWarps; ++u) {
+            const int i = u * kFinalizeWarps + warp;
+            if (i < in_batch && n < N) {
+                sum_s[i][lane] = __ldcg(part_sum + (c0 + i) * N + n);
+                if (part_cnt) cnt_s[i][lane] = __ldcg(part_cnt + (c0 + i) * N + n);
+            }
+        }
+        __syncthreads();
+        if (warp == 0 && n < N) {
+            for (int i = 0; i < in_batch; ++i) {
+                s += sum_s[i][lane];
+                if (part_cnt) c += cnt_s[i][lane];
+            }
+        }
+        __syncthreads();
     }
+    if (warp != 0 || n >= N) return;
     if (part_cnt) alpha[n] = c > 0.0f ? __fdiv_rn(s, c) : 0.0f;
     else alpha[n] = __fdiv_rn(s, static_cast<float>(K));
 }
@@ -426,18 +487,21 @@ int32_t quant_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t 
     if (stream) {
         EncodeTiledFn encode = encode_tiled_fn();
         TBN_REQUIRE(encode != nullptr, TBN_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+        // Two columns per consumer thread (4 KB row pieces) once a job of 1024 columns fits the matrix at least twice.
+        const int cpt = N_pad >= 2048 ? 2 : 1;
         CUtensorMap tmap;
         const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K)};
         const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ldw) * 4};
-        const cuuint32_t box[2] = {kPackBoxCols, kPackTileRows};
+        const cuuint32_t box[2] = {kPackBoxCols, static_cast<cuuint32_t>(32 / cpt)};
         const cuuint32_t estr[2] = {1, 1};
         const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(d_w), gdim, gstride, box, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         TBN_REQUIRE(cr == CUDA_SUCCESS, TBN_CUDA_ERROR,
                     "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(cr)));
-        const int64_t strips = (N_pad + kPackJobCols - 1) / kPackJobCols, jobs = strips * chunks;
-        auto kernel = pack_kn_tma_kernel<TERNARY>;
+        const int64_t job_cols = 512 * cpt;
+        const int64_t strips = (N_pad + job_cols - 1) / job_cols, jobs = strips * chunks;
+        auto kernel = cpt == 2 ? pack_kn_tma_kernel<TERNARY, 2> : pack_kn_tma_kernel<TERNARY, 1>;
         TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPackSmemBytes));
         const int grid = static_cast<int>(std::min<int64_t>(jobs, std::max(sm_count(), 1)));
         kernel<<<grid, kPackConsumers + 32, kPackSmemBytes, st>>>(tmap, K, N, lo, hi, ge, d_neg, d_pos, KW, N_pad, part_sum,
@@ -458,8 +522,17 @@ int32_t quant_pack(const float* d_w, int64_t K, int64_t N, int64_t ldw, int32_t 
     int32_t rc = launched(TERNARY ? "pack_kernel<ternary>" : "pack_kernel<binary>");
     if (rc) return rc;
     if (d_alpha) {
-        alpha_finalize_kernel<<<static_cast<unsigned>((N + 127) / 128), 128, 0, st>>>(part_sum, part_cnt, chunks, N, K,
-                                                                                     d_alpha);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>((N + kFinalizeCols - 1) / kFinalizeCols));
+        cfg.blockDim = dim3(kFinalizeCols * kFinalizeWarps);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        TBN_CUDA_TRY(cudaLaunchKernelEx(&cfg, alpha_finalize_kernel, static_cast<const float*>(part_sum),
+                                        static_cast<const float*>(part_cnt), chunks, N, K, d_alpha));
         rc = launched("alpha_finalize_kernel");
     }
     return rc;
