@@ -229,6 +229,27 @@ FoldGeom fold_geometry(int64_t N, int64_t C, int64_t H, int64_t W, int64_t kh, i
     return g;
 }
 
+// Patch of output pixels that one 128-row tile covers: pbw columns x pbh rows (x pbi whole images when an image fits).
+// Among the widths that divide the output width (and the full width), the one that needs the fewest tiles per image;
+// ties go to the wider patch (longer contiguous runs in the NCHW result).  112 x 112 outputs: 16 x 8 (98 full tiles)
+// instead of 112 x 1 (112 tiles at 7/8 occupancy).
+inline void choose_patch(int64_t OW, int64_t OH, int64_t N, int64_t& pbw, int64_t& pbh, int64_t& pbi) {
+    pbw = std::min<int64_t>(OW, tc::BM);
+    pbh = std::min<int64_t>(OH, tc::BM / pbw);
+    int64_t best = ((OW + pbw - 1) / pbw) * ((OH + pbh - 1) / pbh);
+    for (int64_t w = pbw - 1; w >= 8; --w) {
+        if (OW % w != 0) continue;
+        const int64_t h = std::min<int64_t>(OH, tc::BM / w);
+        const int64_t tiles = (OW / w) * ((OH + h - 1) / h);
+        if (tiles < best) {
+            best = tiles;
+            pbw = w;
+            pbh = h;
+        }
+    }
+    pbi = (pbw == OW && pbh == OH) ? std::max<int64_t>(1, std::min<int64_t>(tc::BM / (pbw * pbh), N)) : 1;
+}
+
 int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float hi, bool allow_fold = true) {
     TBN_REQUIRE(a.N > 0 && a.C > 0 && a.H > 0 && a.W > 0 && a.M_out > 0 && a.kh > 0 && a.kw > 0, TBN_INVALID_SHAPE,
                 "conv2d: dimensions must be positive");
@@ -286,9 +307,8 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
     // Folded form: its activation tensor map (overlapping windows) is encoded before anything is launched; if the
     // driver refuses it, or the workspace only covers the gather path, the element-gather path runs instead.
     CUtensorMap fold_map;
-    const int64_t fold_pbw = std::min<int64_t>(OW, tc::BM), fold_pbh = std::min<int64_t>(OH, tc::BM / fold_pbw);
-    const int64_t fold_pbi =
-        (fold_pbw == OW && fold_pbh == OH) ? std::max<int64_t>(1, std::min<int64_t>(tc::BM / (fold_pbw * fold_pbh), a.N)) : 1;
+    int64_t fold_pbw, fold_pbh, fold_pbi;
+    choose_patch(OW, OH, a.N, fold_pbw, fold_pbh, fold_pbi);
     if (fold.ok) {
         const int64_t t_stride = a.N * fold.rows * fold.Qp * 16;
         // Positions (overlapping 64-element windows, 16 elements apart) x folded rows x images x terms.
@@ -471,9 +491,8 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
         return dispatch_bn<2, false, 4, false, 2>(bn, maps, p, a.st);
     }
     if (fast) {
-        const int64_t pbw = std::min<int64_t>(OW, tc::BM);
-        const int64_t pbh = std::min<int64_t>(OH, tc::BM / pbw);
-        const int64_t pbi = (pbw == OW && pbh == OH) ? std::max<int64_t>(1, std::min<int64_t>(tc::BM / (pbw * pbh), a.N)) : 1;
+        int64_t pbw, pbh, pbi;
+        choose_patch(OW, OH, a.N, pbw, pbh, pbi);
         // Row mode (conv_rows.cuh): stride-1 convolutions with at most three filter columns whose tiles are no
         // emptier than the patch tiles below.  TBN_CONV_ROWS=0 in the environment keeps the patch-mode kernel
         // (for A/B measurements).

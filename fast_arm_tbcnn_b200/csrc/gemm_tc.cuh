@@ -173,7 +173,14 @@ struct Cfg {
     static constexpr int RAW_STAGES = (kSmemLimit - 1024 - AUX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = RAW_STAGES > 6 ? 6 : RAW_STAGES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;  // + alignment slack
-    static constexpr int TMEM_COLS = 2 * BN;
+    // Dense weights with BN <= 128: one instruction multiplies the high activation term with the high AND the low
+    // weight tile (they lie one behind the other in shared memory = one K-major operand of 2 BN rows), so that an
+    // accumulator is 2 BN columns wide and the epilogue adds its halves.  Two instructions per k-step instead of three;
+    // what an instruction costs at these widths is mostly its operand fetch, and the activation tile is fetched twice
+    // instead of three times.
+    static constexpr bool DENSE_WIDE = DENSE && BN <= 128;
+    static constexpr int ACC_COLS = DENSE_WIDE ? 2 * BN : BN;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;
     static_assert(STAGES >= 2, "need at least a double-buffered pipeline");
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns must be a power of two");
     static_assert(B_TILE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
@@ -443,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * C::ACC_COLS);
                     const int kb_begin = seg * p.kb_per_seg;
                     const int kb_end = min(p.num_kb, kb_begin + p.kb_per_seg);
                     for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -458,7 +465,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         const uint32_t a_addr = b_addr + C::B_BYTES;
                         // Binary/ternary weights: every activation term against the one exact weight tile.
                         // Dense weights: hi*hi + hi*lo + lo*hi (the lo*lo term is below fp32 resolution).
-                        constexpr int kPairs = DENSE ? 3 : NPASS;
+                        if constexpr (C::DENSE_WIDE) {
+                            const uint32_t idesc_wide = ptx::umma_idesc_bf16_f32(BM, 2 * BN);
+#pragma unroll
+                            for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {  // hi x [hi ; lo] -> columns [0, 2 BN)
+                                const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr + k4 * UMMA_K * 2);
+                                const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * UMMA_K * 2);
+                                ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc_wide, (kb != kb_begin || k4 != 0) ? 1u : 0u);
+                            }
+#pragma unroll
+                            for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {  // lo x hi -> columns [0, BN)
+                                const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr + A_TILE_BYTES + k4 * UMMA_K * 2);
+                                const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * UMMA_K * 2);
+                                ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, 1u);
+                            }
+                        }
+                        constexpr int kPairs = C::DENSE_WIDE ? 0 : (DENSE ? 3 : NPASS);
 #pragma unroll
                         for (int pr = 0; pr < kPairs; ++pr) {
                             const int qa = DENSE ? (pr == 2 ? 1 : 0) : pr;
@@ -810,11 +832,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     if (n0 + c * 32 >= p.N) break;  // columns past the matrix: nothing to read, add or store
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                           static_cast<uint32_t>(buf * BN + c * 32), r);
-                    ptx::tmem_ld_wait();
+                                           static_cast<uint32_t>(buf * C::ACC_COLS + c * 32), r);
                     float v[32];
+                    if constexpr (C::DENSE_WIDE) {
+                        uint32_t r2[32];  // the hi x lo products of the same columns
+                        ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                               static_cast<uint32_t>(buf * C::ACC_COLS + BN + c * 32), r2);
+                        ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(__uint_as_float(r[j]), __uint_as_float(r2[j]));
+                    } else {
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    }
                     if (!first) {
                         // Add the earlier segments (fp32, round to nearest).  Slot layout
                         // [column group][thread] keeps each warp access contiguous.
