@@ -562,6 +562,34 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                         }
                         const bool resident = st_res >= 2;
                         rp.nstages = resident ? st_res : st_str;
+                        // Three filter columns as one 192-column instruction (conv_rows.cuh, WIDE): 64 output channels,
+                        // resident filters.  TBN_CONV_WIDE=0 in the environment keeps one instruction per filter tap.
+                        static const bool wide_enabled = [] {
+                            const char* v = std::getenv("TBN_CONV_WIDE");
+                            return !(v && v[0] == '0');
+                        }();
+                        const int64_t qpr = (OW + rows::kQuarterOutputs - 1) / rows::kQuarterOutputs;
+                        const int64_t wide_rows = (qpr == 1 || qpr == 2 || qpr == 4) ? 4 / qpr : 0;  // output rows per tile
+                        if (wide_enabled && bn == 64 && N == 64 && a.kw == rows::kMaxTaps && resident && wide_rows > 0 &&
+                            (OH + wide_rows - 1) / wide_rows * 4 <= (OH + rpbh - 1) / rpbh * 5) {  // at most a quarter more tiles
+                            const int st_wide = one_term ? rows::stages_that_fit<64, 1, true, true>(rp.n_btiles)
+                                                         : rows::stages_that_fit<64, 2, true, true>(rp.n_btiles);
+                            CUtensorMap map_q;  // one lane quarter: 32 pixels of one input row, 64 channels
+                            const cuuint32_t qbox[5] = {tc::BK, 32, 1, 1, 1};
+                            const CUresult qr = encode(&map_q, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, xs,
+                                                       gdim, gstride, qbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                            if (st_wide >= 2 && qr == CUDA_SUCCESS && a.N * ((OH + wide_rows - 1) / wide_rows) < (1LL << 31)) {
+                                rp.nstages = st_wide;
+                                rp.qpr = static_cast<int>(qpr);
+                                rp.pbh = static_cast<int>(wide_rows);
+                                rp.tiles_per_image = static_cast<int>((OH + wide_rows - 1) / wide_rows);
+                                rp.tiles_m = static_cast<int>(a.N * rp.tiles_per_image);
+                                rp.a_box_bytes = static_cast<int>(npass * tc::BM * 128);
+                                return one_term ? rows::launch<64, 1, true, true>(map_q, maps.neg, rp, a.st)
+                                                : rows::launch<64, 2, true, true>(map_q, maps.neg, rp, a.st);
+                            }
+                        }
                         if (rp.nstages >= 2) {
                             if (bn == 64) {
                                 if (one_term) return resident ? rows::launch<64, 1, true>(map_x, maps.neg, rp, a.st) : rows::launch<64, 1, false>(map_x, maps.neg, rp, a.st);

@@ -14,6 +14,18 @@
 //     pixel index within the pitch is >= OW compute garbage that is never stored;
 //   * RESIDENT: when all filters fit (N <= BN and K_pad * BN * 2 bytes beside two activation stages), the expanded
 //     +-1 filters are loaded into shared memory once per CTA and stay there for all its tiles.
+//   * WIDE (BN = 64, three filter columns, resident filters): what a tcgen05.mma costs at these widths is mostly the
+//     fetch of its operands (measured: about 100 cycles at N = 64 against 32 of arithmetic), and the three taps of a
+//     filter row read the same activation rows.  So the three filter-column tiles of a filter row (kept one behind
+//     the other in shared memory) are ONE operand of 192 rows, multiplied with the UNSHIFTED activation window:
+//     E[r][tj] = A[r] . W[ti][tj] for all three tj at once, a third of the instructions, each fetching the
+//     activations once instead of three times.  The shift moves into the epilogue: out[r] = E[r][0] + E[r+1][1] +
+//     E[r+2][2], rows r+1 and r+2 coming from the neighbouring lanes by shuffle.  So that no row is ever needed from
+//     another warp (a shared-memory exchange plus a barrier per chunk cost more than the instructions saved:
+//     0.35 ms against 0.23 ms without it), the tile is laid out by TMEM lane quarters: each 32-row quarter is a box
+//     of its own -- 32 consecutive input pixels of one image row, the first at output column 30 k - pad -- and
+//     yields 30 output pixels; `qpr` = ceil(OW / 30) quarters cover an output row, 4 / qpr rows make a tile.
+//     (64x56x56 -> 64 at batch 512: 0.23 ms against 0.38 ms with one instruction per tap.)
 // Everything else follows gemm_tc_kernel: one persistent 448-thread CTA per SM, warp 0 issues TMA, warp 1 issues
 // tcgen05.mma into a double-buffered TMEM accumulator, twelve warps drain it (alpha / bias / residual / ReLU, NCHW
 // fp32 and / or channels-last bf16 terms).  One accumulation segment only (K x terms <= 4096); every wait is bounded.
@@ -39,6 +51,7 @@ struct Params {
     int ph, pw;            // pads
     int H, W, OH, OW;
     int pitch, pbh;        // GEMM rows per output row (multiple of 8), output rows per tile (pitch * pbh <= 128)
+    int qpr;               // WIDE: quarters (boxes of 32 pixels, 30 outputs each) per output row; pbh = 4 / qpr
     int tiles_per_image;   // ceil(OH / pbh)
     int tiles_m, tiles_n;  // images * tiles_per_image, ceil(N / BN)
     int a_box_bytes;       // bytes one activation box delivers, all terms together
@@ -53,27 +66,33 @@ struct Params {
     int* err_word;
 };
 
-template <int BN, int NPASS, bool RESIDENT>
+constexpr int kQuarterOutputs = 30;  // WIDE: output pixels of a 32-row quarter (rows 30 and 31 only feed the shifts)
+
+template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
 struct Cfg {
     static constexpr int B_TILE_BYTES = BN * tc::BK * 2;
     static constexpr int A_BYTES = NPASS * tc::A_TILE_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + (RESIDENT ? 0 : kMaxTaps * B_TILE_BYTES);
     static constexpr int AUX_BYTES = 1024 + 2 * kEpiGroups * BN * 4;  // barriers + alpha / bias staging per epilogue group
-    static constexpr int TMEM_COLS = kAccBufs * BN;
+    static constexpr int ACC_COLS = WIDE ? kMaxTaps * BN : BN;  // columns of one accumulator
+    static constexpr int ACC_BUFS = WIDE ? 2 : kAccBufs;
+    static constexpr int TMEM_COLS = WIDE ? 512 : kAccBufs * BN;
     static_assert(BN == 64 || BN == 128, "row mode keeps the column tile at 64 or 128");
+    static_assert(!WIDE || (BN == 64 && RESIDENT), "one instruction for three filter columns: 192 columns, resident filters");
+    static_assert(ACC_BUFS * ACC_COLS <= TMEM_COLS, "accumulators must fit the allocation");
 };
 
 // Shared memory a launch needs: alignment slack + resident filters + stages + aux.
-template <int BN, int NPASS, bool RESIDENT>
+template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
 inline int smem_bytes(int nstages, int n_btiles) {
-    using C = Cfg<BN, NPASS, RESIDENT>;
+    using C = Cfg<BN, NPASS, RESIDENT, WIDE>;
     return 1024 + (RESIDENT ? n_btiles * C::B_TILE_BYTES : 0) + nstages * C::STAGE_BYTES + C::AUX_BYTES;
 }
 
-template <int BN, int NPASS, bool RESIDENT>
+template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
 __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                 const __grid_constant__ CUtensorMap tmap_w, const Params p) {
-    using C = Cfg<BN, NPASS, RESIDENT>;
+    using C = Cfg<BN, NPASS, RESIDENT, WIDE>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -101,7 +120,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
         }
         for (int b = 0; b < kAccBufs; ++b) {
             ptx::mbar_init(bar_tmem_full + 8 * b, 1);
-            ptx::mbar_init(bar_tmem_empty + 8 * b, kGroupThreads);
+            ptx::mbar_init(bar_tmem_empty + 8 * b, WIDE ? 2 * kGroupThreads : kGroupThreads);  // WIDE: one group per 32-column chunk
         }
         ptx::mbar_init(bar_resident, 1);
         ptx::fence_barrier_init();
@@ -123,8 +142,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
             if (RESIDENT) {
                 // All filters of this CTA's column tile (tiles_n == 1: columns [0, BN)), once.
                 ptx::mbar_arrive_expect_tx(bar_resident, static_cast<uint32_t>(p.n_btiles) * C::B_TILE_BYTES);
-                for (int kt = 0; kt < p.n_btiles; ++kt)
-                    ptx::tma_load_3d(resident + kt * C::B_TILE_BYTES, &tmap_w, kt * tc::BK, 0, 0, bar_resident);
+                for (int kt = 0; kt < p.n_btiles; ++kt) {
+                    // k-block kt = (tap, channel block).  WIDE keeps the kw tiles of one filter row and channel block
+                    // one behind the other: slot ((ti * cblocks + cb) * kw + tj).
+                    int slot = kt;
+                    if (WIDE) {
+                        const int tap = kt / p.cblocks, cb = kt - tap * p.cblocks;
+                        const int ti = tap / p.kw, tj = tap - ti * p.kw;
+                        slot = (ti * p.cblocks + cb) * p.kw + tj;
+                    }
+                    ptx::tma_load_3d(resident + slot * C::B_TILE_BYTES, &tmap_w, kt * tc::BK, 0, 0, bar_resident);
+                }
             }
             int stage = 0;
             uint32_t phase = 0;
@@ -145,9 +173,21 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                         const uint32_t a_dst = stages + stage * C::STAGE_BYTES;
                         // Input pixels (x, y) = (-pw .. -pw + pitch - 1, oh0 - ph + ti*dh .. + pbh - 1), channels [64 cb, +64):
                         // tile row bh * pitch + bw holds pixel (bw - pw, oh0 + bh - ph + ti*dh); outside the image: zeros.
+                        if constexpr (WIDE) {
+                            // One box of 32 pixels per lane quarter: quarter qq holds output row oh0 + qq / qpr, output
+                            // columns 30 (qq % qpr) .. + 29 (and the two pixels to their right for the shifted taps).
+                            for (int qq = 0; qq < 4; ++qq) {
+                                const int x = (qq % p.qpr) * kQuarterOutputs - p.pw;
+                                const int y = oh0 + qq / p.qpr - p.ph + ti * p.dh;
 #pragma unroll
-                        for (int q = 0; q < NPASS; ++q)
-                            ptx::tma_load_5d(a_dst + q * tc::A_TILE_BYTES, &tmap_x, cb * tc::BK, -p.pw, oh0 - p.ph + ti * p.dh, img, q, bar);
+                                for (int q = 0; q < NPASS; ++q)
+                                    ptx::tma_load_5d(a_dst + q * tc::A_TILE_BYTES + qq * 32 * 128, &tmap_x, cb * tc::BK, x, y, img, q, bar);
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < NPASS; ++q)
+                                ptx::tma_load_5d(a_dst + q * tc::A_TILE_BYTES, &tmap_x, cb * tc::BK, -p.pw, oh0 - p.ph + ti * p.dh, img, q, bar);
+                        }
                         if (!RESIDENT) {
                             const uint32_t b_dst = a_dst + C::A_BYTES;
                             for (int tj = 0; tj < p.kw; ++tj)
@@ -171,14 +211,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
             bool ok = true;
             if (RESIDENT) ok = ptx::mbar_wait(bar_resident, 0, p.err_word, kErrWaitFullB);
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++iter) {
-                const int buf = iter % kAccBufs;
-                if (!ptx::mbar_wait(bar_tmem_empty + 8 * buf, static_cast<uint32_t>((iter / kAccBufs) & 1) ^ 1u, p.err_word,
+                const int buf = iter % C::ACC_BUFS;
+                if (!ptx::mbar_wait(bar_tmem_empty + 8 * buf, static_cast<uint32_t>((iter / C::ACC_BUFS) & 1) ^ 1u, p.err_word,
                                     kErrWaitTmemEmpty)) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * C::ACC_COLS);
                 uint32_t accumulate = 0;
                 for (int ti = 0; ti < p.kh && ok; ++ti) {
                     for (int cb = 0; cb < p.cblocks; ++cb) {
@@ -188,7 +228,23 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                         }
                         ptx::tc_fence_after_sync();
                         const uint32_t a_addr = stages + stage * C::STAGE_BYTES;
-                        for (int tj = 0; tj < p.kw; ++tj) {
+                        if constexpr (WIDE) {
+                            // All three filter columns of filter row ti at once: the unshifted window against 3 BN weight rows.
+                            const uint32_t idesc_wide = p.f16 ? ptx::umma_idesc_f16_f32(tc::BM, kMaxTaps * BN)
+                                                              : ptx::umma_idesc_bf16_f32(tc::BM, kMaxTaps * BN);
+                            const uint32_t b_addr = resident + ((ti * p.cblocks + cb) * kMaxTaps) * C::B_TILE_BYTES;
+#pragma unroll
+                            for (int q = 0; q < NPASS; ++q) {
+#pragma unroll
+                                for (int k4 = 0; k4 < tc::BK / tc::UMMA_K; ++k4) {
+                                    const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr + q * tc::A_TILE_BYTES + k4 * tc::UMMA_K * 2);
+                                    const uint64_t b_desc = ptx::umma_desc_k_sw128(b_addr + k4 * tc::UMMA_K * 2);
+                                    ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc_wide, accumulate);
+                                    accumulate = 1u;
+                                }
+                            }
+                        }
+                        for (int tj = 0; tj < (WIDE ? 0 : p.kw); ++tj) {
                             // Filter column tj: the same rows one pixel (one 128-byte row) further on.
                             const uint32_t b_addr = RESIDENT ? resident + ((ti * p.kw + tj) * p.cblocks + cb) * C::B_TILE_BYTES
                                                              : a_addr + C::A_BYTES + tj * C::B_TILE_BYTES;
@@ -233,11 +289,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
         int iter = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++iter) {
-            if (iter % kEpiGroups != group) continue;
+            // A group drains every third tile -- or, WIDE, every third 32-column chunk: chunk (iter, c) is job 2 iter + c.
+            if (!WIDE && iter % kEpiGroups != group) continue;
             const int tm = t % p.tiles_m, tn = t / p.tiles_m;
             const int img = tm / p.tiles_per_image;
             const int oh0 = (tm - img * p.tiles_per_image) * p.pbh;
-            const int buf = iter % kAccBufs;
+            const int buf = iter % C::ACC_BUFS;
             const int n0 = tn * BN;
             if (tn != staged_tn) {  // per-channel scale and bias of this column tile: reloaded only when it changes
                 ptx::named_barrier_sync(1 + group, kGroupThreads);  // everyone has finished reading the old values
@@ -250,24 +307,54 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                 staged_tn = tn;
             }
             const int row = quarter * 32 + lane;
-            const int bh = row / p.pitch, bw = row - bh * p.pitch;
+            const int bh = WIDE ? quarter / p.qpr : row / p.pitch;
+            const int bw = WIDE ? (quarter % p.qpr) * kQuarterOutputs + lane : row - bh * p.pitch;
             const int oh = oh0 + bh;
-            const bool row_ok = bh < p.pbh && bw < p.OW && oh < p.OH;
+            const bool row_ok = bh < p.pbh && bw < p.OW && oh < p.OH && (!WIDE || lane < kQuarterOutputs);
             const int64_t pix = static_cast<int64_t>(oh) * p.OW + bw;          // pixel inside the image
             const int64_t out_base = static_cast<int64_t>(img) * p.N * hw + pix;  // + n * hw
             const int64_t cl_row = static_cast<int64_t>(img) * hw + pix;
-            if (!ptx::mbar_wait(bar_tmem_full + 8 * buf, static_cast<uint32_t>((iter / kAccBufs) & 1), p.err_word, kErrWaitTmemFull)) {
-                ok = false;
-                break;
+            if (!WIDE) {
+                if (!ptx::mbar_wait(bar_tmem_full + 8 * buf, static_cast<uint32_t>((iter / C::ACC_BUFS) & 1), p.err_word, kErrWaitTmemFull)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
             }
-            ptx::tc_fence_after_sync();
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int nc = n0 + c * 32;
-                if (nc >= p.N) break;
+                if (!WIDE && nc >= p.N) break;
+                if (WIDE && (iter * (BN / 32) + c) % kEpiGroups != group) continue;
                 uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN + c * 32), r);
-                ptx::tmem_ld_wait();
+                const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * C::ACC_COLS + c * 32);
+                if constexpr (WIDE) {
+                    // out[row] = E[row][0] + E[row + 1][1] + E[row + 2][2]; this thread holds row = 32 quarter + lane.
+                    if (!ptx::mbar_wait(bar_tmem_full + 8 * buf, static_cast<uint32_t>((iter / C::ACC_BUFS) & 1), p.err_word, kErrWaitTmemFull)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    uint32_t r1[32], r2[32];
+                    ptx::tmem_ld_32x32(t_addr, r);
+                    ptx::tmem_ld_32x32(t_addr + BN, r1);
+                    ptx::tmem_ld_32x32(t_addr + 2 * BN, r2);
+                    ptx::tmem_ld_wait();
+                    // The chunk is in registers: hand the accumulator back now (the other chunk's group does the same),
+                    // so that the next tile's MMAs do not wait for the arithmetic and the stores below.
+                    ptx::tc_fence_before_sync();
+                    ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
+                    // Rows + 1 and + 2 sit in the next lanes of this warp (lanes 30 and 31 hold no output).
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float e1 = __shfl_down_sync(0xffffffffu, __uint_as_float(r1[j]), 1);
+                        const float e2 = __shfl_down_sync(0xffffffffu, __uint_as_float(r2[j]), 2);
+                        r[j] = __float_as_uint(__fadd_rn(__fadd_rn(__uint_as_float(r[j]), e1), e2));
+                    }
+                } else {
+                    ptx::tmem_ld_32x32(t_addr, r);
+                    ptx::tmem_ld_wait();
+                }
                 if (!row_ok) continue;
                 const float* as = as_g + c * 32;
                 const float* bs = bs_g + c * 32;
@@ -337,8 +424,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                     }
                 }
             }
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
+            if (!WIDE) {
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
+            }
         }
     }
 
@@ -350,10 +439,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
     }
 }
 
-template <int BN, int NPASS, bool RESIDENT>
+template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
 int32_t launch(const CUtensorMap& tmap_x, const CUtensorMap& tmap_w, const Params& p, cudaStream_t st) {
-    auto kernel = conv_rows_kernel<BN, NPASS, RESIDENT>;
-    const int smem = smem_bytes<BN, NPASS, RESIDENT>(p.nstages, p.n_btiles);
+    auto kernel = conv_rows_kernel<BN, NPASS, RESIDENT, WIDE>;
+    const int smem = smem_bytes<BN, NPASS, RESIDENT, WIDE>(p.nstages, p.n_btiles);
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
@@ -364,9 +453,9 @@ int32_t launch(const CUtensorMap& tmap_x, const CUtensorMap& tmap_w, const Param
 }
 
 // Pipeline depth that fits beside the resident filters (0: does not fit with at least two stages).
-template <int BN, int NPASS, bool RESIDENT>
+template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
 inline int stages_that_fit(int n_btiles) {
-    using C = Cfg<BN, NPASS, RESIDENT>;
+    using C = Cfg<BN, NPASS, RESIDENT, WIDE>;
     const int left = tc::kSmemLimit - 1024 - C::AUX_BYTES - (RESIDENT ? n_btiles * C::B_TILE_BYTES : 0);
     const int s = left / C::STAGE_BYTES;
     return s < 2 ? 0 : (s > kMaxStages ? kMaxStages : s);

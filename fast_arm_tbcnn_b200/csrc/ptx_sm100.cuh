@@ -95,18 +95,23 @@ constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;  // 2 s
 constexpr int kWaitLimitWordOffset = 2;                  // in ints from the error word (8-byte aligned)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_word, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    // The clock and the error word are looked at only every 1024 failed polls (the first reading starts the
-    // clock): an ordinary short wait costs nothing but the polls themselves.
-    uint64_t t0 = 0;
+    // The clock is looked at only every 1024 failed polls (the first reading starts it): an ordinary short wait costs
+    // nothing but the polls themselves.  The limit and the error word live in host memory mapped into the device (the
+    // host must be able to read them whatever happens to the kernel): the limit is fetched once per long wait, the
+    // error word -- set by a waiter that gave up, so that the others follow -- every 65536 polls, so that thousands
+    // of waiting warps never queue up on the bus.
+    uint64_t t0 = 0, limit = 0;
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ffu) == 0) {
-            if (*reinterpret_cast<volatile int*>(err_word) != 0) return false;
-            const uint64_t limit = *reinterpret_cast<volatile uint64_t*>(err_word + kWaitLimitWordOffset);
             const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > limit) {
+            if (t0 == 0) {
+                t0 = now;
+                limit = *reinterpret_cast<volatile uint64_t*>(err_word + kWaitLimitWordOffset);
+            } else if (now - t0 > limit) {
                 atomicCAS(err_word, 0, code);
+                return false;
+            } else if ((spins & 0xffffu) == 0 && *reinterpret_cast<volatile int*>(err_word) != 0) {
                 return false;
             }
         }
