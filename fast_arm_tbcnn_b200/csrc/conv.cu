@@ -113,6 +113,7 @@ __global__ void s2d_split_kernel(const float* __restrict__ x, int64_t N, int C, 
                                  __nv_bfloat16* __restrict__ t, int64_t term_stride, float lo, float hi) {
     const int64_t total = N * rows * Qp;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const bool pair_ok = (W & 1) == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0;
     for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         int qs, rs;
         int64_t n;
@@ -132,14 +133,36 @@ __global__ void s2d_split_kernel(const float* __restrict__ x, int64_t N, int C, 
         for (int q = 0; q < NPASS; ++q)
 #pragma unroll
             for (int e = 0; e < 8; ++e) packed[q][e] = 0u;
+        // The two columns of a position are neighbours in memory: one 8-byte load where the row allows it.
+        float in[2][2][4];  // [pr][pc][c]
+        const int w0 = 2 * (qs - left);
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float2 v2 = make_float2(0.f, 0.f);
+                const int h = 2 * rs + pr;
+                if (c < C && h < H) {
+                    const float* src = x + ((n * C + c) * H + h) * static_cast<int64_t>(W) + w0;
+                    if (pair_ok && w0 >= 0 && w0 + 1 < W) v2 = __ldg(reinterpret_cast<const float2*>(src));
+                    else {
+                        if (w0 >= 0 && w0 < W) v2.x = __ldg(src);
+                        if (w0 + 1 >= 0 && w0 + 1 < W) v2.y = __ldg(src + 1);
+                    }
+                }
+                in[pr][0][c] = v2.x;
+                in[pr][1][c] = v2.y;
+            }
 #pragma unroll
         for (int sidx = 0; sidx < 16; ++sidx) {
             float v = 0.0f;
-            if (sidx < 4 * C) {
-                const int pr = sidx / (2 * C), pc = (sidx / C) & 1, c = sidx % C;
-                const int h = 2 * rs + pr, w = 2 * (qs - left) + pc;
-                if (h < H && w >= 0 && w < W) v = __ldg(x + ((n * C + c) * H + h) * static_cast<int64_t>(W) + w);
-            }
+#pragma unroll
+            for (int pr = 0; pr < 2; ++pr)
+#pragma unroll
+                for (int pc = 0; pc < 2; ++pc)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (c < C && (pr * 2 + pc) * C + c == sidx) v = in[pr][pc][c];
             uint16_t term[NPASS];
             split_terms<NPASS, TERNARISE>(v, lo, hi, term);
 #pragma unroll
