@@ -516,25 +516,30 @@ def cnn_block(args, ctx):
             logits[j].copy_(sess.get_output("output"))
 
     ms_eager = timed(eager_pass, 1)
-    ms_pass, how = ms_eager, "eager launches"
+    ms_pass, how, ms_graph = ms_eager, "eager launches", None
     try:
-        static_in = torch.empty_like(xs[0])
-        sess.set_input("input", static_in)
-        graph = torch.cuda.CUDAGraph()
-        torch.cuda.synchronize()
-        with torch.cuda.graph(graph):
-            sess.run()
-        static_out = sess.get_output("output")
+        # One captured Session.run per micro-batch, each reading its images where they lie; the graphs run one after
+        # the other and share one memory pool for their intermediates.
+        graphs_, outs, pool = [], [], None
+        for j in range(n_micro):
+            sess.set_input("input", xs[j])
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, pool=pool):
+                sess.run()
+            if pool is None:
+                pool = g.pool()
+            graphs_.append(g)
+            outs.append(sess.get_output("output"))
 
         def graph_pass():
             for j in range(n_micro):
-                static_in.copy_(xs[j])
-                graph.replay()
-                logits[j].copy_(static_out)
+                graphs_[j].replay()
+                logits[j].copy_(outs[j])
 
         ms_graph = timed(graph_pass, 1)
         if ms_graph < ms_pass:
-            ms_pass, how = ms_graph, "CUDA graph replay of one Session.run per micro-batch (input copied into the graph's buffer)"
+            ms_pass, how = ms_graph, "CUDA graph replay: one captured Session.run per micro-batch, reading its images in place"
     except Exception as exc:  # noqa: BLE001 -- capture is an optimisation; the eager number stands
         how = "eager launches (graph capture failed: %r)" % (exc,)
     images = n_micro * micro * world
@@ -543,7 +548,7 @@ def cnn_block(args, ctx):
     exec_flops = (2.0 * fb + 3.0 * ff) * n_micro * micro
     roof_ms = exec_flops / (peaks["bf16_tflops"] * 1e12) * 1e3
     out["resnet18_binary_224"] = {
-        "images_per_s": images / (ms_pass * 1e-3), "batch": images, "ms_per_batch": ms_pass, "ms_per_batch_eager": ms_eager,
+        "images_per_s": images / (ms_pass * 1e-3), "batch": images, "ms_per_batch": ms_pass, "ms_per_batch_eager": ms_eager, "ms_per_batch_graph": ms_graph,
         "ms_per_microbatch": ms_pass / n_micro, "launch_mode": how, "microbatch_per_gpu": micro, "microbatches_per_gpu": n_micro,
         "tflops": (fb + ff) * images / (ms_pass * 1e-3) / 1e12, "flops_per_image": fb + ff,
         "roofline": {"bound": "tensor", "achieved": (fb + ff) * n_micro * micro / (ms_pass * 1e-3) / 1e12,
