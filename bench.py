@@ -40,7 +40,7 @@ if ROOT not in sys.path:
 
 # DRAM bytes of one gemm_tc_kernel launch measured with ncu (a profiler cannot run inside the benchmark):
 # key = (size, mode, GPUs).
-MEASURED_TRAFFIC = {(16384, "x2", 1): 5.09e9, (8192, "x2", 1): 0.639e9}
+MEASURED_TRAFFIC = {(16384, "x2", 1): 5.45e9, (8192, "x2", 1): 0.648e9}
 
 METRIC = "float x binary GEMM throughput (2*M*N*K / time)"
 UNIT = "TFLOP/s"
