@@ -101,6 +101,13 @@ FAST_CASES = [
     (1, 64, 5, 300, 16, 1, 3, (1, 2, 0, 1, 1, 1)),      # output rows longer than one tile
     (2, 128, 28, 28, 64, 1, 1, (2, 2, 0, 0, 1, 1)),     # strided 1x1 (the shortcut convolutions)
     (2, 64, 40, 40, 8, 3, 3, (9, 9, 1, 1, 1, 1)),       # stride beyond the TMA element-stride range: cp.async path
+    # 64 output channels, three filter columns: one 192-column instruction per filter row, tiles laid out by lane quarters
+    (2, 64, 28, 28, 64, 3, 3, (1, 1, 1, 1, 1, 1)),      # one quarter per output row, four rows per tile
+    (1, 128, 30, 60, 64, 3, 3, (1, 1, 1, 1, 1, 1)),     # two quarters per row (30 + 30 outputs), two channel blocks
+    (1, 64, 9, 40, 64, 3, 3, (1, 1, 1, 1, 1, 1)),       # second quarter partly empty, last tile half empty
+    (1, 64, 6, 112, 64, 3, 3, (1, 1, 1, 1, 1, 1)),      # four quarters per row
+    (1, 64, 10, 30, 64, 3, 3, (1, 1, 0, 0, 1, 1)),      # no padding
+    (1, 64, 5, 58, 64, 1, 3, (1, 1, 0, 1, 1, 1)),       # one filter row
 ]
 
 
@@ -536,6 +543,40 @@ def test_chained_convolutions_are_bit_identical(tbn, weights):
     chained, _ = tbn.lib.conv2d_chain(tuple(y1.shape), k2, tuple(w2.shape), p2, x_cl=y1_cl, alpha=a2, residual=res)
     tbn.lib.sync()
     assert torch.equal(plain, chained) and float(plain.abs().sum()) > 0
+
+
+@pytest.mark.gpu
+def test_three_column_instruction_with_residual_and_both_result_forms(tbn, oracle):
+    """64 -> 64 channels, 3x3, stride 1 (the layers that run one 192-column instruction per filter row): input taken
+    as channels-last terms, residual added, ReLU, fp32 NCHW and channels-last results written -- against the
+    reference's float convolution on the dequantised filters, and the two result forms against each other."""
+    import torch
+    from oracle import graphs
+    rng = np.random.default_rng(33)
+    x = rng.standard_normal((3, 64, 28, 28), dtype=np.float32)
+    w = (rng.standard_normal((64, 64, 3, 3), dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    b = (rng.standard_normal(64, dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    res = rng.standard_normal((3, 64, 28, 28), dtype=np.float32)
+    p = (1, 1, 1, 1, 1, 1)
+    dx, dw_, db, dres = (torch.from_numpy(a).cuda() for a in (x, w, b, res))
+    words, alpha = tbn.lib.quant_pack_binary(tbn.lib.permute_filters(dw_), tbn.LAYOUT_NK)
+    k = {"words": words}
+    # a first layer only to obtain the channels-last form of its ReLU output
+    y0, y0_cl = tbn.lib.conv2d_chain(tuple(x.shape), k, tuple(w.shape), p, x=dx, want_y=True, want_y_cl=True, alpha=alpha,
+                                     bias=db, epilogue=tbn.EPI_RELU)
+    y1, y1_cl = tbn.lib.conv2d_chain(tuple(x.shape), k, tuple(w.shape), p, x_cl=y0_cl, want_y=True, want_y_cl=True,
+                                     alpha=alpha, bias=db, residual=dres, epilogue=tbn.EPI_RELU)
+    only_cl = tbn.lib.conv2d_chain(tuple(x.shape), k, tuple(w.shape), p, x_cl=y0_cl, want_y=False, want_y_cl=True,
+                                   alpha=alpha, bias=db, residual=dres, epilogue=tbn.EPI_RELU)[1]
+    tbn.lib.sync()
+    wq = graphs.dequantise(w)
+    e0 = np.maximum(oracle.conv2d_f32(x, wq, b, p), 0.0)
+    assert rel_l2(y0.cpu().numpy(), e0) <= TOL_FP32
+    e1 = np.maximum(oracle.conv2d_f32(y0.cpu().numpy(), wq, b, p) + res, 0.0)
+    assert rel_l2(y1.cpu().numpy(), e1) <= TOL_FP32
+    hi = y1.permute(0, 2, 3, 1).bfloat16()
+    assert torch.equal(y1_cl[0], hi) and torch.equal(y1_cl[1], (y1.permute(0, 2, 3, 1) - hi.float()).bfloat16())
+    assert torch.equal(only_cl, y1_cl)
 
 
 @pytest.mark.gpu
