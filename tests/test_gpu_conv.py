@@ -447,6 +447,32 @@ def test_resnet18_session(tbn, oracle, batch, image):
     assert rel_l2(outs[0], outs[1]) <= 1e-6
 
 
+@pytest.mark.gpu
+def test_resnet18_at_the_benchmark_microbatch_against_a_seeded_subset(tbn, oracle):
+    """The network as the benchmark runs it -- 512 images of 224 x 224 per Session.run, layer chaining on, no
+    intermediates kept -- against the reference's float path on 32 of those images (every 16th; the network treats
+    images independently, so the oracle runs them alone): logits within the end-to-end 3e-5, classes identical."""
+    import torch
+    from fast_arm_tbcnn_b200.session import Session
+    from oracle import graphs
+    batch, step = 512, 16
+    rng = np.random.default_rng(1000)
+    x = rng.standard_normal((batch, 3, 224, 224), dtype=np.float32)
+    sess = Session(graphs.resnet18(batch=batch, seed=2, image=224, classes=1000))
+    sess.keep_intermediates = False
+    sess.set_input("input", torch.from_numpy(x).cuda())
+    sess.run()
+    tbn.lib.sync()
+    got = sess.get_output("output").cpu().numpy()[::step]
+    sub = np.ascontiguousarray(x[::step])
+    expect = graphs.run_float(graphs.resnet18(batch=sub.shape[0], seed=2, image=224, classes=1000), sub, oracle)
+    assert got.shape == expect.shape == (batch // step, 1000)
+    assert rel_l2(got, expect) <= 3e-5
+    for i in range(got.shape[0]):
+        assert rel_l2(got[i], expect[i]) <= 1e-4, i   # no single image far off
+    assert np.array_equal(got.argmax(axis=1), expect.argmax(axis=1))
+
+
 def test_resnet18_every_weight_layer_on_reference_inputs(tbn, oracle):
     """Per-layer bar: every Conv and Gemm of the network, fed the reference's own input to that layer, is
     within 1e-5 of the reference's output of that layer (channels-last and element-wise conv paths)."""
