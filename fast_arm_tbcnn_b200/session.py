@@ -290,12 +290,12 @@ class Session:
         if bias is not None and beta != 1.0:
             bias = bias * beta
         if "words" not in w:
-            ws, _ = L.gemm_workspace(x.shape[0], x.shape[1], capi.MODE_TC_BF16X2, self.device)
+            ws = self._workspace("gemm", L.h.tbn_gemm_workspace_bytes(x.shape[0], x.shape[1], capi.MODE_TC_BF16X2))
             return L.gemm_f32(x.contiguous(), w["split"], N, alpha=alpha_attr, bias=bias, workspace=ws)
         if self.quantization:
             # Weights alpha*sign(w) are not exactly +-1, so the reference quantises them on the fly and runs
             # qlinear_matmul_binary with scale 1 (model.hpp:839-841), then alpha and beta*C (:845-869).
-            ws, _ = L.gemm_workspace(x.shape[0], x.shape[1], capi.MODE_TC_BF16X1, self.device)
+            ws = self._workspace("gemm", L.h.tbn_gemm_workspace_bytes(x.shape[0], x.shape[1], capi.MODE_TC_BF16X1))
             return L.gemm_tbn(x.contiguous(), w["words"], N, scale=alpha_attr, bias=bias, workspace=ws)
-        ws, _ = L.gemm_workspace(x.shape[0], x.shape[1], capi.MODE_TC_BF16X2, self.device)
+        ws = self._workspace("gemm", L.h.tbn_gemm_workspace_bytes(x.shape[0], x.shape[1], capi.MODE_TC_BF16X2))
         return L.gemm_fxb(x.contiguous(), w["words"], N, alpha=w["alpha"], scale=alpha_attr, bias=bias, workspace=ws)
