@@ -386,17 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                         for (int g8 = 0; g8 < 4; ++g8) {
                             uint32_t hi[4], lo[4];
 #pragma unroll
-                            for (int k = 0; k < 8; ++k) {
-                                uint16_t term[2];
-                                split_terms<2, false>(o[g8 * 8 + k], 0.f, 0.f, term);
-                                if (k & 1) {
-                                    hi[k >> 1] |= static_cast<uint32_t>(term[0]) << 16;
-                                    lo[k >> 1] |= static_cast<uint32_t>(term[1]) << 16;
-                                } else {
-                                    hi[k >> 1] = term[0];
-                                    lo[k >> 1] = term[1];
-                                }
-                            }
+                            for (int k = 0; k < 4; ++k) split_pair_terms(o[g8 * 8 + 2 * k], o[g8 * 8 + 2 * k + 1], hi[k], lo[k]);
                             *reinterpret_cast<uint4*>(cl + g8 * 8) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                             *reinterpret_cast<uint4*>(cl + p.y_cl_term_stride + g8 * 8) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                         }

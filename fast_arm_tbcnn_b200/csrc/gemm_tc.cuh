@@ -102,6 +102,18 @@ __device__ __forceinline__ void split_terms(float v, float lo, float hi, uint16_
     }
 }
 
+// Two values at once, two terms each, as the packed words the channels-last form stores: hi = {rn(a), rn(b)},
+// lo = {rn(a - hi_a), rn(b - hi_b)}, a in the low half.  Same values as split_terms<2, false> gives one by one (a
+// non-finite input leaves its second term at zero); one packed conversion per pair and term instead of two scalar ones.
+__device__ __forceinline__ void split_pair_terms(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    const float ra = isfinite(a) ? __fsub_rn(a, __uint_as_float(hi << 16)) : 0.0f;
+    const float rb = isfinite(b) ? __fsub_rn(b, __uint_as_float(hi & 0xffff0000u)) : 0.0f;
+    const __nv_bfloat162 l = __floats2bfloat162_rn(ra, rb);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
 // max |a| over a strided matrix as the bit pattern of a non-negative float (for those, integer order = float order;
 // a NaN has the largest pattern and so wins).  *out must be zero before the launch.
 __global__ void __launch_bounds__(256) absmax_kernel(const float* __restrict__ a, int64_t rows, int64_t cols, int64_t ld,
@@ -951,17 +963,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                                     for (int g8 = 0; g8 < 4; ++g8) {
                                         uint32_t hi[4], lo[4];
 #pragma unroll
-                                        for (int e = 0; e < 8; ++e) {
-                                            uint16_t term[2];
-                                            split_terms<2, false>(o[g8 * 8 + e], 0.f, 0.f, term);
-                                            if (e & 1) {
-                                                hi[e >> 1] |= static_cast<uint32_t>(term[0]) << 16;
-                                                lo[e >> 1] |= static_cast<uint32_t>(term[1]) << 16;
-                                            } else {
-                                                hi[e >> 1] = term[0];
-                                                lo[e >> 1] = term[1];
-                                            }
-                                        }
+                                        for (int e = 0; e < 4; ++e) split_pair_terms(o[g8 * 8 + 2 * e], o[g8 * 8 + 2 * e + 1], hi[e], lo[e]);
                                         *reinterpret_cast<uint4*>(cl + g8 * 8) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                                         *reinterpret_cast<uint4*>(cl + p.out_cl_term_stride + g8 * 8) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                                     }
