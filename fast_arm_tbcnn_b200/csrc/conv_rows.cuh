@@ -328,28 +328,42 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                 if (WIDE && (iter * (BN / 32) + c) % kEpiGroups != group) continue;
                 uint32_t r[32];
                 const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * C::ACC_COLS + c * 32);
+                float rv[32];  // WIDE: the residual values of this chunk, requested before the accumulator is waited for
                 if constexpr (WIDE) {
                     // out[row] = E[row][0] + E[row + 1][1] + E[row + 2][2]; this thread holds row = 32 quarter + lane.
+                    // The residual loads go out first: their latency (the top stall of this epilogue) then runs
+                    // beside the wait for the accumulator and the tensor-memory loads.
+                    if (add_res) {
+                        const float* rp = p.ep.residual + out_base + static_cast<int64_t>(nc) * hw;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) rv[j] = row_ok ? __ldg(rp + j * hw) : 0.0f;
+                    }
                     if (!ptx::mbar_wait(bar_tmem_full + 8 * buf, static_cast<uint32_t>((iter / C::ACC_BUFS) & 1), p.err_word, kErrWaitTmemFull)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    uint32_t r1[32], r2[32];
-                    ptx::tmem_ld_32x32(t_addr, r);
-                    ptx::tmem_ld_32x32(t_addr + BN, r1);
-                    ptx::tmem_ld_32x32(t_addr + 2 * BN, r2);
-                    ptx::tmem_ld_wait();
-                    // The chunk is in registers: hand the accumulator back now (the other chunk's group does the same),
-                    // so that the next tile's MMAs do not wait for the arithmetic and the stores below.
-                    ptx::tc_fence_before_sync();
-                    ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
-                    // Rows + 1 and + 2 sit in the next lanes of this warp (lanes 30 and 31 hold no output).
+                    // Two halves of 16 columns, so that three tensor-memory operands and the residual fit the registers.
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float e1 = __shfl_down_sync(0xffffffffu, __uint_as_float(r1[j]), 1);
-                        const float e2 = __shfl_down_sync(0xffffffffu, __uint_as_float(r2[j]), 2);
-                        r[j] = __float_as_uint(__fadd_rn(__fadd_rn(__uint_as_float(r[j]), e1), e2));
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t e0[16], e1[16], e2[16];
+                        ptx::tmem_ld_32x16(t_addr + h * 16, e0);
+                        ptx::tmem_ld_32x16(t_addr + BN + h * 16, e1);
+                        ptx::tmem_ld_32x16(t_addr + 2 * BN + h * 16, e2);
+                        ptx::tmem_ld_wait();
+                        if (h == 1) {
+                            // The chunk is in registers: hand the accumulator back now (the other chunk's group does the
+                            // same), so that the next tile's MMAs do not wait for the arithmetic and the stores below.
+                            ptx::tc_fence_before_sync();
+                            ptx::mbar_arrive(bar_tmem_empty + 8 * buf);
+                        }
+                        // Rows + 1 and + 2 sit in the next lanes of this warp (lanes 30 and 31 hold no output).
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float s1 = __shfl_down_sync(0xffffffffu, __uint_as_float(e1[j]), 1);
+                            const float s2 = __shfl_down_sync(0xffffffffu, __uint_as_float(e2[j]), 2);
+                            r[h * 16 + j] = __float_as_uint(__fadd_rn(__fadd_rn(__uint_as_float(e0[j]), s1), s2));
+                        }
                     }
                 } else {
                     ptx::tmem_ld_32x32(t_addr, r);
@@ -368,10 +382,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                 const int ncols = min(32, p.N - nc);
                 const int64_t first = out_base + static_cast<int64_t>(nc) * hw;
                 if (add_res) {
-                    const float* rp = p.ep.residual + first;
-                    float rv[32];
+                    if constexpr (!WIDE) {
+                        const float* rp = p.ep.residual + first;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) rv[j] = j < ncols ? __ldg(rp + j * hw) : 0.0f;
+                        for (int j = 0; j < 32; ++j) rv[j] = j < ncols ? __ldg(rp + j * hw) : 0.0f;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) o[j] = __fadd_rn(o[j], rv[j]);
                 }
