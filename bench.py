@@ -997,7 +997,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cnn", action="store_true", help="skip every block but the headline GEMM")
     ap.add_argument("--only-cnn", action="store_true", help="run only the binary-CNN images/s block")
-    ap.add_argument("--resnet-microbatch", type=int, default=512, help="images per GPU and Session.run in the ResNet-18 block")
+    ap.add_argument("--resnet-microbatch", type=int, default=1024, help="images per GPU and Session.run in the ResNet-18 block")
     ap.add_argument("--resnet-batch", type=int, default=8192, help="whole-job batch of the ResNet-18 block")
     ap.add_argument("--parity-rows", type=int, default=32, help="rows of C compared with the CPU oracle after the timed region")
     ap.add_argument("--barrier", choices=["nccl", "symm"], default="nccl",
