@@ -628,6 +628,26 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
         const bool patch_ok = pbw * a.sw <= 256 && pbh * a.sh <= 256 && a.sw <= 8 && a.sh <= 8 && pbi <= 256 &&
                               a.N * a.H * a.W * a.C * 2 < (1LL << 40);
         if (patch_ok) {
+            // Stacked rows (gemm_tc.cuh, ConvGeom::stack_rows): tiles of whole output rows of the sequence img * OH + oh,
+            // one box per image a tile touches -- where that needs at least 5 % fewer tiles than the rectangles.
+            // TBN_CONV_STACK=0 in the environment keeps the rectangles (for A/B measurements).
+            static const bool stack_enabled = [] {
+                const char* v = std::getenv("TBN_CONV_STACK");
+                return !(v && v[0] == '0');
+            }();
+            const int64_t srows = OW <= tc::BM ? tc::BM / OW : 0;
+            const int64_t smax_h = std::min<int64_t>(srows, OH);
+            const int64_t patch_tiles_m = ((OW + pbw - 1) / pbw) * ((OH + pbh - 1) / pbh) * ((a.N + pbi - 1) / pbi);
+            const int64_t stack_tiles_m = srows > 0 ? (a.N * OH + srows - 1) / srows : 0;
+            const bool stacked = stack_enabled && srows >= 2 && smax_h <= 9 && OW * a.sw <= 256 && smax_h * a.sh <= 256 &&
+                                 stack_tiles_m * 20 <= patch_tiles_m * 19 && a.N * OH + tc::BM < (1LL << 31);
+            if (stacked) {
+                pbw = OW;
+                pbh = smax_h;  // the activation map carries the largest height
+                pbi = 1;
+            }
+            p.conv.stack_rows = stacked ? static_cast<int>(srows) : 0;
+            p.conv.stack_max_h = static_cast<int>(smax_h);
             const cuuint64_t gdim[5] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W), static_cast<cuuint64_t>(a.H),
                                         static_cast<cuuint64_t>(a.N), static_cast<cuuint64_t>(npass)};
             const cuuint64_t gstride[4] = {static_cast<cuuint64_t>(a.C) * 2, static_cast<cuuint64_t>(a.W * a.C) * 2,
@@ -635,6 +655,14 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
             const cuuint32_t box[5] = {tc::BK, static_cast<cuuint32_t>(pbw * a.sw), static_cast<cuuint32_t>(pbh * a.sh),
                                        static_cast<cuuint32_t>(pbi), 1};
             const cuuint32_t estr[5] = {1, static_cast<cuuint32_t>(a.sw), static_cast<cuuint32_t>(a.sh), 1, 1};
+            for (int64_t h = 1; stacked && h < smax_h; ++h) {  // the smaller heights
+                const cuuint32_t hbox[5] = {tc::BK, static_cast<cuuint32_t>(OW * a.sw), static_cast<cuuint32_t>(h * a.sh), 1, 1};
+                const CUresult hr = encode(&maps.out.m[h - 1], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, xs, gdim, gstride, hbox, estr,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                TBN_REQUIRE(hr == CUDA_SUCCESS, TBN_CUDA_ERROR,
+                            "cuTensorMapEncodeTiled (activation rows) failed with CUresult " + std::to_string(static_cast<int>(hr)));
+            }
             const CUresult cr = encode(&maps.a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, xs, gdim, gstride, box, estr,
                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -645,8 +673,8 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
             p.conv.pbi = static_cast<int>(pbi);
             p.conv.patches_w = static_cast<int>((OW + pbw - 1) / pbw);
             p.conv.patches_h = static_cast<int>((OH + pbh - 1) / pbh);
-            p.conv.a_box_bytes = static_cast<int>(npass * pbw * pbh * pbi * 128);
-            const int64_t tiles_m = static_cast<int64_t>(p.conv.patches_w) * p.conv.patches_h * ((a.N + pbi - 1) / pbi);
+            p.conv.a_box_bytes = static_cast<int>(npass * (stacked ? srows * OW : pbw * pbh * pbi) * 128);
+            const int64_t tiles_m = stacked ? stack_tiles_m : static_cast<int64_t>(p.conv.patches_w) * p.conv.patches_h * ((a.N + pbi - 1) / pbi);
             TBN_REQUIRE(tiles_m * p.tiles_n < (1LL << 31), TBN_INVALID_SHAPE, "conv2d: too many tiles");
             p.tiles_m = static_cast<int>(tiles_m);
             if (a.dense_w) {

@@ -218,6 +218,14 @@ struct ConvGeom {
     // (pbi*pbh*pbw <= 128 GEMM rows, row = (bi*pbh + bh)*pbw + bw); patches_w x patches_h boxes cover one image
     // group.  a_box_bytes: bytes one TMA box delivers (all terms together).
     int pbw, pbh, pbi, patches_w, patches_h, a_box_bytes;
+    // Patch mode, stacked rows (stack_rows > 0, pbw = OW): the output rows of all images form one sequence
+    // s = img * OH + oh and an m-tile is `stack_rows` consecutive rows of it, whatever images they belong to, so
+    // that tiles stay full where an image's pixel count is not a multiple of the tile (14 x 14: 9 rows = 126 of
+    // 128 GEMM rows instead of 126 and 70 in turn; 7 x 7: 18 rows of up to four images instead of two whole
+    // images).  The rows a tile takes from one image are one TMA box; the box height is a property of the tensor
+    // map, so there is one map per height: heights 1 .. 8 in the (otherwise unused) destination maps, the largest
+    // height min(stack_rows, OH) <= 9 in the activation map itself.
+    int stack_rows, stack_max_h;
 };
 
 // Tensor maps of the destinations of the multi-destination epilogue: [N columns][M rows] fp32 with row stride
@@ -422,6 +430,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                             // for the whole patch; coordinates outside the image read zeros.
                             const int x = pw0 + p_tj * p.conv.dw, y = ph0 + p_ti * p.conv.dh;
                             const bool tap_valid = p_ti * p.conv.kw + p_tj < p.conv.taps;
+                            if (p.conv.stack_rows > 0) {
+                                // One box per image the tile's rows come from (rows past the last image: zeros).
+                                int img = (tm * p.conv.stack_rows) / p.conv.OH;
+                                int oh = tm * p.conv.stack_rows - img * p.conv.OH;
+                                int done = 0;
+                                while (done < p.conv.stack_rows) {
+                                    const int h = min(p.conv.stack_rows - done, p.conv.OH - oh);
+                                    const CUtensorMap* map = h == p.conv.stack_max_h ? &tmap_a : &out_maps.m[h - 1];
+                                    const int yr = oh * p.conv.sh - p.conv.ph + p_ti * p.conv.dh;
+#pragma unroll
+                                    for (int q = 0; q < NPASS; ++q)
+                                        ptx::tma_load_5d(a_dst + q * A_TILE_BYTES + done * p.conv.OW * 128, map, p_cb * BK,
+                                                         tap_valid ? -p.conv.pw + p_tj * p.conv.dw : -(1 << 20), yr, img, q, bar);
+                                    done += h;
+                                    oh = 0;
+                                    ++img;
+                                }
+                            } else
 #pragma unroll
                             for (int q = 0; q < NPASS; ++q)
                                 ptx::tma_load_5d(a_dst + q * A_TILE_BYTES, &tmap_a, p_cb * BK, tap_valid ? x : -(1 << 20), y, pimg0, q, bar);
@@ -812,11 +838,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             if (PATCH) {
                 // Row of the tile -> (image, output row, output column) inside this tile's patch.
                 const int row = quarter * 32 + lane;
-                const int bw = row % p.conv.pbw, bh = (row / p.conv.pbw) % p.conv.pbh, bi = row / (p.conv.pbw * p.conv.pbh);
-                const int px = tm % p.conv.patches_w, py = (tm / p.conv.patches_w) % p.conv.patches_h;
-                const int64_t img = static_cast<int64_t>(tm / (p.conv.patches_w * p.conv.patches_h)) * p.conv.pbi + bi;
-                const int oh = py * p.conv.pbh + bh, ow = px * p.conv.pbw + bw;
-                row_ok = bi < p.conv.pbi && oh < p.conv.OH && ow < p.conv.OW && img * p.out_hw < p.M;
+                int64_t img;
+                int oh, ow;
+                if (p.conv.stack_rows > 0) {
+                    // Stacked rows: tile row r of this tile is row tm * stack_rows + r of the sequence img * OH + oh.
+                    const int r = row / p.conv.OW;
+                    const int64_t s = static_cast<int64_t>(tm) * p.conv.stack_rows + r;
+                    img = s / p.conv.OH;
+                    oh = static_cast<int>(s - img * p.conv.OH);
+                    ow = row - r * p.conv.OW;
+                    row_ok = r < p.conv.stack_rows && img * p.out_hw < p.M;
+                } else {
+                    const int bw = row % p.conv.pbw, bh = (row / p.conv.pbw) % p.conv.pbh, bi = row / (p.conv.pbw * p.conv.pbh);
+                    const int px = tm % p.conv.patches_w, py = (tm / p.conv.patches_w) % p.conv.patches_h;
+                    img = static_cast<int64_t>(tm / (p.conv.patches_w * p.conv.patches_h)) * p.conv.pbi + bi;
+                    oh = py * p.conv.pbh + bh;
+                    ow = px * p.conv.pbw + bw;
+                    row_ok = bi < p.conv.pbi && oh < p.conv.OH && ow < p.conv.OW && img * p.out_hw < p.M;
+                }
                 out_base = img * p.N * p.out_hw + static_cast<int64_t>(oh) * p.conv.OW + ow;
                 out_cs = p.out_hw;
                 cl_row = img * p.out_hw + static_cast<int64_t>(oh) * p.conv.OW + ow;

@@ -101,6 +101,10 @@ FAST_CASES = [
     (1, 64, 5, 300, 16, 1, 3, (1, 2, 0, 1, 1, 1)),      # output rows longer than one tile
     (2, 128, 28, 28, 64, 1, 1, (2, 2, 0, 0, 1, 1)),     # strided 1x1 (the shortcut convolutions)
     (2, 64, 40, 40, 8, 3, 3, (9, 9, 1, 1, 1, 1)),       # stride beyond the TMA element-stride range: cp.async path
+    # tiles of whole output rows that run on into the next image (one TMA box per image a tile touches)
+    (5, 64, 14, 14, 256, 3, 3, (1, 1, 1, 1, 1, 1)),     # nine rows per tile, 14 per image
+    (3, 64, 28, 28, 256, 3, 3, (2, 2, 1, 1, 1, 1)),     # the same with stride 2
+    (9, 128, 7, 7, 256, 3, 3, (1, 1, 1, 1, 1, 1)),      # eighteen rows per tile: up to four images in one tile
     # 64 output channels, three filter columns: one 192-column instruction per filter row, tiles laid out by lane quarters
     (2, 64, 28, 28, 64, 3, 3, (1, 1, 1, 1, 1, 1)),      # one quarter per output row, four rows per tile
     (1, 128, 30, 60, 64, 3, 3, (1, 1, 1, 1, 1, 1)),     # two quarters per row (30 + 30 outputs), two channel blocks
