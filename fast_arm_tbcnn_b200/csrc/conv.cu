@@ -524,12 +524,26 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                 const char* v = std::getenv("TBN_CONV_ROWS");
                 return !(v && v[0] == '0');
             }();
+            static const bool stack_rows_enabled = [] {
+                const char* v = std::getenv("TBN_CONV_STACK");
+                return !(v && v[0] == '0');
+            }();
             const int64_t pitch = round_up(OW + a.kw - 1, 8);
-            const int64_t rpbh = pitch <= tc::BM ? std::min<int64_t>(OH, tc::BM / pitch) : 0;
+            int64_t rpbh = pitch <= tc::BM ? std::min<int64_t>(OH, tc::BM / pitch) : 0;
+            // Stacked rows (conv_rows.cuh, Params::stack): tiles of BM / pitch consecutive rows of the sequence
+            // img * OH + oh where that needs at least 5 % fewer tiles than whole tiles per image.
+            const int64_t spbh = pitch <= tc::BM ? tc::BM / pitch : 0;
+            const int64_t plain_tiles = rpbh > 0 ? a.N * ((OH + rpbh - 1) / rpbh) : 0;
+            const int64_t stack_tiles = spbh > 0 ? (a.N * OH + spbh - 1) / spbh : 0;
+            const bool row_stack = stack_rows_enabled && spbh >= 1 && std::min<int64_t>(spbh, OH) <= 9 &&
+                                   stack_tiles * 20 <= plain_tiles * 19 && a.N * OH + tc::BM < (1LL << 31);
+            const int64_t row_tiles = row_stack ? stack_tiles : plain_tiles;
+            const int64_t row_max_h = row_stack ? std::min<int64_t>(spbh, OH) : rpbh;  // height of the largest box
+            if (row_stack) rpbh = spbh;
             const int64_t patch_tiles = ((OW + pbw - 1) / pbw) * ((OH + pbh - 1) / pbh) * ((a.N + pbi - 1) / pbi);
             const bool applicable = rows_enabled && !a.dense_w && a.sh == 1 && a.sw == 1 && a.dw == 1 && a.kw <= rows::kMaxTaps &&
                                     (bn == 64 || bn == 128) && npass * K <= tc::kMaxAccumSteps && rpbh >= 1 &&
-                                    a.N * ((OH + std::max<int64_t>(rpbh, 1) - 1) / std::max<int64_t>(rpbh, 1)) * 20 <= patch_tiles * 21 &&
+                                    row_tiles * 20 <= patch_tiles * 21 &&
                                     a.N * a.H * a.W * a.C * 2 < (1LL << 40) && a.W + a.pw < 32000;
             if (applicable) {
                 rows::Params rp = {};
@@ -548,7 +562,10 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                 rp.pitch = static_cast<int>(pitch);
                 rp.pbh = static_cast<int>(rpbh);
                 rp.tiles_per_image = static_cast<int>((OH + rpbh - 1) / rpbh);
-                const int64_t tiles_m = a.N * rp.tiles_per_image;
+                rp.stack = row_stack ? 1 : 0;
+                rp.images = static_cast<int>(a.N);
+                rp.max_h = static_cast<int>(row_max_h);
+                const int64_t tiles_m = row_tiles;
                 rp.tiles_n = static_cast<int>((N + bn - 1) / bn);
                 rp.a_box_bytes = static_cast<int>(npass * pitch * rpbh * 128);
                 rp.n_btiles = static_cast<int>(K / 64);
@@ -567,12 +584,21 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                                                 static_cast<cuuint64_t>(a.N), static_cast<cuuint64_t>(npass)};
                     const cuuint64_t gstride[4] = {static_cast<cuuint64_t>(a.C) * 2, static_cast<cuuint64_t>(a.W * a.C) * 2,
                                                    static_cast<cuuint64_t>(a.H * a.W * a.C) * 2, static_cast<cuuint64_t>(term_stride) * 2};
-                    const cuuint32_t box[5] = {tc::BK, static_cast<cuuint32_t>(pitch), static_cast<cuuint32_t>(rpbh), 1, 1};
+                    const cuuint32_t box[5] = {tc::BK, static_cast<cuuint32_t>(pitch), static_cast<cuuint32_t>(row_max_h), 1, 1};
                     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+                    rows::RowMaps row_maps = {};
+                    bool maps_ok = true;
+                    for (int64_t h = 1; row_stack && h < row_max_h; ++h) {  // the smaller box heights of stacked tiles
+                        const cuuint32_t hbox[5] = {tc::BK, static_cast<cuuint32_t>(pitch), static_cast<cuuint32_t>(h), 1, 1};
+                        maps_ok = maps_ok && encode(&row_maps.m[h - 1], f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                                    5, xs, gdim, gstride, hbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+                    }
                     const CUresult cr = encode(&map_x, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, xs, gdim,
                                                gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-                    if (cr == CUDA_SUCCESS) {
+                    if (cr == CUDA_SUCCESS && maps_ok) {
                         const bool one_term = tern_act || npass == 1;
                         // Resident filters when one column tile covers all output channels and they fit beside two stages.
                         int st_res = 0, st_str = 0;
@@ -593,8 +619,13 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                         }();
                         const int64_t qpr = (OW + rows::kQuarterOutputs - 1) / rows::kQuarterOutputs;
                         const int64_t wide_rows = (qpr == 1 || qpr == 2 || qpr == 4) ? 4 / qpr : 0;  // output rows per tile
+                        const int64_t wide_plain = wide_rows > 0 ? a.N * ((OH + wide_rows - 1) / wide_rows) : 0;
+                        const int64_t wide_stacked = wide_rows > 0 ? (a.N * OH + wide_rows - 1) / wide_rows : 0;
+                        const bool wide_stack = stack_rows_enabled && wide_rows > 0 && wide_stacked * 20 <= wide_plain * 19 &&
+                                                a.N * OH + tc::BM < (1LL << 31);
+                        const int64_t wide_tiles = wide_stack ? wide_stacked : wide_plain;
                         if (wide_enabled && bn == 64 && N == 64 && a.kw == rows::kMaxTaps && resident && wide_rows > 0 &&
-                            (OH + wide_rows - 1) / wide_rows * 4 <= (OH + rpbh - 1) / rpbh * 5) {  // at most a quarter more tiles
+                            wide_tiles * 4 <= row_tiles * 5) {  // at most a quarter more tiles
                             const int st_wide = one_term ? rows::stages_that_fit<64, 1, true, true>(rp.n_btiles)
                                                          : rows::stages_that_fit<64, 2, true, true>(rp.n_btiles);
                             CUtensorMap map_q;  // one lane quarter: 32 pixels of one input row, 64 channels
@@ -602,12 +633,13 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                             const CUresult qr = encode(&map_q, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, xs,
                                                        gdim, gstride, qbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-                            if (st_wide >= 2 && qr == CUDA_SUCCESS && a.N * ((OH + wide_rows - 1) / wide_rows) < (1LL << 31)) {
+                            if (st_wide >= 2 && qr == CUDA_SUCCESS && wide_tiles < (1LL << 31)) {
                                 rp.nstages = st_wide;
                                 rp.qpr = static_cast<int>(qpr);
                                 rp.pbh = static_cast<int>(wide_rows);
                                 rp.tiles_per_image = static_cast<int>((OH + wide_rows - 1) / wide_rows);
-                                rp.tiles_m = static_cast<int>(a.N * rp.tiles_per_image);
+                                rp.stack = wide_stack ? 1 : 0;
+                                rp.tiles_m = static_cast<int>(wide_tiles);
                                 rp.a_box_bytes = static_cast<int>(npass * tc::BM * 128);
                                 return one_term ? rows::launch<64, 1, true, true>(map_q, maps.neg, rp, a.st)
                                                 : rows::launch<64, 2, true, true>(map_q, maps.neg, rp, a.st);
@@ -615,11 +647,11 @@ int32_t conv_common(const ConvArgs& a, int npass, bool tern_act, float lo, float
                         }
                         if (rp.nstages >= 2) {
                             if (bn == 64) {
-                                if (one_term) return resident ? rows::launch<64, 1, true>(map_x, maps.neg, rp, a.st) : rows::launch<64, 1, false>(map_x, maps.neg, rp, a.st);
-                                return resident ? rows::launch<64, 2, true>(map_x, maps.neg, rp, a.st) : rows::launch<64, 2, false>(map_x, maps.neg, rp, a.st);
+                                if (one_term) return resident ? rows::launch<64, 1, true>(map_x, maps.neg, rp, a.st, &row_maps) : rows::launch<64, 1, false>(map_x, maps.neg, rp, a.st, &row_maps);
+                                return resident ? rows::launch<64, 2, true>(map_x, maps.neg, rp, a.st, &row_maps) : rows::launch<64, 2, false>(map_x, maps.neg, rp, a.st, &row_maps);
                             }
-                            if (one_term) return resident ? rows::launch<128, 1, true>(map_x, maps.neg, rp, a.st) : rows::launch<128, 1, false>(map_x, maps.neg, rp, a.st);
-                            return resident ? rows::launch<128, 2, true>(map_x, maps.neg, rp, a.st) : rows::launch<128, 2, false>(map_x, maps.neg, rp, a.st);
+                            if (one_term) return resident ? rows::launch<128, 1, true>(map_x, maps.neg, rp, a.st, &row_maps) : rows::launch<128, 1, false>(map_x, maps.neg, rp, a.st, &row_maps);
+                            return resident ? rows::launch<128, 2, true>(map_x, maps.neg, rp, a.st, &row_maps) : rows::launch<128, 2, false>(map_x, maps.neg, rp, a.st, &row_maps);
                         }
                     }
                 }

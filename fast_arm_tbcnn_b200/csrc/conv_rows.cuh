@@ -53,6 +53,11 @@ struct Params {
     int pitch, pbh;        // GEMM rows per output row (multiple of 8), output rows per tile (pitch * pbh <= 128)
     int qpr;               // WIDE: quarters (boxes of 32 pixels, 30 outputs each) per output row; pbh = 4 / qpr
     int tiles_per_image;   // ceil(OH / pbh)
+    // stack != 0: the output rows of all `images` form one sequence s = img * OH + oh and a tile is pbh consecutive
+    // rows of it, whatever images they come from (no half-empty last tile per image).  The rows from one image are
+    // one TMA box; its height belongs to the tensor map: heights below the largest travel in RowMaps.  (WIDE tiles
+    // are built from per-row boxes anyway and need no extra maps.)
+    int stack, images, max_h;
     int tiles_m, tiles_n;  // images * tiles_per_image, ceil(N / BN)
     int a_box_bytes;       // bytes one activation box delivers, all terms together
     int nstages;           // pipeline depth (2 .. kMaxStages), chosen by the host from the shared memory left
@@ -67,6 +72,10 @@ struct Params {
 };
 
 constexpr int kQuarterOutputs = 30;  // WIDE: output pixels of a 32-row quarter (rows 30 and 31 only feed the shifts)
+
+struct RowMaps {
+    CUtensorMap m[8];  // activation maps with box heights 1 .. 8 (stacked tiles)
+};
 
 template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
 struct Cfg {
@@ -91,7 +100,8 @@ inline int smem_bytes(int nstages, int n_btiles) {
 
 template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
 __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                                                                const __grid_constant__ CUtensorMap tmap_w, const Params p) {
+                                                                const __grid_constant__ CUtensorMap tmap_w,
+                                                                const __grid_constant__ RowMaps row_maps, const Params p) {
     using C = Cfg<BN, NPASS, RESIDENT, WIDE>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -159,8 +169,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int tm = t % p.tiles_m, tn = t / p.tiles_m;
-                const int img = tm / p.tiles_per_image;
-                const int oh0 = (tm - img * p.tiles_per_image) * p.pbh;
+                int img, oh0;  // first output row of the tile
+                if (p.stack) {
+                    img = (tm * p.pbh) / p.OH;
+                    oh0 = tm * p.pbh - img * p.OH;
+                } else {
+                    img = tm / p.tiles_per_image;
+                    oh0 = (tm - img * p.tiles_per_image) * p.pbh;
+                }
                 for (int ti = 0; ti < p.kh && ok; ++ti) {
                     for (int cb = 0; cb < p.cblocks; ++cb) {
                         if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, p.err_word, kErrWaitEmpty)) {
@@ -178,10 +194,29 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
                             // columns 30 (qq % qpr) .. + 29 (and the two pixels to their right for the shifted taps).
                             for (int qq = 0; qq < 4; ++qq) {
                                 const int x = (qq % p.qpr) * kQuarterOutputs - p.pw;
-                                const int y = oh0 + qq / p.qpr - p.ph + ti * p.dh;
+                                int oh = oh0 + qq / p.qpr, im = img;
+                                if (p.stack && oh >= p.OH) {  // the tile runs on into the next image(s)
+                                    im += oh / p.OH;
+                                    oh %= p.OH;
+                                }
+                                const int y = oh - p.ph + ti * p.dh;
 #pragma unroll
                                 for (int q = 0; q < NPASS; ++q)
-                                    ptx::tma_load_5d(a_dst + q * tc::A_TILE_BYTES + qq * 32 * 128, &tmap_x, cb * tc::BK, x, y, img, q, bar);
+                                    ptx::tma_load_5d(a_dst + q * tc::A_TILE_BYTES + qq * 32 * 128, &tmap_x, cb * tc::BK, x, y, im, q, bar);
+                            }
+                        } else if (p.stack) {
+                            // One box per image the tile's rows come from (rows past the last image: zeros).
+                            int im = img, oh = oh0, done = 0;
+                            while (done < p.pbh) {
+                                const int h = min(p.pbh - done, p.OH - oh);
+                                const CUtensorMap* map = h == p.max_h ? &tmap_x : &row_maps.m[h - 1];
+#pragma unroll
+                                for (int q = 0; q < NPASS; ++q)
+                                    ptx::tma_load_5d(a_dst + q * tc::A_TILE_BYTES + done * p.pitch * 128, map, cb * tc::BK, -p.pw,
+                                                     oh - p.ph + ti * p.dh, im, q, bar);
+                                done += h;
+                                oh = 0;
+                                ++im;
                             }
                         } else {
 #pragma unroll
@@ -292,8 +327,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
             // A group drains every third tile -- or, WIDE, every third 32-column chunk: chunk (iter, c) is job 2 iter + c.
             if (!WIDE && iter % kEpiGroups != group) continue;
             const int tm = t % p.tiles_m, tn = t / p.tiles_m;
-            const int img = tm / p.tiles_per_image;
-            const int oh0 = (tm - img * p.tiles_per_image) * p.pbh;
             const int buf = iter % C::ACC_BUFS;
             const int n0 = tn * BN;
             if (tn != staged_tn) {  // per-channel scale and bias of this column tile: reloaded only when it changes
@@ -309,8 +342,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
             const int row = quarter * 32 + lane;
             const int bh = WIDE ? quarter / p.qpr : row / p.pitch;
             const int bw = WIDE ? (quarter % p.qpr) * kQuarterOutputs + lane : row - bh * p.pitch;
-            const int oh = oh0 + bh;
-            const bool row_ok = bh < p.pbh && bw < p.OW && oh < p.OH && (!WIDE || lane < kQuarterOutputs);
+            int img, oh;
+            if (p.stack) {
+                const int srow = tm * p.pbh + bh;  // row of the sequence img * OH + oh
+                img = srow / p.OH;
+                oh = srow - img * p.OH;
+            } else {
+                img = tm / p.tiles_per_image;
+                oh = (tm - img * p.tiles_per_image) * p.pbh + bh;
+            }
+            const bool row_ok = bh < p.pbh && bw < p.OW && oh < p.OH && img < p.images && (!WIDE || lane < kQuarterOutputs);
             const int64_t pix = static_cast<int64_t>(oh) * p.OW + bw;          // pixel inside the image
             const int64_t out_base = static_cast<int64_t>(img) * p.N * hw + pix;  // + n * hw
             const int64_t cl_row = static_cast<int64_t>(img) * hw + pix;
@@ -445,14 +486,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_rows_kernel(const __grid_con
 }
 
 template <int BN, int NPASS, bool RESIDENT, bool WIDE = false>
-int32_t launch(const CUtensorMap& tmap_x, const CUtensorMap& tmap_w, const Params& p, cudaStream_t st) {
+int32_t launch(const CUtensorMap& tmap_x, const CUtensorMap& tmap_w, const Params& p, cudaStream_t st,
+               const RowMaps* row_maps = nullptr) {
+    static const RowMaps no_maps = {};
     auto kernel = conv_rows_kernel<BN, NPASS, RESIDENT, WIDE>;
     const int smem = smem_bytes<BN, NPASS, RESIDENT, WIDE>(p.nstages, p.n_btiles);
     TBN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int total = p.tiles_m * p.tiles_n;
     const int grid = std::max(1, std::min(total, sm_count()));
     profile_begin(kProfGemm, st);
-    kernel<<<grid, kThreads, smem, st>>>(tmap_x, tmap_w, p);
+    kernel<<<grid, kThreads, smem, st>>>(tmap_x, tmap_w, row_maps ? *row_maps : no_maps, p);
     profile_end(kProfGemm, st);
     return launched("conv_rows_kernel");
 }

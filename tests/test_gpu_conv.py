@@ -105,6 +105,8 @@ FAST_CASES = [
     (5, 64, 14, 14, 256, 3, 3, (1, 1, 1, 1, 1, 1)),     # nine rows per tile, 14 per image
     (3, 64, 28, 28, 256, 3, 3, (2, 2, 1, 1, 1, 1)),     # the same with stride 2
     (9, 128, 7, 7, 256, 3, 3, (1, 1, 1, 1, 1, 1)),      # eighteen rows per tile: up to four images in one tile
+    (5, 64, 14, 14, 128, 3, 3, (1, 1, 1, 1, 1, 1)),     # row mode: eight rows per tile running on into the next image
+    (3, 64, 10, 28, 64, 3, 3, (1, 1, 1, 1, 1, 1)),      # the same in the three-column kernel (four rows per tile, 10 per image)
     # 64 output channels, three filter columns: one 192-column instruction per filter row, tiles laid out by lane quarters
     (2, 64, 28, 28, 64, 3, 3, (1, 1, 1, 1, 1, 1)),      # one quarter per output row, four rows per tile
     (1, 128, 30, 60, 64, 3, 3, (1, 1, 1, 1, 1, 1)),     # two quarters per row (30 + 30 outputs), two channel blocks
