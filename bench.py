@@ -463,9 +463,13 @@ def cnn_block(args, ctx):
     ws, _ = L.conv_workspace(x.shape, 128, 3, 3, dev, order)
     y = torch.empty((b1 - b0, 128, 14, 14), device=dev)
     p = (1, 1, 1, 1, 1, 1)
+    conv_call = lambda: L.conv2d_fxb(x, words, w.shape, p, alpha=alpha, bias=bias, workspace=ws, out=y, order=order)  # noqa: E731
+    for _ in range(2):   # first launches (code upload) stay outside the per-kernel events
+        conv_call()
+    torch.cuda.synchronize()
     L.profile_read()
     L.profile_enable(True)
-    ms = timed(lambda: L.conv2d_fxb(x, words, w.shape, p, alpha=alpha, bias=bias, workspace=ws, out=y, order=order), 10)
+    ms = timed(conv_call, 10, warm=0)
     prof = L.profile_read()
     L.profile_enable(False)
     flops = 2.0 * 4096 * 196 * 128 * 576
