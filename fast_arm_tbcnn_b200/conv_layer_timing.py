@@ -4,8 +4,9 @@
 
 `form` selects what the layer reads and writes: `nchw` (default: fp32 NCHW in and out, pre-pass included), or, as
 inside a network (input already in channels-last bf16 terms, ReLU in the epilogue; needs C_in == C_out for the
-residual): `cl` (writes the channels-last terms only), `y` (writes fp32 NCHW only), `y_cl_res` (adds a residual and
-writes both forms -- the second convolution of a ResNet block).
+residual): `cl` (writes the channels-last terms only), `y` (writes fp32 NCHW only), `y_cl` (both), `y_res` / `cl_res`
+(one form plus a residual), `y_cl_res` (adds a residual and writes both forms -- the second convolution of a ResNet
+block).
 
 Prints the call time (CUDA events around back-to-back calls) and the kernel / pre-pass times from the library's own
 per-kernel events (tbn_cuda_profile_enable).  TBN_CONV_ROWS=0 in the environment selects the patch-mode kernel
@@ -40,6 +41,8 @@ def main(argv):
         _, x_cl = L.conv2d_chain(tuple(x.shape), wd, tuple(w.shape), p, x=x, want_y=False, want_y_cl=True, alpha=alpha,
                                  epilogue=capi.EPI_RELU, workspace=ws)
         kw = {"cl": dict(want_y=False, want_y_cl=True), "y": dict(want_y=True, want_y_cl=False),
+              "y_cl": dict(want_y=True, want_y_cl=True), "y_res": dict(want_y=True, want_y_cl=False, residual=x),
+              "cl_res": dict(want_y=False, want_y_cl=True, residual=x),
               "y_cl_res": dict(want_y=True, want_y_cl=True, residual=x)}[form]
 
         def call():
