@@ -577,6 +577,47 @@ def test_chained_convolutions_are_bit_identical(tbn, weights):
     assert torch.equal(plain, chained) and float(plain.abs().sum()) > 0
 
 
+def _random_fast_cases(count, seed):
+    """Seeded random channels-last convolution shapes: sizes chosen so that every tile geometry the library picks from
+    (rectangular patches, stacked rows, row mode with and without stacking, the three-column kernel, strided and 1x1
+    filters) is hit several times."""
+    rng = np.random.default_rng(seed)
+    cases = []
+    while len(cases) < count:
+        c = int(rng.choice([64, 128]))
+        m = int(rng.choice([64, 64, 128, 256, 40]))
+        k = int(rng.choice([1, 3, 3, 3]))
+        s = int(rng.choice([1, 1, 1, 2]))
+        h, w = int(rng.integers(3, 40)), int(rng.integers(3, 62))
+        n = int(rng.integers(1, 7))
+        pad = int(rng.integers(0, 2)) if k == 3 else 0
+        if (h + 2 * pad - k) // s + 1 < 1 or (w + 2 * pad - k) // s + 1 < 1:
+            continue
+        cases.append((n, c, h, w, m, k, k, (s, s, pad, pad, 1, 1)))
+    return cases
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", _random_fast_cases(36, seed=77))
+def test_conv_channels_last_random_shapes(tbn, oracle, case):
+    """Float x binary convolution with tap-major filters on random shapes, with bias, residual and ReLU in the epilogue,
+    against the reference's float convolution on the dequantised filters; the channels-last result form equals the
+    split of the fp32 result."""
+    import torch
+    from oracle import graphs
+    x, w, b, p = _conv_inputs(case, seed=case[2] * 100 + case[3])
+    dx, dw_, db = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda()
+    words, alpha = tbn.lib.quant_pack_binary(tbn.lib.permute_filters(dw_), tbn.LAYOUT_NK)
+    expect = oracle.conv2d_f32(x, graphs.dequantise(w), b, p)
+    res = np.random.default_rng(5).standard_normal(expect.shape, dtype=np.float32)
+    y, y_cl = tbn.lib.conv2d_chain(tuple(x.shape), {"words": words}, tuple(w.shape), p, x=dx, want_y=True, want_y_cl=True,
+                                   alpha=alpha, bias=db, residual=torch.from_numpy(res).cuda(), epilogue=tbn.EPI_RELU)
+    tbn.lib.sync()
+    assert rel_l2(y.cpu().numpy(), np.maximum(expect + res, 0.0)) <= TOL_FP32
+    hi = y.permute(0, 2, 3, 1).bfloat16()
+    assert torch.equal(y_cl[0], hi) and torch.equal(y_cl[1], (y.permute(0, 2, 3, 1) - hi.float()).bfloat16())
+
+
 @pytest.mark.gpu
 def test_three_column_instruction_with_residual_and_both_result_forms(tbn, oracle):
     """64 -> 64 channels, 3x3, stride 1 (the layers that run one 192-column instruction per filter row): input taken
