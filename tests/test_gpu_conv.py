@@ -619,6 +619,28 @@ def test_conv_channels_last_random_shapes(tbn, oracle, case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("case", _random_fast_cases(16, seed=78))
+def test_conv_float_filters_and_tbn_mode_random_shapes(tbn, oracle, case):
+    """The same random shapes with float filters (two terms on both sides: within 1e-5 of the reference's float
+    convolution) and in TBN mode (ternarised activations x sign filters: bit-equal to the Session's integer path)."""
+    import torch
+    from oracle import graphs
+    x, w, b, p = _conv_inputs(case, seed=case[2] * 100 + case[3] + 1)
+    dx, dw_, db = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda()
+    order = tbn.CONV_WEIGHTS_TAP_MAJOR
+    yd = tbn.lib.conv2d_f32(dx, tbn.lib.dense_pack(tbn.lib.permute_filters(dw_), tbn.LAYOUT_NK), w.shape, p, bias=db, order=order)
+    tbn.lib.sync()
+    assert rel_l2(yd.cpu().numpy(), oracle.conv2d_f32(x, w, b, p)) <= TOL_FP32
+    wq = graphs.dequantise(w)
+    dwq = torch.from_numpy(wq).cuda()
+    words_q, _ = tbn.lib.quant_pack_binary(tbn.lib.permute_filters(dwq), tbn.LAYOUT_NK, 0.0, True, want_alpha=False)
+    yq = tbn.lib.conv2d_tbn(dx, words_q, w.shape, p, alpha=tbn.lib.channel_abs_mean(dwq), bias=db,
+                            epilogue=tbn.EPI_BIAS_BEFORE_ALPHA, order=order)
+    tbn.lib.sync()
+    assert np.array_equal(yq.cpu().numpy(), oracle.conv2d_tbn_session(x, wq, b, p))
+
+
+@pytest.mark.gpu
 def test_three_column_instruction_with_residual_and_both_result_forms(tbn, oracle):
     """64 -> 64 channels, 3x3, stride 1 (the layers that run one 192-column instruction per filter row): input taken
     as channels-last terms, residual added, ReLU, fp32 NCHW and channels-last results written -- against the
