@@ -68,6 +68,27 @@ __device__ __forceinline__ uint4 unpack8(uint32_t neg_byte, uint32_t pos_byte, u
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// The same with fewer instructions on the integer pipe (the build warps of the GEMM spend their issue slots here; the
+// ternary kernel ran 20 % behind the binary one on them).  Four bits become four bytes with one multiply and one mask
+// (bit e of a nibble lands at bit 8 e: the partial products of 0x00204081 never meet), a value's code is its byte
+// (binary: 0 plus, 1 minus; ternary: 0 zero, 1 plus, 2 minus = pos + 2 neg), and each pair of values is ONE byte
+// permute out of two small byte tables -- the high and the low byte of the operand-type constants -- whose selector is
+// code * 0x11 + 0x0404 (prmt reads only the low 16 bits of its selector).
+//   binary:  lut_hi = {hi(+1), hi(-1)},     lut_lo = {lo(+1), lo(-1)}          (byte 0, 1 of each word)
+//   ternary: lut_hi = {0, hi(+1), hi(-1)},  lut_lo = {0, lo(+1), lo(-1)}       (byte 0, 1, 2)
+__device__ __forceinline__ uint32_t nibble_to_bytes(uint32_t bits4) { return (bits4 * 0x00204081u) & 0x01010101u; }
+
+template <bool TERNARY>
+__device__ __forceinline__ uint4 unpack8_lut(uint32_t neg_byte, uint32_t pos_byte, uint32_t lut_hi, uint32_t lut_lo) {
+    uint32_t lo4 = nibble_to_bytes(neg_byte & 0xFu), hi4 = nibble_to_bytes(neg_byte >> 4);  // values 0-3, 4-7
+    if (TERNARY) {
+        lo4 = nibble_to_bytes(pos_byte & 0xFu) + 2u * lo4;
+        hi4 = nibble_to_bytes(pos_byte >> 4) + 2u * hi4;
+    }
+    return make_uint4(__byte_perm(lut_hi, lut_lo, lo4 * 0x11u + 0x0404u), __byte_perm(lut_hi, lut_lo, (lo4 >> 16) * 0x11u + 0x0404u),
+                      __byte_perm(lut_hi, lut_lo, hi4 * 0x11u + 0x0404u), __byte_perm(lut_hi, lut_lo, (hi4 >> 16) * 0x11u + 0x0404u));
+}
+
 // The one-pass fp16 mode scales the activations of a call by a power of two so that the largest magnitude lands in
 // [2^14, 2^15): nothing overflows fp16 and values down to 2^-28 of the largest stay normal.  `amax_bits` is the
 // bit pattern of max |a| (a non-negative float).  mul * inv == 1 exactly; the epilogue multiplies by inv.
@@ -170,10 +191,15 @@ struct Cfg {
     // k-blocks covered by one packed-word tile.  A TMA box is delivered row by row (a row here = the words of one
     // column), so longer rows mean fewer rows per k-block for the TMA unit: 32-byte rows (4 k-blocks) where the
     // shared memory allows it, 16-byte rows (2 k-blocks) with two planes or with the staging buffers of MULTI.
-    // (Measured A/B at 16384^3 on one box: 11.74-11.82 ms against 11.67-11.85 ms -- no difference; the kernel is
-    // not bound by the TMA unit.  Kept: it halves the word-tile loads.)
-    static constexpr int WORD_KB = (!TERNARY && !MULTI && !CONV && BSRC == 0) ? 4 : 2;
-    static constexpr int kWordStages = BSRC != 0 ? 1 : (CONV ? kWordStagesConv : kWordStagesGemm);  // TMA-fed weights use no words
+    // (Measured A/B at 16384^3 on one box, binary: 11.74-11.82 ms against 11.67-11.85 ms -- no difference; with TWO
+    // planes the 16-byte rows are what binds: 256 activation rows plus 2 x 128 word rows per k-block through a TMA unit
+    // that moves a row in 3-4 cycles is longer than the k-block's MMAs, and the ternary 4096 x 4096 x 11008 product ran
+    // 20 % slower than the binary one until its word rows were 32 bytes too.)
+    static constexpr int WORD_KB = (!MULTI && !CONV && BSRC == 0) ? 4 : 2;
+    // Word tiles in flight.  The build warps copy a tile's words to registers as soon as it arrives and hand the slot
+    // back at once, so the two 4-k-block planes of the ternary GEMM (16 KB) get along with a single slot -- two
+    // would cost a pipeline stage.  (TMA-fed weights use no words.)
+    static constexpr int kWordStages = BSRC != 0 ? 1 : (CONV ? kWordStagesConv : ((TERNARY && WORD_KB == 4) ? 1 : kWordStagesGemm));
     static constexpr int B_TILE_BYTES = BN * BK * 2;
     static constexpr int B_TERMS = DENSE ? 2 : 1;  // dense weights: hi and lo bf16 terms
     static constexpr int B_BYTES = B_TERMS * B_TILE_BYTES;
@@ -547,13 +573,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         static_assert(BN <= kBuildThreads, "one build thread per weight column of the tile");
         const int r = threadIdx.x - 64;  // weight column (row of the K-major weight tile) of this thread
         const uint32_t one16 = p.f16 ? kOneF16 : kOneBf16;
+        // byte tables of unpack8_lut: binary {+1, -1}, ternary {0, +1, -1}
+        const uint32_t hi_p = one16 >> 8, hi_m = hi_p | 0x80u, lo_b = one16 & 0xffu;
+        const uint32_t lut_hi = TERNARY ? ((hi_p << 8) | (hi_m << 16)) : (hi_p | (hi_m << 8));
+        const uint32_t lut_lo = TERNARY ? ((lo_b << 8) | (lo_b << 16)) : (lo_b | (lo_b << 8));
         // CONV mode: this thread also builds activation row (r & 127), 16-byte chunks (r >> 7) + {0, 2, 4, 6}.
         const int a_row = r & (BM - 1);
         const int a_chunk0 = r >> 7;
         int stage = 0, wstage = 0;
         uint32_t phase = 0, wphase = 0;
         bool ok = true;
-        uint4 wn = make_uint4(0u, 0u, 0u, 0u), wp = make_uint4(0u, 0u, 0u, 0u);
+        uint4 wn = make_uint4(0u, 0u, 0u, 0u), wp = make_uint4(0u, 0u, 0u, 0u), wp2 = make_uint4(0u, 0u, 0u, 0u);
         uint4 wn2 = make_uint4(0u, 0u, 0u, 0u);  // words of the third and fourth k-block of a 4-k-block tile
         // FAST: oldest stage whose copies are in flight and whose arrive is still owed, and how many are owed.
         constexpr int kCopyLag = C::STAGES >= 4 ? 2 : 1;
@@ -644,10 +674,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                         wn = ptx::ld_shared_v4(wt);
                         if (WORD_KB == 4) wn2 = ptx::ld_shared_v4(wt + 16);
                         if (TERNARY) wp = ptx::ld_shared_v4(wt + BN * C::WORD_ROW_BYTES);
+                        if (TERNARY && WORD_KB == 4) wp2 = ptx::ld_shared_v4(wt + BN * C::WORD_ROW_BYTES + 16);
                     }
                     // The slot may be refilled by TMA as soon as this arrive lands, so the loads above
                     // must have returned their data first: the arrive is made to depend on them.
-                    ptx::mbar_arrive_after(bar_empty_w + 8 * wstage, wn.x ^ wn.w ^ wp.x ^ wp.w ^ wn2.x ^ wn2.w);
+                    ptx::mbar_arrive_after(bar_empty_w + 8 * wstage, wn.x ^ wn.w ^ wp.x ^ wp.w ^ wn2.x ^ wn2.w ^ wp2.x ^ wp2.w);
                     if (++wstage == kWordStages) {
                         wstage = 0;
                         wphase ^= 1u;
@@ -686,13 +717,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     uint8_t* row = stage_ptr + r * 128;
                     const uint4 wsel = (WORD_KB == 4 && (kb & 2)) ? wn2 : wn;
                     const uint32_t nw[2] = {(kb & 1) ? wsel.z : wsel.x, (kb & 1) ? wsel.w : wsel.y};
-                    const uint32_t pw[2] = {(kb & 1) ? wp.z : wp.x, (kb & 1) ? wp.w : wp.y};
+                    const uint4 psel = (WORD_KB == 4 && (kb & 2)) ? wp2 : wp;
+                    const uint32_t pw[2] = {(kb & 1) ? psel.z : psel.x, (kb & 1) ? psel.w : psel.y};
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         const uint32_t nb = (nw[c >> 2] >> (8 * (c & 3))) & 0xffu;
                         const uint32_t pb = (pw[c >> 2] >> (8 * (c & 3))) & 0xffu;
                         // 16-byte chunk c of row r lands at chunk (c ^ (r & 7)): the 128-byte swizzle.
-                        *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8<TERNARY>(nb, pb, one16);
+                        *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = unpack8_lut<TERNARY>(nb, pb, lut_hi, lut_lo);
                     }
                 }
                 if (FAST) {
@@ -1134,7 +1166,7 @@ int32_t dispatch_bn(int bn, const TensorMaps& maps, const tc::Params& p, cudaStr
 }
 
 // Words per row of the packed-word box that the kernel instantiation (plain GEMM, AMODE 0 or 3) expects.
-inline int gemm_words_per_row(bool ternary, bool multi) { return (!ternary && !multi) ? 8 : 4; }
+inline int gemm_words_per_row(bool ternary, bool multi) { (void)ternary; return !multi ? 8 : 4; }
 
 // Tensor map over bf16 terms laid out [terms][rows_pad][K_pad] (split activations or split dense weights):
 // box = 64 k x `box_rows` rows x 1 term, 128-byte swizzle.
